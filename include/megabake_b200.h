@@ -1,0 +1,234 @@
+/*
+ * megabake_b200 -- C ABI of the B200 (sm_100a) persistent-megakernel decoder backend.
+ *
+ * The Python host (megabake_b200.planner) turns one captured decoder invocation into a
+ * table of fixed-size phase records plus a table of device addresses ("slots") and hands
+ * both to this library.  One call of mb_plan_launch() is one cooperative persistent
+ * kernel launch that executes every phase in order, separated by grid barriers where a
+ * record asks for one.
+ *
+ * What each entry point replaces in the reference (paths relative to the reference
+ * project root):
+ *   mb_plan_create   compile_plan(): emit + JIT the CuTe module, occupancy admission
+ *                    (src/megabake/compiler.py:625-796) and the phase/GEMM tables built by
+ *                    _emit_table_module (src/megabake/codegen.py:728-1784)
+ *   mb_plan_bind     _RuntimeState.rebind / _fast_table_rebind: static slot addresses
+ *                    (src/megabake/compiler.py:2156-2208)
+ *   mb_plan_launch   _RuntimeState.prepare_launch + run_compiled_program: per-call dynamic
+ *                    addresses and the cooperative launch
+ *                    (src/megabake/compiler.py:2464-2524, src/megabake/runtime.py:153-190)
+ *   mb_plan_status   the device-side trap_if sites (src/megabake/runtime.py:139-149,
+ *                    src/megabake/bodies/cuda/sm100/attention.py:982): here a status word
+ *                    the host reads after it synchronised, never a trap
+ *   mb_plan_reset    no counterpart (the reference traps; a trapped context is lost)
+ *   mb_plan_destroy  release of _RuntimeState buffers
+ *   mb_plan_query    CompiledResources / launch requirements
+ *                    (src/megabake/codegen.py:100-143)
+ *
+ * Conventions: every function returns an int code (MB_OK == 0) and never throws, aborts
+ * or exits.  Pointers are borrowed for the duration of the call; slot addresses are
+ * copied.  A plan is not re-entrant (the caller serialises calls on one plan); different
+ * plans are independent.  No function synchronises the device except mb_plan_create,
+ * mb_plan_bind, mb_plan_status, mb_plan_reset and mb_plan_destroy.  mb_plan_launch
+ * performs no allocation and no host synchronisation and always passes the same kernel
+ * parameters for the same dynamic addresses, so it can be captured in a CUDA graph.
+ */
+#ifndef MEGABAKE_B200_H
+#define MEGABAKE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MB_ABI_VERSION 1
+
+/* ---- return codes of the host API ------------------------------------------------ */
+enum mb_error {
+    MB_OK = 0,
+    MB_ERR_INVALID = 1,     /* bad argument / malformed descriptor                      */
+    MB_ERR_CUDA = 2,        /* a CUDA runtime call failed (mb_last_cuda_error())         */
+    MB_ERR_UNSUPPORTED = 3, /* body / shape outside what the kernels implement           */
+    MB_ERR_RESOURCE = 4,    /* shared memory or co-residency admission failed            */
+    MB_ERR_UNBOUND = 5,     /* launch before every static slot was bound                 */
+    MB_ERR_VERSION = 6      /* descriptor abi_version != MB_ABI_VERSION                  */
+};
+
+/* ---- device status word (read back by mb_plan_status) ---------------------------- */
+enum mb_status_code {
+    MB_ST_OK = 0,
+    MB_ST_BARRIER_TIMEOUT = 1, /* a grid-barrier wait ran out                            */
+    MB_ST_PIPE_TIMEOUT = 2,    /* a shared-memory pipeline (mbarrier) wait ran out       */
+    MB_ST_KV_OVERFLOW = 3,     /* valid_length + 1 > cache capacity                      */
+    MB_ST_TOKEN_RANGE = 4,     /* an input id outside [0, vocab)                         */
+    MB_ST_BAD_PHASE = 5,       /* unknown body id in the phase table                     */
+    MB_ST_TMEM = 6             /* tensor-memory allocation failed                        */
+};
+
+typedef struct mb_status {
+    int32_t code;   /* enum mb_status_code of the first fault, 0 if none                */
+    int32_t phase;  /* phase index that recorded it                                     */
+    int32_t detail; /* body-specific (CTA index, offending value ...)                   */
+    int32_t calls;  /* launches completed on this plan since create/reset               */
+} mb_status;
+
+/* ---- plan modes ------------------------------------------------------------------- */
+enum mb_mode { MB_MODE_DECODE = 0, MB_MODE_PREFILL = 1 };
+
+/* ---- device bodies ---------------------------------------------------------------- */
+enum mb_body {
+    MB_BODY_NOP = 0,
+    /* Skinny GEMM for <= 8 activation rows: out[r, n] = epi(pro(x)[r, :] . W[n, :] + b[n]).
+     * Weight rows are streamed by a dedicated producer warp with bulk async copies into a
+     * shared-memory ring; up to three weight segments share one activation (q|k|v), or two
+     * matrices are paired (gate|up) for a gated-activation epilogue.                      */
+    MB_BODY_GEMV = 1,
+    /* One-token attention over the KV cache: RoPE of q and the new k, append of k/v at
+     * valid_length, split-key flash decoding with an online softmax, last-arriver merge.  */
+    MB_BODY_ATTN_DECODE = 2,
+    /* ---- prefill bodies ---- */
+    MB_BODY_EMBED_ROWS = 3,   /* gather embedding rows (+ scalar scale)                    */
+    MB_BODY_RMSNORM_ROWS = 4, /* row-wise RMSNorm                                          */
+    MB_BODY_GEMM_TC = 5,      /* tcgen05/TMEM GEMM fed by TMA                              */
+    MB_BODY_ROPE_ROWS = 6,    /* rotary embedding of q and k rows, in place                */
+    MB_BODY_ATTN_PREFILL = 7, /* causal / masked softmax attention, tensor-core flash form */
+    MB_BODY_COUNT = 8
+};
+
+/* mb_phase.flags */
+#define MB_FLAG_BARRIER 1      /* grid barrier after the phase                            */
+#define MB_FLAG_BUMP_LENGTH 2  /* after that barrier CTA 0 adds 1 to the int32 at
+                                  slot[MB_AT_S_LEN] (attention phases only)                */
+
+/* GEMV / GEMM prologues (applied to the activation rows) */
+enum mb_prologue {
+    MB_PRO_NONE = 0,
+    MB_PRO_RMS_LLAMA = 1, /* bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))                    */
+    MB_PRO_RMS_GEMMA = 2  /* bf16(x * rsqrt(mean(x^2) + eps) * (1 + w)), all in fp32       */
+};
+
+/* GEMV / GEMM epilogues.  acc is the fp32 accumulator (+ fp32 bias); y = bf16(acc). */
+enum mb_epilogue {
+    MB_EPI_NONE = 0,          /* out = y                                                   */
+    MB_EPI_RESIDUAL = 1,      /* out = bf16(res + y)                                       */
+    MB_EPI_SILU_MUL = 2,      /* paired: out = bf16(bf16(silu(y_gate)) * y_up)             */
+    MB_EPI_GELU_TANH_MUL = 3  /* paired: out = bf16(bf16(gelu_tanh(y_gate)) * y_up)        */
+};
+
+/* ---- phase record ------------------------------------------------------------------ */
+#define MB_PHASE_INTS 24
+#define MB_PHASE_FLOATS 4
+#define MB_PHASE_SLOTS 20
+
+typedef struct mb_phase {
+    int32_t body;
+    int32_t flags;
+    int32_t i[MB_PHASE_INTS];
+    float f[MB_PHASE_FLOATS];
+    int32_t slot[MB_PHASE_SLOTS]; /* indices into the address table; -1 = absent         */
+} mb_phase;
+
+/* MB_BODY_GEMV: integer fields */
+#define MB_GV_I_ROWS 0     /* activation rows (batch), 1..8                               */
+#define MB_GV_I_K 1        /* reduction length, multiple of 16                            */
+#define MB_GV_I_NSEG 2     /* weight segments, 1..3                                       */
+#define MB_GV_I_N0 3       /* output features of segment 0 (1 and 2 follow)               */
+#define MB_GV_I_NMAT 6     /* 1, or 2 for a paired gate/up phase (then NSEG == 1)         */
+#define MB_GV_I_PROLOGUE 7
+#define MB_GV_I_EPILOGUE 8
+#define MB_GV_I_ROW_TILE 9 /* weight rows per pipeline stage: 8,16,32,64,128              */
+#define MB_GV_I_K_CHUNK 10 /* reduction elements per pipeline stage, multiple of 16       */
+#define MB_GV_I_GATHER 11  /* 1: activation rows are gathered from an embedding table     */
+#define MB_GV_I_VOCAB 12   /* rows of that table (range check)                            */
+#define MB_GV_I_STORE_X 13 /* 1: CTA 0 also stores the un-normalised rows at S_XSTORE     */
+/* floats */
+#define MB_GV_F_EPS 0
+#define MB_GV_F_EMBED_SCALE 1 /* 0 = none; else gathered rows are bf16(row * scale)       */
+/* slots */
+#define MB_GV_S_X 0        /* activations [rows, K] bf16, or the embedding table [V, K]   */
+#define MB_GV_S_NORM_W 1   /* [K] bf16                                                    */
+#define MB_GV_S_W0 2       /* weights [N, K] bf16 row-major, segments 0..2                */
+#define MB_GV_S_BIAS0 5    /* [N] bf16, segments 0..2, -1 if absent                       */
+#define MB_GV_S_OUT0 8     /* [rows, N] bf16, segments 0..2                               */
+#define MB_GV_S_W_PAIR 11  /* second matrix of a paired phase                             */
+#define MB_GV_S_RESIDUAL 12
+#define MB_GV_S_IDS 13     /* int64 [rows] token ids (gather)                             */
+#define MB_GV_S_XSTORE 14
+
+/* MB_BODY_ATTN_DECODE */
+#define MB_AT_I_BATCH 0
+#define MB_AT_I_HEADS 1
+#define MB_AT_I_KV_HEADS 2
+#define MB_AT_I_HEAD_DIM 3   /* 64, 128 or 256                                            */
+#define MB_AT_I_CAPACITY 4
+#define MB_AT_I_INVFREQ_BF16 5 /* 1 if the inv_freq buffer is bf16, 0 if fp32             */
+#define MB_AT_I_MAX_CHUNKS 6 /* key chunks per (batch, kv head) the workspace is sized for */
+#define MB_AT_I_MERGE_SLOTS 7 /* per-warp states that fit the shared scratch at once      */
+#define MB_AT_F_SCALE 0      /* head_dim ** -0.5, applied in fp32                          */
+#define MB_AT_F_ROPE_SCALE 1 /* attention_scaling multiplied into cos/sin                  */
+#define MB_AT_F_Q_SCALE 2    /* 0 or 1 = none; else q = bf16(q * this) after RoPE          */
+#define MB_AT_S_Q 0          /* [B, Hq*D] bf16 before RoPE                                 */
+#define MB_AT_S_K 1          /* [B, Hkv*D]                                                 */
+#define MB_AT_S_V 2
+#define MB_AT_S_KCACHE 3     /* [B, capacity, Hkv, D] bf16                                 */
+#define MB_AT_S_VCACHE 4
+#define MB_AT_S_LEN 5        /* int32 [1]                                                  */
+#define MB_AT_S_POS 6        /* int64 [B]                                                  */
+#define MB_AT_S_INVFREQ 7    /* [D/2]                                                      */
+#define MB_AT_S_OUT 8        /* [B, Hq*D] bf16                                             */
+#define MB_AT_S_PARTIAL 9    /* fp32 [B*Hkv, max_chunks, Hq/Hkv, D+2]                      */
+#define MB_AT_S_COUNTER 10   /* int32 [B*Hkv], zero before the first launch                */
+
+/* ---- plan descriptor ---------------------------------------------------------------- */
+#define MB_MAX_DYNAMIC 8
+
+typedef struct mb_plan_desc {
+    uint32_t abi_version;     /* MB_ABI_VERSION                                           */
+    int32_t device;           /* CUDA device ordinal                                      */
+    int32_t mode;             /* enum mb_mode                                             */
+    uint32_t n_phases;
+    const mb_phase* phases;
+    uint32_t n_slots;         /* size of the address table                                */
+    uint32_t n_dynamic;       /* slots [0, n_dynamic) are given per launch, <= 8          */
+    uint32_t activation_bytes;/* shared memory for activations / attention scratch        */
+    uint32_t ctas;            /* 0 = one per SM                                           */
+    uint32_t reserved[4];
+} mb_plan_desc;
+
+typedef struct mb_plan_info {
+    int32_t ctas;             /* cooperative grid size                                    */
+    int32_t threads;          /* threads per CTA                                          */
+    int32_t smem_bytes;       /* dynamic shared memory per CTA                            */
+    int32_t stages;           /* weight-ring stages                                       */
+    int32_t barriers;         /* grid barriers per launch                                 */
+    int32_t sm_count;
+    int32_t reserved[2];
+} mb_plan_info;
+
+typedef struct mb_plan mb_plan;
+
+int mb_plan_create(const mb_plan_desc* desc, mb_plan** out);
+int mb_plan_query(const mb_plan* plan, mb_plan_info* out);
+int mb_plan_bind(mb_plan* plan, const uint64_t* slot_addresses, size_t n);
+int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, void* stream);
+int mb_plan_status(mb_plan* plan, mb_status* out);
+int mb_plan_reset(mb_plan* plan);
+void mb_plan_destroy(mb_plan* plan);
+
+const char* mb_strerror(int code);
+const char* mb_status_string(int status_code);
+const char* mb_last_cuda_error(void);
+int mb_abi_version(void);
+
+/* Shared-memory need of the fixed parts, so the host planner can size activation_bytes
+ * and predict the ring depth without a device: returns bytes, or -1 for a bad mode. */
+int mb_fixed_smem_bytes(int mode);
+int mb_stage_bytes(int mode);
+int mb_max_smem_bytes(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGABAKE_B200_H */

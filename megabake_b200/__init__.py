@@ -1,0 +1,35 @@
+"""megabake_b200: a B200-native (sm_100a) persistent-megakernel backend for decoder inference
+behind MegaBake's ``make_backend()`` / ``torch.compile`` boundary.
+
+Public surface (names follow the reference's ``src/megabake/__init__.py:61-121`` for the
+parts of it this backend keeps):
+
+``make_backend(mode=..., ...)``     the ``torch.compile`` backend factory
+``graphed(function, *args)``        CUDA-graph capture of one compiled call
+``kv_attention`` / ``attention``    the declared attention operators (``torch.ops.megabake.*``)
+``DecodeStep``, ``StatefulDecoder`` explicit-state decode wrappers for Hugging Face models
+``register_transformers_attention`` the ``"megabake"`` attention implementation for HF models
+``CompilerError``                   every refusal, with a staged diagnostic
+"""
+
+from .diagnostics import CompilerDiagnostic, CompilerError
+from .ops import attention, kv_attention
+
+__all__ = [
+    "CompilerDiagnostic", "CompilerError", "DecodeStep", "StatefulDecoder", "attention",
+    "graphed", "kv_attention", "make_backend", "register_transformers_attention",
+]
+
+
+def __getattr__(name):
+    # Heavier modules load on first use so that `import megabake_b200` stays light.
+    if name == "make_backend":
+        from .frontend import make_backend
+        return make_backend
+    if name in ("graphed", "GraphedCall", "BoundDecoder"):
+        from . import engine
+        return getattr(engine, name)
+    if name in ("DecodeStep", "StatefulDecoder", "register_transformers_attention"):
+        from . import hf
+        return getattr(hf, name)
+    raise AttributeError(name)

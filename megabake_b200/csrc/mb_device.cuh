@@ -1,0 +1,236 @@
+// Device-side primitives shared by the decode and prefill megakernels: bf16 rounding
+// helpers, mbarrier / bulk-copy / mma wrappers, bounded waits, the counting grid barrier
+// and the status word.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/megabake_b200.h"
+
+namespace mb {
+
+// ---------------------------------------------------------------------------------------
+// Control block in global memory, one per plan.
+// ---------------------------------------------------------------------------------------
+struct Control {
+    unsigned int barrier;   // counting grid barrier, grows by `ctas` per barrier
+    unsigned int calls;     // completed launches; the barrier targets derive from it
+    int status[4];          // code, phase, detail, (unused)
+    unsigned int pad[2];
+};
+
+struct KernelParams {
+    const mb_phase* phases;
+    const unsigned long long* slots;  // device address table
+    Control* ctl;
+    unsigned long long dyn[MB_MAX_DYNAMIC];
+    int n_phases;
+    int n_dynamic;
+    int barriers_per_launch;
+    int stages;            // weight-ring depth
+    int activation_bytes;  // shared bytes reserved for activations / attention scratch
+};
+
+// Wait limits.  Every wait in the kernels is bounded: when one runs out the kernel records
+// a status, raises the CTA's abort flag and drains instead of spinning forever.
+constexpr unsigned long long kBarrierTimeoutNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kPipeTimeoutNs = 2000000000ull;     // 2 s
+constexpr unsigned int kDrainTryLimit = 1000000u;                 // try_wait calls while draining
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ unsigned long long slot_address(const KernelParams& p, int s) {
+    if (s < 0) return 0ull;
+    if (s < p.n_dynamic) {
+        unsigned long long a = p.dyn[0];
+#pragma unroll
+        for (int i = 1; i < MB_MAX_DYNAMIC; ++i)
+            if (s == i) a = p.dyn[i];
+        return a;
+    }
+    return __ldg(p.slots + s);
+}
+
+__device__ __forceinline__ void record_status(Control* ctl, int code, int phase, int detail) {
+    if (atomicCAS(&ctl->status[0], 0, code) == 0) {
+        ctl->status[1] = phase;
+        ctl->status[2] = detail;
+        __threadfence();
+    }
+}
+
+__device__ __forceinline__ int peek_status(const Control* ctl) {
+    return *reinterpret_cast<const volatile int*>(&ctl->status[0]);
+}
+
+// ---------------------------------------------------------------------------------------
+// bf16 helpers.  Every rounding point of the eager forward is an explicit call here.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_round(float v) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
+    return __uint_as_float(static_cast<unsigned int>(bits) << 16);
+}
+__device__ __forceinline__ unsigned short float_to_bf16_bits(float v) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float lo_bf16(unsigned int packed) {
+    return __uint_as_float(packed << 16);
+}
+__device__ __forceinline__ float hi_bf16(unsigned int packed) {
+    return __uint_as_float(packed & 0xffff0000u);
+}
+__device__ __forceinline__ unsigned int pack_bf16(float lo, float hi) {
+    return static_cast<unsigned int>(float_to_bf16_bits(lo)) |
+           (static_cast<unsigned int>(float_to_bf16_bits(hi)) << 16);
+}
+
+// x / (1 + exp(-x)) with the operation order of the decomposed graph.
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+// 0.5 * x * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+    const float kBeta = 0.7978845608028654f;
+    const float kKappa = 0.044715f;
+    float inner = kBeta * (x + kKappa * (x * x * x));
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+// ---------------------------------------------------------------------------------------
+// Loads that bypass L1 for data another CTA produced earlier in the same launch.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+    return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ unsigned int ld_cg_u32(const void* p) {
+    return __ldcg(reinterpret_cast<const unsigned int*>(p));
+}
+__device__ __forceinline__ unsigned short ld_cg_u16(const void* p) {
+    return __ldcg(reinterpret_cast<const unsigned short*>(p));
+}
+__device__ __forceinline__ float ld_cg_f32(const void* p) {
+    return __ldcg(reinterpret_cast<const float*>(p));
+}
+
+// ---------------------------------------------------------------------------------------
+// Shared-memory addresses, named barriers, mbarriers, bulk async copies.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int smem_u32(const void* p) {
+    return static_cast<unsigned int>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar,
+                                                      unsigned int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned int parity) {
+    unsigned int done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded mbarrier wait.  `abort_flag` is a CTA-shared int that any thread raises when a
+// wait of its own ran out; everybody else then stops waiting too.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned int parity,
+                                                  volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = global_timer_ns();
+    for (unsigned int tries = 1;; ++tries) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((tries & 127u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > kPipeTimeoutNs) return false;
+        }
+    }
+}
+
+// 1-D bulk async copy global -> shared, completion counted in bytes on an mbarrier.
+// Source, destination and size must be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem,
+                                              unsigned int bytes, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned int a0, unsigned int a1,
+                                               unsigned int a2, unsigned int a3, unsigned int b0,
+                                               unsigned int b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------------------
+// Counting grid barrier.  Called by `threads` threads of every CTA (named barrier `bar_id`).
+// `target` is the counter value that means "everybody arrived".  Returns false after a
+// timeout or when another CTA already recorded a fault; the caller then drains.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int target, int bar_id,
+                                             int threads, int tid, volatile int* abort_flag,
+                                             int phase) {
+    named_barrier(bar_id, threads);
+    if (tid == 0) {
+        __threadfence();
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ctl->barrier) : "memory");
+        const unsigned long long start = global_timer_ns();
+        unsigned int polls = 0;
+        for (;;) {
+            unsigned int seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
+                         : "=r"(seen)
+                         : "l"(&ctl->barrier)
+                         : "memory");
+            if (static_cast<int>(seen - target) >= 0) break;
+            if ((++polls & 63u) == 0u) {
+                if (peek_status(ctl) != 0) {
+                    *abort_flag = 1;
+                    break;
+                }
+                if (global_timer_ns() - start > kBarrierTimeoutNs) {
+                    record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase, static_cast<int>(blockIdx.x));
+                    *abort_flag = 1;
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    named_barrier(bar_id, threads);
+    return *abort_flag == 0;
+}
+
+}  // namespace mb

@@ -1,0 +1,336 @@
+"""Execution planner: packs a ``DecoderProgram`` into barrier intervals and emits the
+phase records + address-table layout of the C ABI.
+
+Decode packing (one grid barrier closes each interval):
+
+    [embed gather (layer 0) . rmsnorm . q|k|v (+bias)]          |
+    [rope(q, new k) . kv append . split-key attention . merge]   |  (+ valid_length += 1)
+    [o_proj + residual]                                          |
+    [rmsnorm . gate|up . act(gate) * up]                         |
+    [down + residual]                                            |   x layers
+    [rmsnorm . lm head]
+
+RMSNorm, the embedding gather, RoPE, bias, residual adds and the gated activation never get
+an interval of their own: they are folded into the consumer's prologue (recomputed by every
+CTA, the rows are tiny) or the producer's epilogue.  That is the 5-intervals-per-layer
+shape the reference's schedule reaches with interval folding
+(``src/megabake/schedule.py:1220-1245,1298-1409``; ``docs/roadmap.md:56-59``), with the gate/up
+pair fused (the reference's sm100 provider cannot, ``bodies/cuda/sm100/table.py:28-30``) and
+the embedding + RoPE-table intervals removed.
+
+The planner runs without a GPU (it only asks the native library for its shared-memory
+constants), so the tables are unit-testable on CPU.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass, field
+
+from . import runtime as rt
+from .diagnostics import fail
+from .program import DecoderProgram
+
+DYN_INPUT_IDS, DYN_POSITION_IDS, DYN_LOGITS = 0, 1, 2
+N_DYNAMIC = 3
+CONSUMER_WARPS = 8
+MAX_GEMV_ROWS = 8
+
+
+@dataclass(frozen=True)
+class SlotSpec:
+    kind: str  # "dynamic" | "arg" | "workspace"
+    index: int = 0  # argument position, or dynamic ordinal
+    offset: int = 0  # byte offset into the workspace
+    name: str = ""
+
+
+@dataclass
+class PlanLayout:
+    program: DecoderProgram
+    phases: list[rt.Phase]
+    slots: list[SlotSpec]
+    workspace_bytes: int
+    zero_ranges: list[tuple[int, int]]  # workspace byte ranges that must start zeroed
+    activation_bytes: int
+    intervals: int
+    notes: list[str] = field(default_factory=list)
+    mode: int = rt.MODE_DECODE
+
+
+@dataclass(frozen=True)
+class PlannerOptions:
+    ctas: int = 148  # CTAs the tile split is planned for (one per SM on B200)
+    row_tile: int | None = None  # force the GEMV row tile (tuning sweeps)
+    max_chunks: int = 64
+    merge_slots: int | None = None
+
+    @classmethod
+    def from_env(cls, **overrides) -> "PlannerOptions":
+        values = {}
+        if os.environ.get("MEGABAKE_B200_ROW_TILE"):
+            values["row_tile"] = int(os.environ["MEGABAKE_B200_ROW_TILE"])
+        values.update(overrides)
+        return cls(**values)
+
+
+def _align(value: int, to: int) -> int:
+    return (value + to - 1) // to * to
+
+
+class _Slots:
+    def __init__(self):
+        self.specs: list[SlotSpec] = [
+            SlotSpec("dynamic", DYN_INPUT_IDS, name="input_ids"),
+            SlotSpec("dynamic", DYN_POSITION_IDS, name="position_ids"),
+            SlotSpec("dynamic", DYN_LOGITS, name="logits"),
+        ]
+        self._args: dict[int, int] = {}
+        self.workspace = 0
+        self.zero: list[tuple[int, int]] = []
+
+    def arg(self, position: int | None, name: str = "") -> int:
+        if position is None:
+            return -1
+        if position not in self._args:
+            self._args[position] = len(self.specs)
+            self.specs.append(SlotSpec("arg", position, name=name))
+        return self._args[position]
+
+    def buffer(self, nbytes: int, name: str, zero: bool = False) -> int:
+        offset = _align(self.workspace, 256)
+        self.workspace = offset + nbytes
+        if zero:
+            self.zero.append((offset, nbytes))
+        self.specs.append(SlotSpec("workspace", offset=offset, name=name))
+        return len(self.specs) - 1
+
+
+def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, row_pad: int,
+                  forced_row_tile: int | None = None) -> tuple[int, int]:
+    """(row_tile, k_chunk) of a skinny-GEMM phase.
+
+    A CTA owns ``ceil(n_total / ctas)`` consecutive weight rows and streams them in stages of
+    ``row_tile`` rows x ``k_chunk`` reduction elements (x ``nmat`` matrices) that must fit one
+    ring slot; the consumer warps not needed for rows split K.  Among row tiles 8/16/32/64 the
+    one needing the fewest stages wins (long contiguous row copies, few pipeline hand-offs);
+    ties go to the larger tile, which needs less cross-warp reduction.
+    """
+    rows_per_cta = max(1, math.ceil(n_total / ctas))
+
+    def max_chunk(tile: int) -> int:
+        return min(k, ((stage_bytes // (tile * nmat)) - row_pad) // 2 // 16 * 16)
+
+    def stages(tile: int) -> int:
+        return math.ceil(rows_per_cta / tile) * math.ceil(k / max_chunk(tile))
+
+    candidates = [tile for tile in (8, 16, 32, 64) if max_chunk(tile) >= 16]
+    if forced_row_tile is not None:
+        candidates = [forced_row_tile] if forced_row_tile in candidates else []
+    if not candidates:
+        fail("resource-admission", f"no GEMV row tile fits K={k} x {nmat} matrices in a stage")
+    row_tile = min(candidates, key=lambda tile: (stages(tile), -tile))
+    limit = max_chunk(row_tile)
+    chunks = math.ceil(k / limit)
+    k_chunk = min(_align(math.ceil(k / chunks), 16), limit)
+    return row_tile, k_chunk
+
+
+def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int) -> int:
+    return 16 * (head_dim + 32) + 4 * head_dim + 4 * (head_dim + 2) * group * (merge_slots + 2)
+
+
+def _check_program(p: DecoderProgram) -> None:
+    if p.mode != "decode":
+        fail("planning", f"plan_decode got a {p.mode!r} program")
+    if p.tokens != 1:
+        fail("planning", "decode plans take one token per row")
+    if not 1 <= p.batch <= MAX_GEMV_ROWS:
+        fail("resource-admission", f"decode batch {p.batch} outside 1..{MAX_GEMV_ROWS}",
+             requirement="batch <= 8 rows per GPU")
+    if p.head_dim not in (64, 128, 256):
+        fail("resource-admission", f"head_dim {p.head_dim} not in (64, 128, 256)")
+    if p.heads % p.kv_heads or p.group > 8:
+        fail("resource-admission",
+             f"{p.heads} query heads over {p.kv_heads} kv heads (group size must divide, <= 8)")
+    for name, value in (("hidden", p.hidden), ("intermediate", p.intermediate)):
+        if value % 16:
+            fail("resource-admission", f"{name} size {value} is not a multiple of 16")
+    if p.norm not in ("llama", "gemma"):
+        fail("planning", f"unknown norm kind {p.norm!r}")
+    if p.activation not in ("silu", "gelu_tanh"):
+        fail("planning", f"unknown activation {p.activation!r}")
+
+
+def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) -> PlanLayout:
+    options = options or PlannerOptions.from_env()
+    _check_program(program)
+    lib = rt.load_library()
+    stage_bytes = lib.mb_stage_bytes(rt.MODE_DECODE)
+    fixed_bytes = lib.mb_fixed_smem_bytes(rt.MODE_DECODE)
+    max_smem = lib.mb_max_smem_bytes()
+    row_pad = 16
+    p = program
+    B, H, D = p.batch, p.hidden, p.head_dim
+    q_dim, kv_dim = p.heads * D, p.kv_heads * D
+    slots = _Slots()
+    pro = rt.PRO_RMS_LLAMA if p.norm == "llama" else rt.PRO_RMS_GEMMA
+    act = rt.EPI_SILU_MUL if p.activation == "silu" else rt.EPI_GELU_TANH_MUL
+
+    hidden = slots.buffer(B * H * 2, "hidden")
+    q_buf = slots.buffer(B * q_dim * 2, "q")
+    k_buf = slots.buffer(B * kv_dim * 2, "k")
+    v_buf = slots.buffer(B * kv_dim * 2, "v")
+    attn = slots.buffer(B * q_dim * 2, "attention")
+    glu = slots.buffer(B * p.intermediate * 2, "gated")
+    max_chunks = max(1, min(options.max_chunks, math.ceil(p.capacity / 16)))
+    pairs = B * p.kv_heads
+    partial = slots.buffer(pairs * max_chunks * p.group * (D + 2) * 4, "attention_partials")
+    counters = slots.buffer(_align(pairs * 4, 16), "attention_arrivals", zero=True)
+
+    merge_slots = options.merge_slots or CONSUMER_WARPS
+    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots) > 48 * 1024:
+        merge_slots //= 2
+    activation = attention_scratch_bytes(D, p.group, merge_slots)
+
+    phases: list[rt.Phase] = []
+
+    def gemv(*, k, segments, x_slot, prologue=rt.PRO_NONE, norm_slot=-1, epilogue=rt.EPI_NONE,
+             pair_slot=-1, residual_slot=-1, barrier=True, gather=False, store_x=-1):
+        nonlocal activation
+        n_total = sum(n for n, _, _, _ in segments)
+        nmat = 2 if pair_slot >= 0 else 1
+        row_tile, k_chunk = gemv_geometry(n_total, k, nmat, options.ctas, stage_bytes, row_pad,
+                                          options.row_tile)
+        phase = rt.Phase.blank(rt.BODY_GEMV, rt.FLAG_BARRIER if barrier else 0)
+        phase.i[rt.GV_I_ROWS] = B
+        phase.i[rt.GV_I_K] = k
+        phase.i[rt.GV_I_NSEG] = len(segments)
+        phase.i[rt.GV_I_NMAT] = nmat
+        phase.i[rt.GV_I_PROLOGUE] = prologue
+        phase.i[rt.GV_I_EPILOGUE] = epilogue
+        phase.i[rt.GV_I_ROW_TILE] = row_tile
+        phase.i[rt.GV_I_K_CHUNK] = k_chunk
+        phase.f[rt.GV_F_EPS] = p.eps
+        phase.slot[rt.GV_S_X] = x_slot
+        phase.slot[rt.GV_S_NORM_W] = norm_slot
+        for index, (n, weight, bias, out) in enumerate(segments):
+            phase.i[rt.GV_I_N0 + index] = n
+            phase.slot[rt.GV_S_W0 + index] = weight
+            phase.slot[rt.GV_S_BIAS0 + index] = bias
+            phase.slot[rt.GV_S_OUT0 + index] = out
+        phase.slot[rt.GV_S_W_PAIR] = pair_slot
+        phase.slot[rt.GV_S_RESIDUAL] = residual_slot
+        if gather:
+            phase.i[rt.GV_I_GATHER] = 1
+            phase.i[rt.GV_I_VOCAB] = p.vocab
+            phase.f[rt.GV_F_EMBED_SCALE] = float(p.embed_scale or 0.0)
+            phase.slot[rt.GV_S_IDS] = DYN_INPUT_IDS
+            if store_x >= 0:
+                phase.i[rt.GV_I_STORE_X] = 1
+                phase.slot[rt.GV_S_XSTORE] = store_x
+        activation = max(activation, B * (k + 8) * 2)
+        phases.append(phase)
+
+    inv_freq = slots.arg(p.inv_freq, "inv_freq")
+    embed = slots.arg(p.embed_weight, "embed_tokens.weight")
+    for index, layer in enumerate(p.layers):
+        tag = f"layers.{index}."
+        first = index == 0
+        gemv(
+            k=H,
+            segments=[
+                (q_dim, slots.arg(layer.q_weight, tag + "q_proj.weight"),
+                 slots.arg(layer.q_bias, tag + "q_proj.bias"), q_buf),
+                (kv_dim, slots.arg(layer.k_weight, tag + "k_proj.weight"),
+                 slots.arg(layer.k_bias, tag + "k_proj.bias"), k_buf),
+                (kv_dim, slots.arg(layer.v_weight, tag + "v_proj.weight"),
+                 slots.arg(layer.v_bias, tag + "v_proj.bias"), v_buf),
+            ],
+            x_slot=embed if first else hidden,
+            prologue=pro,
+            norm_slot=slots.arg(layer.input_norm, tag + "input_layernorm.weight"),
+            gather=first,
+            store_x=hidden if first else -1,
+        )
+        attention = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BARRIER | rt.FLAG_BUMP_LENGTH)
+        attention.i[rt.AT_I_BATCH] = B
+        attention.i[rt.AT_I_HEADS] = p.heads
+        attention.i[rt.AT_I_KV_HEADS] = p.kv_heads
+        attention.i[rt.AT_I_HEAD_DIM] = D
+        attention.i[rt.AT_I_CAPACITY] = p.capacity
+        attention.i[rt.AT_I_INVFREQ_BF16] = 1 if p.inv_freq_dtype == "bf16" else 0
+        attention.i[rt.AT_I_MAX_CHUNKS] = max_chunks
+        attention.i[rt.AT_I_MERGE_SLOTS] = merge_slots
+        attention.f[rt.AT_F_SCALE] = p.softmax_scale
+        attention.f[rt.AT_F_ROPE_SCALE] = p.rope_scale
+        attention.f[rt.AT_F_Q_SCALE] = float(p.q_scale or 0.0)
+        attention.slot[rt.AT_S_Q] = q_buf
+        attention.slot[rt.AT_S_K] = k_buf
+        attention.slot[rt.AT_S_V] = v_buf
+        attention.slot[rt.AT_S_KCACHE] = slots.arg(layer.key_cache, tag + "key_cache")
+        attention.slot[rt.AT_S_VCACHE] = slots.arg(layer.value_cache, tag + "value_cache")
+        attention.slot[rt.AT_S_LEN] = slots.arg(layer.valid_length, tag + "valid_length")
+        attention.slot[rt.AT_S_POS] = DYN_POSITION_IDS
+        attention.slot[rt.AT_S_INVFREQ] = inv_freq
+        attention.slot[rt.AT_S_OUT] = attn
+        attention.slot[rt.AT_S_PARTIAL] = partial
+        attention.slot[rt.AT_S_COUNTER] = counters
+        phases.append(attention)
+        gemv(
+            k=q_dim,
+            segments=[(H, slots.arg(layer.o_weight, tag + "o_proj.weight"),
+                       slots.arg(layer.o_bias, tag + "o_proj.bias"), hidden)],
+            x_slot=attn,
+            epilogue=rt.EPI_RESIDUAL,
+            residual_slot=hidden,
+        )
+        if layer.gate_bias is not None or layer.up_bias is not None:
+            fail("pattern-recognition", "biased gate/up projections are not covered")
+        gemv(
+            k=H,
+            segments=[(p.intermediate, slots.arg(layer.gate_weight, tag + "gate_proj.weight"),
+                       -1, glu)],
+            x_slot=hidden,
+            prologue=pro,
+            norm_slot=slots.arg(layer.post_norm, tag + "post_attention_layernorm.weight"),
+            epilogue=act,
+            pair_slot=slots.arg(layer.up_weight, tag + "up_proj.weight"),
+        )
+        gemv(
+            k=p.intermediate,
+            segments=[(H, slots.arg(layer.down_weight, tag + "down_proj.weight"),
+                       slots.arg(layer.down_bias, tag + "down_proj.bias"), hidden)],
+            x_slot=glu,
+            epilogue=rt.EPI_RESIDUAL,
+            residual_slot=hidden,
+        )
+    gemv(
+        k=H,
+        segments=[(p.vocab, slots.arg(p.lm_head_weight, "lm_head.weight"),
+                   slots.arg(p.lm_head_bias, "lm_head.bias"), DYN_LOGITS)],
+        x_slot=hidden,
+        prologue=pro,
+        norm_slot=slots.arg(p.final_norm, "norm.weight"),
+        barrier=False,
+    )
+
+    activation = _align(activation, 128)
+    if fixed_bytes + activation + 2 * stage_bytes > max_smem:
+        fail("resource-admission",
+             f"activations need {activation} B of shared memory; with {fixed_bytes} B fixed and two "
+             f"{stage_bytes} B weight stages that exceeds {max_smem} B",
+             requirement="batch * max(hidden, intermediate) * 2 B must leave room for the ring")
+    intervals = sum(1 for phase in phases if phase.flags & rt.FLAG_BARRIER) + 1
+    return PlanLayout(
+        program=p,
+        phases=phases,
+        slots=slots.specs,
+        workspace_bytes=_align(slots.workspace, 256),
+        zero_ranges=slots.zero,
+        activation_bytes=activation,
+        intervals=intervals,
+        notes=[f"{len(phases)} phases in {intervals} barrier intervals",
+               f"attention: max_chunks={max_chunks} merge_slots={merge_slots}"],
+    )

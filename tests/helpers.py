@@ -1,0 +1,50 @@
+"""Shared test helpers: single-phase plans through the C ABI, tolerance checks."""
+
+from __future__ import annotations
+
+import torch
+
+from megabake_b200 import runtime as rt
+
+# Tolerances of the parity contract: logits max-abs <= 3e-2 and cosine >= 0.9999 against the
+# CPU forward; greedy ids exact.
+LOGIT_MAX_ABS = 3e-2
+LOGIT_COSINE = 0.9999
+
+
+def cosine(a: torch.Tensor, b: torch.Tensor) -> float:
+    a = a.detach().double().flatten().cpu()
+    b = b.detach().double().flatten().cpu()
+    return float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-30))
+
+
+def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.detach().double().cpu() - b.detach().double().cpu()).abs().max())
+
+
+class PhaseRunner:
+    """Builds an address table from named tensors and runs hand-made phase records."""
+
+    def __init__(self, device="cuda"):
+        self.device = torch.device(device)
+        self.tensors: list[torch.Tensor] = []
+        self.names: dict[str, int] = {}
+
+    def slot(self, name: str, tensor: torch.Tensor | None) -> int:
+        if tensor is None:
+            return -1
+        if name in self.names:
+            return self.names[name]
+        assert tensor.is_cuda and tensor.is_contiguous() and tensor.data_ptr() % 16 == 0, name
+        self.names[name] = len(self.tensors)
+        self.tensors.append(tensor)
+        return self.names[name]
+
+    def run(self, phases, activation_bytes: int, ctas: int = 0) -> rt.Plan:
+        plan = rt.Plan(list(phases), n_slots=len(self.tensors), n_dynamic=0,
+                       activation_bytes=(activation_bytes + 127) // 128 * 128,
+                       device=self.device.index or 0, ctas=ctas)
+        plan.bind([t.data_ptr() for t in self.tensors])
+        plan.launch([], torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        return plan

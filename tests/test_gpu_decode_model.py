@@ -1,0 +1,155 @@
+"""Whole-model decode parity: the CUDA megakernel (through the C ABI) against the CPU oracle on
+the same seeded weights, token ids and KV state.
+
+Bar (from the parity contract): greedy argmax ids identical at every call; logits max-abs
+<= 3e-2 and cosine >= 0.9999; appended KV rows within bf16 tolerance, untouched cache rows
+byte-equal, valid lengths exact.
+"""
+
+import pytest
+import torch
+
+from megabake_b200 import models
+from megabake_b200.engine import BoundDecoder
+from megabake_b200.planner import PlannerOptions, plan_decode
+from oracle import decoder_oracle as oracle
+from oracle.adapters import oracle_config, oracle_weights
+from tests.helpers import LOGIT_COSINE, LOGIT_MAX_ABS, cosine, max_abs
+
+pytestmark = pytest.mark.gpu
+
+
+class Harness:
+    def __init__(self, name, batch, capacity, seed=0, row_tile=None):
+        self.spec = models.get_spec(name)
+        self.batch, self.capacity = batch, capacity
+        self.weights = models.init_weights(self.spec, seed)
+        self.inv_freq = models.inv_freq_buffer(self.spec)
+        self.cfg = oracle_config(self.spec)
+        self.ow = oracle_weights(self.weights, self.inv_freq)
+        self.dev_weights = {k: v.cuda() for k, v in self.weights.items()}
+        self.dev_inv = self.inv_freq.cuda()
+        self.state = models.make_state(self.spec, batch, capacity, "cuda")
+        program = models.direct_program(self.spec, batch, capacity)
+        self.layout = plan_decode(program, PlannerOptions(row_tile=row_tile))
+        self.ids = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+        self.pos = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+        self.args = models.direct_arguments(self.spec, self.dev_weights, self.dev_inv, self.ids,
+                                            self.pos, self.state)
+        self.decoder = BoundDecoder(self.layout, self.args)
+
+    def step(self, ids, pos, _state=None):
+        self.ids.copy_(ids)
+        self.pos.copy_(pos)
+        logits = self.decoder(*self.args)
+        self.decoder.check()
+        return logits.cpu()
+
+    def load_state(self, cpu_state):
+        for mine, theirs in zip(self.state, cpu_state):
+            mine.copy_(theirs)
+
+
+def _compare_state(h: Harness, ref_state, used):
+    for index in range(h.spec.layers):
+        kc, vc, ln = (t.cpu() for t in h.state[3 * index: 3 * index + 3])
+        rk, rv, rl = ref_state[3 * index: 3 * index + 3]
+        assert int(ln) == int(rl) == used
+        assert max_abs(kc[:, :used], rk[:, :used]) <= 6e-2
+        assert max_abs(vc[:, :used], rv[:, :used]) <= 6e-2
+        assert cosine(kc[:, :used], rk[:, :used]) > 0.9999
+        assert torch.equal(kc[:, used:], rk[:, used:])  # untouched rows byte-equal
+        assert torch.equal(vc[:, used:], rv[:, used:])
+
+
+@pytest.mark.parametrize("name,batch", [
+    ("tiny-llama", 1), ("tiny-llama", 3), ("tiny-llama3", 2), ("tiny-qwen2", 4), ("tiny-mha", 8),
+    ("tiny-gemma", 2), ("tiny-gemma256", 1),
+])
+def test_tiny_models_match_oracle(name, batch):
+    prompt_len, steps, capacity = 6, 6, 16
+    h = Harness(name, batch, capacity, seed=3)
+    prompt = torch.randint(0, h.spec.vocab, (batch, prompt_len),
+                           generator=torch.Generator().manual_seed(7))
+    ref_ids, ref_logits, ref_state = oracle.greedy_decode(h.cfg, h.ow, prompt, steps, capacity)
+    # teacher-forced comparison: feed the oracle's tokens so one flipped argmax cannot hide the
+    # numerics of later calls, and check the argmax of every call
+    tokens = torch.cat([prompt, ref_ids[:, prompt_len - 1:-1]], dim=1)
+    for call in range(prompt_len + steps):
+        pos = torch.full((batch, 1), call, dtype=torch.int64)
+        logits = h.step(tokens[:, call:call + 1].contiguous(), pos)
+        ref = ref_logits[call]
+        assert max_abs(logits, ref) <= LOGIT_MAX_ABS, (call, max_abs(logits, ref))
+        assert cosine(logits, ref) >= LOGIT_COSINE, (call, cosine(logits, ref))
+        assert torch.equal(logits[:, -1].float().argmax(-1), ref_ids[:, call]), call
+    _compare_state(h, ref_state, prompt_len + steps)
+
+
+@pytest.mark.parametrize("row_tile", [8, 16, 32, 64])
+def test_row_tile_variants_agree(row_tile):
+    """Every GEMV tiling must give the same answer within accumulation-order noise."""
+    h = Harness("tiny-qwen2", 2, 8, seed=1, row_tile=row_tile)
+    ids = torch.tensor([[5], [900]])
+    pos = torch.zeros(2, 1, dtype=torch.int64)
+    state = oracle.make_state(h.cfg, 2, 8)
+    ref = oracle.decode_step(h.cfg, h.ow, ids, pos, state)
+    logits = h.step(ids, pos)
+    assert max_abs(logits, ref) <= LOGIT_MAX_ABS
+    assert cosine(logits, ref) >= LOGIT_COSINE
+
+
+def test_smollm_135m_protocol():
+    """BASELINE config 1: SmolLM-135M shape, batch 1, 32-token prompt + 32 greedy steps;
+    the greedy ids must be bit-exact, free-running (each implementation feeds its own picks)."""
+    h = Harness("smollm-135m", 1, 96, seed=0)
+    prompt = torch.randint(0, h.spec.vocab, (1, 32), generator=torch.Generator().manual_seed(1))
+    ref_ids, ref_logits, ref_state = oracle.greedy_decode(h.cfg, h.ow, prompt, 32, 96)
+    got_ids, got_logits, _ = oracle.greedy_decode(h.cfg, h.ow, prompt, 32, 96, step_fn=h.step)
+    assert torch.equal(got_ids, ref_ids)
+    worst = max(max_abs(a, b) for a, b in zip(got_logits, ref_logits))
+    worst_cos = min(cosine(a, b) for a, b in zip(got_logits, ref_logits))
+    assert worst <= LOGIT_MAX_ABS, worst
+    assert worst_cos >= LOGIT_COSINE, worst_cos
+    _compare_state(h, ref_state, 64)
+
+
+def test_long_context_prefilled_cache():
+    """Decode on top of a long cache (the 4096-key shape of config 2, shortened model):
+    the cache is filled by a seeded oracle prefill; the next steps must match the oracle."""
+    spec = models.get_spec("tiny-qwen2")
+    batch, cached, capacity = 2, 1500, 1500 + 4
+    h = Harness("tiny-qwen2", batch, capacity, seed=5)
+    ids = torch.randint(0, spec.vocab, (batch, cached), generator=torch.Generator().manual_seed(2))
+    _, kv = oracle.prefill(h.cfg, h.ow, ids, return_kv=True)
+    ref_state = oracle.make_state(h.cfg, batch, capacity)
+    for index, (k, v) in enumerate(kv):
+        ref_state[3 * index][:, :cached] = k
+        ref_state[3 * index + 1][:, :cached] = v
+        ref_state[3 * index + 2].fill_(cached)
+    h.load_state(ref_state)
+    token = torch.randint(0, spec.vocab, (batch, 1), generator=torch.Generator().manual_seed(3))
+    for step in range(3):
+        pos = torch.full((batch, 1), cached + step, dtype=torch.int64)
+        ref = oracle.decode_step(h.cfg, h.ow, token, pos, ref_state)
+        logits = h.step(token, pos)
+        assert max_abs(logits, ref) <= LOGIT_MAX_ABS, (step, max_abs(logits, ref))
+        assert cosine(logits, ref) >= LOGIT_COSINE
+        assert torch.equal(logits[:, -1].float().argmax(-1), ref[:, -1].float().argmax(-1))
+        token = ref[:, -1].float().argmax(-1, keepdim=True)
+    _compare_state(h, ref_state, cached + 3)
+
+
+def test_kv_overflow_raises_and_recovers():
+    from megabake_b200 import CompilerError
+
+    h = Harness("tiny-llama", 1, 2, seed=0)
+    ids = torch.tensor([[3]])
+    for call in range(2):
+        h.step(ids, torch.tensor([[call]]))
+    with pytest.raises(CompilerError) as info:
+        h.step(ids, torch.tensor([[2]]))
+    assert info.value.diagnostic.stage == "state-capacity"
+    # after recovery and a state reset the plan works again
+    for tensor in h.state[2::3]:
+        tensor.zero_()
+    h.step(ids, torch.tensor([[0]]))
