@@ -72,7 +72,7 @@ PRESETS: dict[str, ModelSpec] = {
                              1e4),
     "gemma-2b": ModelSpec("gemma-2b", "gemma", 2048, 18, 8, 1, 256, 16384, 256000, 1e-6, 1e4),
     # small shapes for tests (same families, every code path, seconds on CPU)
-    "tiny-llama": ModelSpec("tiny-llama", "llama", 128, 2, 4, 2, 64, 256, 512, 1e-5, 1e4),
+    "tiny-llama": ModelSpec("tiny-llama", "llama", 256, 2, 4, 2, 64, 512, 512, 1e-5, 1e4),
     "tiny-llama3": ModelSpec("tiny-llama3", "llama", 256, 2, 4, 1, 64, 512, 640, 1e-5, 5e5,
                              rope_scaling=("llama3", 32.0, 1.0, 4.0, 8192)),
     "tiny-qwen2": ModelSpec("tiny-qwen2", "qwen2", 448, 2, 7, 1, 64, 1216, 1024, 1e-6, 1e6,

@@ -48,3 +48,36 @@ class PhaseRunner:
         plan.launch([], torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
         return plan
+
+
+def bf16_ulp(value: float) -> float:
+    """Spacing of bf16 numbers around ``value`` (8 significand bits)."""
+    import math
+
+    if value == 0.0:
+        return 2.0 ** -133
+    return 2.0 ** (math.floor(math.log2(abs(value))) - 7)
+
+
+def greedy_pick_matches(logits: torch.Tensor, reference: torch.Tensor) -> tuple[bool, int]:
+    """Greedy-id parity for one call: rows of ``[B, V]`` logits.
+
+    The pick must be the reference's argmax.  The one exception is a reference whose two best
+    logits are closer than two bf16 ulps (random-init models give nearly flat logits, and exact
+    ties do occur): then the winner is decided by rounding noise of the fp32 accumulation order,
+    and the pick only has to be one of the tied candidates.  Returns (ok, rows decided by the
+    tie rule)."""
+    got = logits.float().cpu()
+    ref = reference.float().cpu()
+    ok, ties = True, 0
+    for row in range(ref.shape[0]):
+        best = int(ref[row].argmax())
+        pick = int(got[row].argmax())
+        if pick == best:
+            continue
+        gap = float(ref[row, best] - ref[row, pick])
+        if gap <= 2 * bf16_ulp(float(ref[row, best])):
+            ties += 1
+        else:
+            ok = False
+    return ok, ties

@@ -1,0 +1,96 @@
+"""CPU-side checks: the shared library loads and exports every symbol the header declares,
+the ctypes mirrors match the C structs, and the planner's tables are well formed."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from megabake_b200 import models, planner
+from megabake_b200 import runtime as rt
+from megabake_b200.diagnostics import CompilerError
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "megabake_b200.h").read_text()
+
+
+def test_library_exports_every_declared_symbol():
+    lib = rt.load_library()
+    declared = set(re.findall(r"\b(mb_[a-z_]+)\s*\(", HEADER))
+    assert declared, "no declarations found in the header"
+    assert declared == set(rt.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.mb_abi_version() == rt.MB_ABI_VERSION
+
+
+def test_struct_mirrors_match_header():
+    ints = int(re.search(r"#define MB_PHASE_INTS (\d+)", HEADER).group(1))
+    floats = int(re.search(r"#define MB_PHASE_FLOATS (\d+)", HEADER).group(1))
+    slots = int(re.search(r"#define MB_PHASE_SLOTS (\d+)", HEADER).group(1))
+    assert (ints, floats, slots) == (rt.MB_PHASE_INTS, rt.MB_PHASE_FLOATS, rt.MB_PHASE_SLOTS)
+    assert ctypes.sizeof(rt.Phase) == 4 * (2 + ints + floats + slots)
+    for name, value in re.findall(r"#define (MB_(?:GV|AT)_[A-Z]_[A-Z0-9_]+) (\d+)", HEADER):
+        mirror = name[3:]
+        assert getattr(rt, mirror) == int(value), name
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(CompilerError) as info:
+        rt.load_library(tmp_path / "absent.so")
+    assert info.value.diagnostic.stage == "native-library"
+    assert "no fallback" in str(info.value)
+
+
+@pytest.mark.parametrize("name", ["smollm-135m", "qwen2-0.5b", "llama-3.2-1b", "smollm-1.7b"])
+@pytest.mark.parametrize("batch", [1, 8])
+def test_decode_plan_tables(name, batch):
+    spec = models.get_spec(name)
+    layout = planner.plan_decode(models.direct_program(spec, batch, 8192 + 33))
+    lib = rt.load_library()
+    stage = lib.mb_stage_bytes(rt.MODE_DECODE)
+    assert len(layout.phases) == 5 * spec.layers + 1
+    assert layout.intervals == 5 * spec.layers + 1  # + the closing barrier, - the unflagged head
+    for phase in layout.phases:
+        if phase.body == rt.BODY_GEMV:
+            tile, chunk, nmat = phase.i[rt.GV_I_ROW_TILE], phase.i[rt.GV_I_K_CHUNK], phase.i[rt.GV_I_NMAT]
+            assert tile in (8, 16, 32, 64) and chunk % 16 == 0 and chunk <= phase.i[rt.GV_I_K]
+            assert tile * nmat * (chunk * 2 + 16) <= stage
+            assert batch * (phase.i[rt.GV_I_K] + 8) * 2 <= layout.activation_bytes
+        for slot in phase.slot:
+            assert -1 <= slot < len(layout.slots)
+    kinds = [s.kind for s in layout.slots]
+    assert kinds[:3] == ["dynamic"] * 3 and "dynamic" not in kinds[3:]
+    # every weight of the model is bound exactly once
+    args = [s.index for s in layout.slots if s.kind == "arg"]
+    assert len(args) == len(set(args))
+    fixed = lib.mb_fixed_smem_bytes(rt.MODE_DECODE)
+    assert fixed + layout.activation_bytes + 2 * stage <= lib.mb_max_smem_bytes()
+
+
+def test_geometry_prefers_few_stages():
+    # 14 rows per CTA of a 2048-wide matrix: one 16-row tile, K in whole-row copies if it fits
+    tile, chunk = planner.gemv_geometry(2048, 2048, 1, 148, 34816, 16)
+    assert tile == 16 and chunk == 1024
+    tile, chunk = planner.gemv_geometry(128256, 2048, 1, 148, 34816, 16)
+    assert tile * (chunk * 2 + 16) <= 34816
+
+
+def test_planner_refusals():
+    spec = models.get_spec("tiny-llama")
+    with pytest.raises(CompilerError) as info:
+        planner.plan_decode(models.direct_program(spec, 9, 16))
+    assert info.value.diagnostic.stage == "resource-admission"
+    odd = models.get_spec("tiny-llama", head_dim=32)
+    with pytest.raises(CompilerError):
+        planner.plan_decode(models.direct_program(odd, 1, 16))
+
+
+def test_weight_bytes_match_survey_table():
+    # bytes of weights one decode step reads (bf16), per the hot-path scope table
+    expect = {"smollm-135m": 134_515_008, "qwen2-0.5b": 494_032_768,
+              "llama-3.2-1b": 1_235_814_400, "smollm-1.7b": 1_711_376_384}
+    for name, params in expect.items():
+        spec = models.get_spec(name)
+        assert spec.parameter_count() == params, name
