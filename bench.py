@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the decoder hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One step = one decode call (one cooperative megakernel launch) on one batch of synthetic
+input: a seeded random-init model of the named shape whose KV cache already holds the stated
+number of keys (filled by a seeded prefill of uniform-random token ids).  Prints ONE JSON line.
+
+* ``value``      decode microseconds per generated token with inputs resident in HBM:
+                 max-over-ranks device time of K back-to-back launches / (K * batch * N)
+* ``e2e``        the same metric through the public call (``BoundDecoder.__call__``, what
+                 ``make_backend`` returns) with HOST buffers: per step a pinned host->device copy
+                 of token and position ids, the launch, a device argmax of the logits and a
+                 device->host read of the picked ids, synchronised every step
+* ``roofline``   HBM roofline of the megakernel: algorithmic bytes per launch (weights once +
+                 the valid KV rows) / mean launch time, against the measured copy bandwidth
+* ``cpu_baseline`` / ``--impl reference``  the CPU port of the reference forward (``oracle/``),
+                 timed on this box's host cores on the same workload
+
+Multi-GPU: one process per GPU under torchrun, independent replicas (seed + rank), no collective
+on the data path; the only collective is the max-reduction of the timing scalar.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+# workload name -> (model preset, batch, cached keys)
+WORKLOADS = {
+    "qwen2-0.5b-b8-k4096": ("qwen2-0.5b", 8, 4096),
+    "qwen2-0.5b-b4-k4096": ("qwen2-0.5b", 4, 4096),
+    "qwen2-0.5b-b1-k4096": ("qwen2-0.5b", 1, 4096),
+    "smollm-135m-b1-k32": ("smollm-135m", 1, 32),
+    "llama-3.2-1b-b1-k512": ("llama-3.2-1b", 1, 512),
+    "llama-3.2-1b-b1-k8192": ("llama-3.2-1b", 1, 8192),
+    "smollm-1.7b-b1-k8192": ("smollm-1.7b", 1, 8192),
+    "smollm-1.7b-b8-k8192": ("smollm-1.7b", 8, 8192),
+}
+DEFAULT_WORKLOAD = "qwen2-0.5b-b8-k4096"
+METRIC = "decode_us_per_token"
+UNIT = "us/token"
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def ncu_traffic(workload: str):
+    """DRAM bytes per launch from the committed ncu summary, if one covers this workload."""
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()).get(workload)
+        except Exception:
+            return None
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.samples.append([c.strip() for c in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        clocks = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        reasons = set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for sample in self.samples:
+            for name, flag in zip(names, sample[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": float(self.samples[0][1]) if self.samples else None,
+            "reasons": sorted(reasons),
+            "samples": len(self.samples),
+        }
+
+
+def build_workload(name: str, rank: int, extra_steps: int, device, cache_fill: str = "prefill"):
+    import torch
+
+    from megabake_b200 import models
+
+    preset, batch, keys = WORKLOADS[name]
+    spec = models.get_spec(preset)
+    capacity = keys + extra_steps + 1
+    weights = models.init_weights(spec, seed=rank, device=device, on_device=True)
+    inv_freq = models.inv_freq_buffer(spec, device)
+    state = models.make_state(spec, batch, capacity, device)
+    if keys > 0 and cache_fill == "prefill":
+        models.fill_cache_by_prefill(spec, weights, inv_freq, state, keys, seed=100 + rank)
+    elif keys > 0:
+        # profiling runs: seeded random rows instead of thousands of library launches
+        gen = torch.Generator(device=device).manual_seed(100 + rank)
+        for index in range(spec.layers):
+            for t in state[3 * index: 3 * index + 2]:
+                t[:, :keys].normal_(0.0, 1.0, generator=gen)
+            state[3 * index + 2].fill_(keys)
+    return spec, batch, keys, capacity, weights, inv_freq, state
+
+
+def algorithmic_bytes(spec, program, batch: int, mean_keys: float) -> float:
+    return program.weight_bytes() + batch * mean_keys * program.kv_bytes_per_key()
+
+
+def cpu_reference_run(name: str, steps: int, warmup: int, budget_s: float, rank: int = 0) -> dict:
+    """Time the CPU port of the reference forward on this box's host cores."""
+    import torch
+
+    from megabake_b200 import models
+    from oracle import decoder_oracle as oracle
+    from oracle.adapters import oracle_config, oracle_weights
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    preset, batch, keys = WORKLOADS[name]
+    spec = models.get_spec(preset)
+    capacity = keys + steps + warmup + 1
+    weights = models.init_weights(spec, seed=rank)
+    inv_freq = models.inv_freq_buffer(spec)
+    state = models.make_state(spec, batch, capacity)
+    if keys > 0:
+        # same protocol as the GPU arm; on CPU the fill is the slow part, so use seeded random
+        # K/V rows of the prefill's magnitude when the context is long (timing is unaffected)
+        if keys <= 512:
+            models.fill_cache_by_prefill(spec, weights, inv_freq, state, keys, seed=100 + rank)
+        else:
+            gen = torch.Generator().manual_seed(100 + rank)
+            for index in range(spec.layers):
+                for t in state[3 * index: 3 * index + 2]:
+                    t[:, :keys] = torch.randn(t[:, :keys].shape, generator=gen).to(t.dtype)
+                state[3 * index + 2].fill_(keys)
+    cfg, ow = oracle_config(spec), oracle_weights(weights, inv_freq)
+    ids = torch.randint(0, spec.vocab, (batch, 1), generator=torch.Generator().manual_seed(7))
+    times = []
+    started = time.perf_counter()
+    with torch.no_grad():
+        for call in range(warmup + steps):
+            pos = torch.full((batch, 1), keys + call, dtype=torch.int64)
+            t0 = time.perf_counter()
+            oracle.decode_step(cfg, ow, ids, pos, state)
+            dt = time.perf_counter() - t0
+            if call >= warmup:
+                times.append(dt)
+            if time.perf_counter() - started > budget_s and len(times) >= 2:
+                break
+    per_step = statistics.median(times)
+    return {
+        "value": per_step * 1e6 / batch, "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"{len(times)} decode steps of {name} (median), CPU port of the reference "
+                  f"eager forward, {cores} threads",
+        "ms_per_step": per_step * 1e3, "steps": len(times),
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    result = cpu_reference_run(args.workload, args.steps, min(args.warmup, 2), budget_s=120.0)
+    preset, batch, keys = WORKLOADS[args.workload]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": result["steps"], "warmup": min(args.warmup, 2),
+        "ms_per_step": result["ms_per_step"], "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "model": preset, "batch": batch,
+                   "cached_keys": keys, "device": "host cpu"},
+        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": result["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch
+
+    from megabake_b200 import models
+    from megabake_b200.engine import BoundDecoder
+    from megabake_b200.planner import plan_decode
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU execution path "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    total_calls = 2 * (steps + warmup) + 8
+    spec, batch, keys, capacity, weights, inv_freq, state = build_workload(
+        args.workload, rank, total_calls, device, args.cache_fill)
+    program = models.direct_program(spec, batch, capacity)
+    layout = plan_decode(program)
+    ids = torch.randint(0, spec.vocab, (batch, 1), generator=torch.Generator().manual_seed(7 + rank))
+    ids_dev = ids.to(device)
+    pos_all = (torch.arange(total_calls, dtype=torch.int64)[:, None, None] + keys).expand(
+        total_calls, batch, 1).contiguous().to(device)
+    call_args = models.direct_arguments(spec, weights, inv_freq, ids_dev, pos_all[0], state)
+    decoder = BoundDecoder(layout, call_args)
+    logits = torch.empty(batch, 1, spec.vocab, dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- resident-input timing -----------------------------------------------------------
+    call = 0
+    for _ in range(warmup):
+        decoder.launch_into(ids_dev, pos_all[call], logits)
+        call += 1
+    decoder.check()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_key = keys + call
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        start.record()
+        for _ in range(steps):
+            decoder.launch_into(ids_dev, pos_all[call], logits)
+            call += 1
+        stop.record()
+        barrier()
+    decoder.check()
+    device_ms = start.elapsed_time(stop)
+    mean_keys = first_key + (steps - 1) / 2 + 1
+
+    # ---- end-to-end timing: host buffers in, picked ids out, synchronised per step ---------
+    host_ids = ids.clone().pin_memory()
+    host_pos = torch.zeros(batch, 1, dtype=torch.int64).pin_memory()
+    host_pick = torch.zeros(batch, dtype=torch.int64).pin_memory()
+    dev_ids = torch.empty_like(ids_dev)
+    dev_pos = torch.empty(batch, 1, dtype=torch.int64, device=device)
+    e2e_args = list(call_args)
+    e2e_args[program.input_ids], e2e_args[program.position_ids] = dev_ids, dev_pos
+
+    def e2e_step(index: int):
+        host_pos.fill_(keys + index)
+        dev_ids.copy_(host_ids, non_blocking=True)
+        dev_pos.copy_(host_pos, non_blocking=True)
+        out = decoder(*e2e_args)
+        host_pick.copy_(out[:, -1].argmax(-1), non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        e2e_step(call)
+        call += 1
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step(call)
+        call += 1
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    decoder.check()
+
+    times = torch.tensor([device_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_ms, e2e_ms = (float(x) for x in times.cpu())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        ms_per_step = device_ms / steps
+        bytes_per_launch = algorithmic_bytes(spec, program, batch, mean_keys)
+        achieved = bytes_per_launch / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": ms_per_step * 1e3 / (batch * world), "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {
+                "workload": args.workload, "model": spec.name, "batch_per_gpu": batch,
+                "cached_keys": keys, "replicas": world, "parallelism": f"dp{world} replicas",
+                "weights": "seeded N(0,0.02) random init, tied embeddings",
+                "cache_fill": args.cache_fill,
+                "l2": "inputs larger than L2: weights + KV read per step "
+                      f"{bytes_per_launch / 1e6:.0f} MB vs 126 MB L2",
+                "tokens_per_s": batch * world / (ms_per_step * 1e-3),
+                "phases": len(layout.phases), "barrier_intervals": layout.intervals,
+                "ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages,
+            },
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": ncu_traffic(args.workload),
+                "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": bytes_per_launch,
+            },
+            "e2e": {
+                "value": e2e_ms * 1e3 / steps / (batch * world), "unit": UNIT,
+                "h2d_bytes_per_step": 2 * batch * 8, "d2h_bytes_per_step": batch * 8,
+                "ms_per_step": e2e_ms / steps,
+                "path": "BoundDecoder.__call__ + torch argmax, synchronised every step",
+            },
+            "gpu_launches": steps,
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base = cpu_reference_run(args.workload, 8, 1, budget_s=25.0)
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--cache-fill", default="prefill", choices=["prefill", "random"],
+                        help="how the KV cache gets its cached keys (random: for profiler runs)")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

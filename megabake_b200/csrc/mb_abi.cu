@@ -46,7 +46,6 @@ struct DeviceGuard {
     }
 };
 
-bool is_row_tile(int v) { return v == 8 || v == 16 || v == 32 || v == 64; }
 
 }  // namespace
 
@@ -64,19 +63,21 @@ struct mb_plan {
     int smem_bytes = 0;
     int stages = 0;
     int barriers = 0;
-    mb_phase* d_phases = nullptr;
-    unsigned long long* d_slots = nullptr;
+    mb::PhaseEntry* d_entries = nullptr;
     mb::Control* d_ctl = nullptr;
+    unsigned long long trace = 0;
 };
 
 namespace {
 
 // Shared-memory scratch the decode attention body carves from the activation region.
-long long attention_scratch_bytes(int head_dim, int group, int merge_slots) {
+long long attention_scratch_bytes(int head_dim, int group, int merge_slots, int exact_keys) {
     const long long qs = 8LL * (head_dim + 32) * 2;
     const long long cs = 4LL * head_dim;
+    const long long stats = 4LL * (2 * 8 * 8 + 8 * 64 + 16);
     const long long states = 4LL * (head_dim + 2) * group * (merge_slots + 2);
-    return qs + cs + states;
+    const long long scores = 4LL * group * exact_keys;
+    return qs + cs + stats + states + scores;
 }
 
 int check_slot(const mb_plan_desc* d, int s, bool required) {
@@ -89,16 +90,16 @@ int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     const int nmat = P.i[MB_GV_I_NMAT], rt = P.i[MB_GV_I_ROW_TILE], kc = P.i[MB_GV_I_K_CHUNK];
     const int epi = P.i[MB_GV_I_EPILOGUE], pro = P.i[MB_GV_I_PROLOGUE];
     if (rows < 1 || rows > 8) return MB_ERR_UNSUPPORTED;
-    if (K < 16 || K % 16 != 0) return MB_ERR_UNSUPPORTED;
+    if (K < 32 || K % 32 != 0) return MB_ERR_UNSUPPORTED;
     if (nseg < 1 || nseg > 3) return MB_ERR_INVALID;
     if (nmat != 1 && nmat != 2) return MB_ERR_INVALID;
     if (nmat == 2 && nseg != 1) return MB_ERR_INVALID;
-    if (!is_row_tile(rt)) return MB_ERR_INVALID;
-    if (kc < 16 || kc % 16 != 0 || kc > K) return MB_ERR_INVALID;
+    if (rt != mb::decode_row_tile()) return MB_ERR_INVALID;
+    if (kc < 32 || kc % 32 != 0 || kc > K) return MB_ERR_INVALID;
     if (static_cast<long long>(rt) * nmat * (kc * 2 + mb::decode_row_pad()) >
         mb::decode_stage_bytes())
         return MB_ERR_RESOURCE;
-    if (static_cast<long long>(rows) * (K + 8) * 2 > d->activation_bytes) return MB_ERR_RESOURCE;
+    if (static_cast<long long>(rows) * (K + 32) * 2 > d->activation_bytes) return MB_ERR_RESOURCE;
     if (pro < MB_PRO_NONE || pro > MB_PRO_RMS_GEMMA) return MB_ERR_INVALID;
     if (epi < MB_EPI_NONE || epi > MB_EPI_GELU_TANH_MUL) return MB_ERR_INVALID;
     const bool paired_epi = epi == MB_EPI_SILU_MUL || epi == MB_EPI_GELU_TANH_MUL;
@@ -132,7 +133,10 @@ int validate_attention(const mb_plan_desc* d, const mb_phase& P) {
     if (D != 64 && D != 128 && D != 256) return MB_ERR_UNSUPPORTED;
     if (chunks < 1 || chunks > 64) return MB_ERR_INVALID;
     if (slots < 1 || slots > 8) return MB_ERR_INVALID;
-    if (attention_scratch_bytes(D, Hq / Hkv, slots) > d->activation_bytes) return MB_ERR_RESOURCE;
+    const int exact = P.i[MB_AT_I_EXACT_KEYS];
+    if (exact < 0 || exact % 16 != 0) return MB_ERR_INVALID;
+    if (attention_scratch_bytes(D, Hq / Hkv, slots, exact) > d->activation_bytes)
+        return MB_ERR_RESOURCE;
     for (int s = MB_AT_S_Q; s <= MB_AT_S_COUNTER; ++s)
         if (check_slot(d, P.slot[s], true)) return MB_ERR_INVALID;
     if ((P.flags & MB_FLAG_BUMP_LENGTH) && !(P.flags & MB_FLAG_BARRIER)) return MB_ERR_INVALID;
@@ -249,13 +253,8 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     plan->stages = stages;
     plan->barriers = barriers;
 
-    cudaError_t err = cudaMalloc(&plan->d_phases, sizeof(mb_phase) * desc->n_phases);
-    if (err == cudaSuccess)
-        err = cudaMalloc(&plan->d_slots, sizeof(unsigned long long) * (desc->n_slots + 1));
+    cudaError_t err = cudaMalloc(&plan->d_entries, sizeof(mb::PhaseEntry) * desc->n_phases);
     if (err == cudaSuccess) err = cudaMalloc(&plan->d_ctl, sizeof(mb::Control));
-    if (err == cudaSuccess)
-        err = cudaMemcpy(plan->d_phases, desc->phases, sizeof(mb_phase) * desc->n_phases,
-                         cudaMemcpyHostToDevice);
     if (err == cudaSuccess) err = cudaMemset(plan->d_ctl, 0, sizeof(mb::Control));
     if (err != cudaSuccess) {
         cuda_fail(err, "plan table allocation");
@@ -285,9 +284,24 @@ int mb_plan_bind(mb_plan* plan, const uint64_t* slot_addresses, size_t n) {
         if (slot_addresses[i] == 0 || (slot_addresses[i] & 15ull) != 0) return MB_ERR_INVALID;
         plan->slots[i] = slot_addresses[i];
     }
+    // Resolve every slot a phase names into its entry, so the kernel reads one record per
+    // phase and never a second table.
+    std::vector<mb::PhaseEntry> entries(plan->phases.size());
+    for (size_t ph = 0; ph < plan->phases.size(); ++ph) {
+        entries[ph].rec = plan->phases[ph];
+        for (int j = 0; j < MB_PHASE_SLOTS; ++j) {
+            const int slot = plan->phases[ph].slot[j];
+            if (slot < 0)
+                entries[ph].addr[j] = 0ull;
+            else if (static_cast<unsigned int>(slot) < plan->n_dynamic)
+                entries[ph].addr[j] = mb::kDynamicTag | static_cast<unsigned long long>(slot);
+            else
+                entries[ph].addr[j] = plan->slots[slot];
+        }
+    }
     DeviceGuard guard(plan->device);
     if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
-    MB_CUDA(cudaMemcpy(plan->d_slots, plan->slots.data(), sizeof(unsigned long long) * n,
+    MB_CUDA(cudaMemcpy(plan->d_entries, entries.data(), sizeof(mb::PhaseEntry) * entries.size(),
                        cudaMemcpyHostToDevice));
     plan->bound = true;
     return MB_OK;
@@ -299,11 +313,11 @@ int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, v
     if (n != plan->n_dynamic || (n > 0 && dynamic_addresses == nullptr)) return MB_ERR_INVALID;
     mb::KernelParams params;
     std::memset(&params, 0, sizeof(params));
-    params.phases = plan->d_phases;
-    params.slots = plan->d_slots;
+    params.entries = plan->d_entries;
     params.ctl = plan->d_ctl;
+    params.trace = reinterpret_cast<unsigned long long*>(plan->trace);
     for (size_t i = 0; i < n; ++i) {
-        if (dynamic_addresses[i] == 0 || (dynamic_addresses[i] & 15ull) != 0) return MB_ERR_INVALID;
+        if (dynamic_addresses[i] == 0 || (dynamic_addresses[i] & 7ull) != 0) return MB_ERR_INVALID;
         params.dyn[i] = dynamic_addresses[i];
     }
     params.n_phases = static_cast<int>(plan->phases.size());
@@ -331,6 +345,16 @@ int mb_plan_status(mb_plan* plan, mb_status* out) {
     return MB_OK;
 }
 
+int mb_plan_set_trace(mb_plan* plan, uint64_t device_address, size_t bytes) {
+    if (plan == nullptr) return MB_ERR_INVALID;
+    if (device_address != 0) {
+        const size_t need = static_cast<size_t>(plan->ctas) * plan->phases.size() * 4 * sizeof(uint64_t);
+        if (bytes < need || (device_address & 7ull) != 0) return MB_ERR_INVALID;
+    }
+    plan->trace = device_address;
+    return MB_OK;
+}
+
 int mb_plan_reset(mb_plan* plan) {
     if (plan == nullptr) return MB_ERR_INVALID;
     DeviceGuard guard(plan->device);
@@ -344,8 +368,7 @@ void mb_plan_destroy(mb_plan* plan) {
     if (plan == nullptr) return;
     {
         DeviceGuard guard(plan->device);
-        if (plan->d_phases) cudaFree(plan->d_phases);
-        if (plan->d_slots) cudaFree(plan->d_slots);
+        if (plan->d_entries) cudaFree(plan->d_entries);
         if (plan->d_ctl) cudaFree(plan->d_ctl);
     }
     delete plan;

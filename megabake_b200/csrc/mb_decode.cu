@@ -25,75 +25,119 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxStages = 8;
-constexpr int kStageBytes = 34816;  // 32 KiB of weights + room for per-row padding
-constexpr int kRowPad = 16;         // bytes added to each staged row (bank spreading)
-constexpr int kReduceBytes = 8192;  // two parities of cross-warp partial sums
-constexpr int kCtlBytes = 1024;
+constexpr int kRowTile = 8;          // weight rows per stage = one n8 MMA tile
+constexpr int kRowPad = 64;          // bytes added to each staged row: with row lengths that are
+                                     // multiples of 128 B this makes 16-byte fragment loads of
+                                     // two neighbouring rows hit disjoint banks
+constexpr int kStageBytes = 30720;   // 8 rows x 2 matrices x (896 * 2 + 64) B and change
+constexpr int kCtlBytes = 2048;
+constexpr int kReduceBytes = 16384;  // partial sums of one reduction group of row blocks
 constexpr int kFixedBytes = kCtlBytes + kReduceBytes;
-constexpr int kBarConsumers = 1;    // named barrier ids
-constexpr int kBarReduce = 2;
+constexpr int kBarConsumers = 1;     // named barrier id of the consumer warps
+constexpr int kFoldFloats = 8 * 64 + 16;  // attention: chunk weights + denominators
+constexpr int kEntryVectors = sizeof(PhaseEntry) / 16;
 
 struct SharedCtl {
     unsigned long long full[kMaxStages];
     unsigned long long empty[kMaxStages];
     volatile int abort_flag;
     volatile unsigned int issued;    // stages the producer armed
-    volatile unsigned int consumed;  // stages the consumers released
     int bcast[4];                    // small broadcasts (attention chunking, arrival order)
+    volatile int verdict;            // thread 0's go / drain decision at a barrier
     float red[kConsumerWarps][8];    // per-warp partials of the activation prologue
+    __align__(16) PhaseEntry entry[2];  // current / next phase record with resolved addresses
 };
 static_assert(sizeof(SharedCtl) <= kCtlBytes, "control block too large");
+static_assert(sizeof(PhaseEntry) % 16 == 0, "phase entries are copied in 16-byte vectors");
+
+__device__ __forceinline__ unsigned long long entry_address(const KernelParams& p,
+                                                            const PhaseEntry* e, int j) {
+    const unsigned long long v = e->addr[j];
+    if (v >> 63) {  // dynamic slot: the address comes with the launch
+        const int s = static_cast<int>(v & 0xffu);
+        unsigned long long a = p.dyn[0];
+#pragma unroll
+        for (int i = 1; i < MB_MAX_DYNAMIC; ++i)
+            if (s == i) a = p.dyn[i];
+        return a;
+    }
+    return v;
+}
 
 // Geometry of one GEMV phase for one CTA; producer and consumers derive it identically.
+// A CTA owns weight rows [r0, r1) of the phase's (virtually concatenated) output rows and
+// streams them as row blocks of 8, each cut into n_chunks stages of k_chunk elements.
 struct GemvGeom {
     int rows, K, nseg, nmat, n[3], ntotal;
-    int row_tile, k_chunk, n_chunks, pitch;
-    int r0, r1;
+    int k_chunk, n_chunks, pitch;
+    int r0, r1, n_blocks;
 };
 
-__device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase* P, int cta, int ctas) {
+__device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, int ctas) {
     GemvGeom g;
-    g.rows = P->i[MB_GV_I_ROWS];
-    g.K = P->i[MB_GV_I_K];
-    g.nseg = P->i[MB_GV_I_NSEG];
-    g.nmat = P->i[MB_GV_I_NMAT];
-    g.n[0] = P->i[MB_GV_I_N0];
-    g.n[1] = g.nseg > 1 ? P->i[MB_GV_I_N0 + 1] : 0;
-    g.n[2] = g.nseg > 2 ? P->i[MB_GV_I_N0 + 2] : 0;
+    g.rows = P.i[MB_GV_I_ROWS];
+    g.K = P.i[MB_GV_I_K];
+    g.nseg = P.i[MB_GV_I_NSEG];
+    g.nmat = P.i[MB_GV_I_NMAT];
+    g.n[0] = P.i[MB_GV_I_N0];
+    g.n[1] = g.nseg > 1 ? P.i[MB_GV_I_N0 + 1] : 0;
+    g.n[2] = g.nseg > 2 ? P.i[MB_GV_I_N0 + 2] : 0;
     g.ntotal = g.n[0] + g.n[1] + g.n[2];
-    g.row_tile = P->i[MB_GV_I_ROW_TILE];
-    g.k_chunk = P->i[MB_GV_I_K_CHUNK];
+    g.k_chunk = P.i[MB_GV_I_K_CHUNK];
     g.n_chunks = (g.K + g.k_chunk - 1) / g.k_chunk;
     g.pitch = g.k_chunk * 2 + kRowPad;
     g.r0 = static_cast<int>((static_cast<long long>(cta) * g.ntotal) / ctas);
     g.r1 = static_cast<int>((static_cast<long long>(cta + 1) * g.ntotal) / ctas);
+    g.n_blocks = (g.r1 - g.r0 + kRowTile - 1) / kRowTile;
     return g;
 }
 
 // ---------------------------------------------------------------------------------------
-// Producer warp.
+// Producer warp: for every GEMV phase, in phase order, stream this CTA's weight rows into
+// the ring -- stage order is (row block, k chunk), the order the consumers expect.
 // ---------------------------------------------------------------------------------------
-__device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc, char* ring, int lane) {
+__device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc, char* ring,
+                                           int lane) {
     const int cta = blockIdx.x, ctas = gridDim.x;
     unsigned int it = 0;
     for (int ph = 0; ph < p.n_phases; ++ph) {
-        const mb_phase* P = p.phases + ph;
-        if (P->body != MB_BODY_GEMV) continue;
-        const GemvGeom g = gemv_geometry(P, cta, ctas);
-        const char* wbase[3];
-        wbase[0] = reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_W0]));
-        wbase[1] = g.nseg > 1
-                       ? reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_W0 + 1]))
-                       : nullptr;
-        wbase[2] = g.nseg > 2
-                       ? reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_W0 + 2]))
-                       : nullptr;
-        const char* wpair =
-            g.nmat > 1 ? reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_W_PAIR]))
-                       : nullptr;
+        const PhaseEntry* E = p.entries + ph;
+        if (E->rec.body != MB_BODY_GEMV) continue;
+        const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
+        const char* w0 = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_W0));
+        const char* w1 = g.nseg > 1
+                             ? reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_W0 + 1))
+                             : nullptr;
+        const char* w2 = g.nseg > 2
+                             ? reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_W0 + 2))
+                             : nullptr;
+        const char* wpair = g.nmat > 1 ? reinterpret_cast<const char*>(
+                                             entry_address(p, E, MB_GV_S_W_PAIR))
+                                       : nullptr;
         const size_t row_bytes = static_cast<size_t>(g.K) * 2;
-        for (int block0 = g.r0; block0 < g.r1; block0 += g.row_tile) {
-            const int nrows = min(g.row_tile, g.r1 - block0);
+        for (int blk = 0; blk < g.n_blocks; ++blk) {
+            const int block0 = g.r0 + blk * kRowTile;
+            const int nrows = min(kRowTile, g.r1 - block0);
+            // this lane's copy: matrix m, row r of the block (at most 16 copies per stage)
+            const int m = lane / nrows, r = lane - m * nrows;
+            const bool mine = lane < nrows * g.nmat;
+            const char* src_row = nullptr;
+            if (mine) {
+                int local = block0 + r;
+                const char* base;
+                if (m == 1) {
+                    base = wpair;
+                } else if (local < g.n[0]) {
+                    base = w0;
+                } else if (local < g.n[0] + g.n[1]) {
+                    base = w1;
+                    local -= g.n[0];
+                } else {
+                    base = w2;
+                    local -= g.n[0] + g.n[1];
+                }
+                src_row = base + static_cast<size_t>(local) * row_bytes;
+            }
             for (int c = 0; c < g.n_chunks; ++c) {
                 const int stage = it % p.stages;
                 const unsigned int parity = ((it / p.stages) & 1u) ^ 1u;
@@ -106,33 +150,16 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                 }
                 const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
                 const unsigned int seg_bytes = static_cast<unsigned int>(kc) * 2u;
-                char* dst_stage = ring + static_cast<size_t>(stage) * kStageBytes;
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&sc->full[stage], seg_bytes * nrows * g.nmat);
                     sc->issued = it + 1;
                 }
                 __syncwarp();
-                const int copies = nrows * g.nmat;
-                for (int idx = lane; idx < copies; idx += 32) {
-                    const int m = idx / nrows;
-                    const int r = idx - m * nrows;
-                    int local = block0 + r;
-                    const char* base;
-                    if (m == 1) {
-                        base = wpair;
-                    } else if (local < g.n[0]) {
-                        base = wbase[0];
-                    } else if (local < g.n[0] + g.n[1]) {
-                        base = wbase[1];
-                        local -= g.n[0];
-                    } else {
-                        base = wbase[2];
-                        local -= g.n[0] + g.n[1];
-                    }
-                    const char* src = base + static_cast<size_t>(local) * row_bytes +
-                                      static_cast<size_t>(c) * g.k_chunk * 2;
-                    char* dst = dst_stage + static_cast<size_t>(m * g.row_tile + r) * g.pitch;
-                    bulk_copy_g2s(dst, src, seg_bytes, &sc->full[stage]);
+                if (mine) {
+                    char* dst = ring + static_cast<size_t>(stage) * kStageBytes +
+                                static_cast<size_t>(m * kRowTile + r) * g.pitch;
+                    bulk_copy_g2s(dst, src_row + static_cast<size_t>(c) * g.k_chunk * 2, seg_bytes,
+                                  &sc->full[stage]);
                 }
                 ++it;
             }
@@ -143,141 +170,245 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
 // ---------------------------------------------------------------------------------------
 // Activation prologue: bring the phase's activation rows into shared memory as bf16,
 // applying the embedding gather and/or RMSNorm.  All consumer threads.
-// xs layout: [rows][K + 8] bf16.
+// xs layout: [rows][K + 32] bf16 (the 64-byte pad spreads rows over banks).
 // ---------------------------------------------------------------------------------------
-__device__ __noinline__ bool activation_prologue(const KernelParams& p, const mb_phase* P, int ph,
-                                    SharedCtl* sc, __nv_bfloat16* xs, int tid) {
-    const int rows = P->i[MB_GV_I_ROWS];
-    const int K = P->i[MB_GV_I_K];
-    const int xpitch = K + 8;
-    const int pro = P->i[MB_GV_I_PROLOGUE];
-    const bool gather = P->i[MB_GV_I_GATHER] != 0;
-    const float embed_scale = P->f[MB_GV_F_EMBED_SCALE];
-    const char* xbase = reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_X]));
+__device__ __forceinline__ const char* activation_row(const PhaseEntry* E, const char* xbase,
+                                                      const long long* ids, int r, int K,
+                                                      bool* bad_token) {
+    if (ids != nullptr) {
+        long long id = ids[r];
+        if (id < 0 || id >= E->rec.i[MB_GV_I_VOCAB]) {
+            *bad_token = true;
+            id = 0;
+        }
+        return xbase + static_cast<size_t>(id) * K * 2;
+    }
+    return xbase + static_cast<size_t>(r) * K * 2;
+}
+
+__device__ __forceinline__ uint4 scale_vector(uint4 raw, float scale) {
+    raw.x = pack_bf16(lo_bf16(raw.x) * scale, hi_bf16(raw.x) * scale);
+    raw.y = pack_bf16(lo_bf16(raw.y) * scale, hi_bf16(raw.y) * scale);
+    raw.z = pack_bf16(lo_bf16(raw.z) * scale, hi_bf16(raw.z) * scale);
+    raw.w = pack_bf16(lo_bf16(raw.w) * scale, hi_bf16(raw.w) * scale);
+    return raw;
+}
+
+__device__ __forceinline__ float sum_squares(uint4 v) {
+    float s = 0.f;
+    const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float a = lo_bf16(w[q]), b = hi_bf16(w[q]);
+        s += a * a;
+        s += b * b;
+    }
+    return s;
+}
+
+__device__ __forceinline__ uint4 normalise_vector(uint4 x, uint4 w, float inv, int kind) {
+    unsigned int xv[4] = {x.x, x.y, x.z, x.w};
+    const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float a = lo_bf16(xv[q]), b = hi_bf16(xv[q]);
+        const float wa = lo_bf16(wv[q]), wb = hi_bf16(wv[q]);
+        if (kind == MB_PRO_RMS_LLAMA) {
+            a = bf16_round(a * inv) * wa;
+            b = bf16_round(b * inv) * wb;
+        } else {
+            a = (a * inv) * (1.0f + wa);
+            b = (b * inv) * (1.0f + wb);
+        }
+        xv[q] = pack_bf16(a, b);
+    }
+    return make_uint4(xv[0], xv[1], xv[2], xv[3]);
+}
+
+// NV = 16-byte vectors of a row each thread keeps in registers between the two passes of the
+// norm (K <= NV * 2048); NV == 0 re-reads shared memory instead (any K).
+template <int NV>
+__device__ __forceinline__ void activation_prologue(const KernelParams& p, const PhaseEntry* E,
+                                                 int ph, SharedCtl* sc, __nv_bfloat16* xs,
+                                                 int tid) {
+    const mb_phase& P = E->rec;
+    const int rows = P.i[MB_GV_I_ROWS];
+    const int K = P.i[MB_GV_I_K];
+    const int xpitch = K + 32;
+    const int pro = P.i[MB_GV_I_PROLOGUE];
+    const bool gather = P.i[MB_GV_I_GATHER] != 0;
+    const float embed_scale = P.f[MB_GV_F_EMBED_SCALE];
+    const bool scaled = gather && embed_scale != 0.f;
+    const char* xbase = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X));
     const long long* ids =
-        gather ? reinterpret_cast<const long long*>(slot_address(p, P->slot[MB_GV_S_IDS]))
-               : nullptr;
+        gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
     const int warp = tid >> 5, lane = tid & 31;
     const int vec_per_row = K / 8;  // 16-byte vectors
+    bool bad_token = false;
+    constexpr int NVR = NV > 0 ? NV : 1;
 
-    // Pass 1: copy raw rows (gathered / scaled) into xs and accumulate sums of squares.
+    // norm weights first: their latency overlaps the activation loads
+    uint4 wreg[NVR];
+    if (NV > 0 && pro != MB_PRO_NONE) {
+        const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int v = tid + j * kConsumerThreads;
+            wreg[j] = v < vec_per_row ? __ldg(reinterpret_cast<const uint4*>(nw) + v)
+                                      : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+
     float ss[8];
 #pragma unroll
     for (int r = 0; r < 8; ++r) ss[r] = 0.f;
-    bool bad_token = false;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        if (r >= rows) break;
-        const char* src;
-        if (gather) {
-            long long id = ids[r];
-            if (id < 0 || id >= P->i[MB_GV_I_VOCAB]) {
-                bad_token = true;
-                id = 0;
-            }
-            src = xbase + static_cast<size_t>(id) * K * 2;
-        } else {
-            src = xbase + static_cast<size_t>(r) * K * 2;
-        }
-        for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-            uint4 raw = ld_cg_u4(src + static_cast<size_t>(v) * 16);
-            unsigned int w[4] = {raw.x, raw.y, raw.z, raw.w};
-            if (gather && embed_scale != 0.f) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    w[q] = pack_bf16(lo_bf16(w[q]) * embed_scale, hi_bf16(w[q]) * embed_scale);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float a = lo_bf16(w[q]), b = hi_bf16(w[q]);
-                ss[r] += a * a;
-                ss[r] += b * b;
-            }
-            *reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8) =
-                make_uint4(w[0], w[1], w[2], w[3]);
-        }
-    }
-    if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
 
-    if (gather && P->i[MB_GV_I_STORE_X] && blockIdx.x == 0) {
-        // The residual stream needs the un-normalised rows in global memory.
-        named_barrier(kBarConsumers, kConsumerThreads);
-        char* store = reinterpret_cast<char*>(slot_address(p, P->slot[MB_GV_S_XSTORE]));
-        for (int r = 0; r < rows; ++r)
-            for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-                *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) =
-                    *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
-    }
-
-    if (pro == MB_PRO_NONE) {
-        named_barrier(kBarConsumers, kConsumerThreads);
-        return true;
-    }
-
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        float v = ss[r];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) sc->red[warp][r] = v;
-    }
-    named_barrier(kBarConsumers, kConsumerThreads);
-    float inv[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        float total = 0.f;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) total += sc->red[w][r];
-        const float mean = total / static_cast<float>(K);
-        inv[r] = 1.0f / sqrtf(mean + P->f[MB_GV_F_EPS]);
-    }
-    const char* nw = reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_NORM_W]));
-    // Pass 2: each thread rescales the vectors it wrote itself (same indices as pass 1).
-    for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-        uint4 wraw = __ldg(reinterpret_cast<const uint4*>(nw + static_cast<size_t>(v) * 16));
-        const unsigned int wv[4] = {wraw.x, wraw.y, wraw.z, wraw.w};
+    if (NV > 0) {
+        // ---- register path: one global round trip, two CTA barriers
+        uint4 xreg[8][NVR];
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             if (r >= rows) break;
-            uint4* cell = reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
-            uint4 raw = *cell;
-            unsigned int xv[4] = {raw.x, raw.y, raw.z, raw.w};
+            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float a = lo_bf16(xv[q]), b = hi_bf16(xv[q]);
-                float wa = lo_bf16(wv[q]), wb = hi_bf16(wv[q]);
-                if (pro == MB_PRO_RMS_LLAMA) {
-                    a = bf16_round(a * inv[r]) * wa;
-                    b = bf16_round(b * inv[r]) * wb;
-                } else {
-                    a = (a * inv[r]) * (1.0f + wa);
-                    b = (b * inv[r]) * (1.0f + wb);
-                }
-                xv[q] = pack_bf16(a, b);
+            for (int j = 0; j < NV; ++j) {
+                const int v = tid + j * kConsumerThreads;
+                xreg[r][j] = v < vec_per_row ? ld_cg_u4(src + static_cast<size_t>(v) * 16)
+                                             : make_uint4(0u, 0u, 0u, 0u);
             }
-            *cell = make_uint4(xv[0], xv[1], xv[2], xv[3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= rows) break;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                if (scaled) xreg[r][j] = scale_vector(xreg[r][j], embed_scale);
+                ss[r] += sum_squares(xreg[r][j]);
+            }
+        }
+        if (gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0) {
+            // the residual stream needs the un-normalised rows in global memory
+            char* store = reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE));
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r >= rows) break;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const int v = tid + j * kConsumerThreads;
+                    if (v < vec_per_row)
+                        *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) =
+                            xreg[r][j];
+                }
+            }
+        }
+        float inv[8];
+        if (pro != MB_PRO_NONE) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float v = ss[r];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) sc->red[warp][r] = v;
+            }
+            named_barrier(kBarConsumers, kConsumerThreads);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float total = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) total += sc->red[w][r];
+                inv[r] = 1.0f / sqrtf(total / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= rows) break;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int v = tid + j * kConsumerThreads;
+                if (v < vec_per_row) {
+                    const uint4 value = pro != MB_PRO_NONE
+                                            ? normalise_vector(xreg[r][j], wreg[j], inv[r], pro)
+                                            : xreg[r][j];
+                    *reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8) = value;
+                }
+            }
+        }
+    } else {
+        // ---- shared-memory path for long rows
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= rows) break;
+            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
+            for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+                uint4 raw = ld_cg_u4(src + static_cast<size_t>(v) * 16);
+                if (scaled) raw = scale_vector(raw, embed_scale);
+                ss[r] += sum_squares(raw);
+                *reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8) = raw;
+            }
+        }
+        if (gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0) {
+            char* store = reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE));
+            for (int r = 0; r < rows; ++r)
+                for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) =
+                        *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
+        }
+        if (pro != MB_PRO_NONE) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float v = ss[r];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) sc->red[warp][r] = v;
+            }
+            named_barrier(kBarConsumers, kConsumerThreads);
+            float inv[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float total = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) total += sc->red[w][r];
+                inv[r] = 1.0f / sqrtf(total / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
+            }
+            const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+            // each thread rescales the vectors it wrote itself
+            for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(nw) + v);
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    if (r >= rows) break;
+                    uint4* cell =
+                        reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
+                    *cell = normalise_vector(*cell, w, inv[r], pro);
+                }
+            }
         }
     }
+    if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
     named_barrier(kBarConsumers, kConsumerThreads);
-    return true;
 }
 
 // ---------------------------------------------------------------------------------------
 // Consumer side of a GEMV phase.
 // ---------------------------------------------------------------------------------------
 struct EpilogueCtx {
-    const mb_phase* P;
     char* out[3];
     const char* bias[3];
     const char* residual;
     int n[3];
-    int rows;
     int epilogue;
 };
 
-__device__ __forceinline__ void store_output(const EpilogueCtx& e, int token, int vrow, float acc,
-                                             float acc_pair) {
-    // Segment lookup without dynamically indexed arrays (those would live in local memory).
+// Where one output element lives: segment lookup without dynamically indexed arrays (those
+// would be placed in local memory).
+struct OutputCell {
+    unsigned short* out;
+    const unsigned short* bias;
+    size_t index;
+    int local;
+};
+
+__device__ __forceinline__ OutputCell locate_output(const EpilogueCtx& e, int token, int vrow) {
     int local = vrow, n = e.n[0];
     char* out = e.out[0];
     const char* bias = e.bias[0];
@@ -293,18 +424,40 @@ __device__ __forceinline__ void store_output(const EpilogueCtx& e, int token, in
             bias = e.bias[2];
         }
     }
-    if (bias != nullptr)
-        acc += bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(bias) + local));
-    const float y = bf16_round(acc);
-    const size_t index = static_cast<size_t>(token) * n + local;
+    OutputCell cell;
+    cell.out = reinterpret_cast<unsigned short*>(out);
+    cell.bias = reinterpret_cast<const unsigned short*>(bias);
+    cell.local = local;
+    cell.index = static_cast<size_t>(token) * n + local;
+    return cell;
+}
+
+// Operands of the epilogue that come from global memory, fetched before the reduction loop
+// so that their latency hides behind it.
+struct EpilogueOperands {
+    float bias, residual;
+};
+
+__device__ __forceinline__ EpilogueOperands fetch_epilogue(const EpilogueCtx& e,
+                                                           const OutputCell& cell) {
+    EpilogueOperands op;
+    op.bias = cell.bias != nullptr ? bf16_bits_to_float(__ldg(cell.bias + cell.local)) : 0.f;
+    op.residual = e.epilogue == MB_EPI_RESIDUAL
+                      ? bf16_bits_to_float(ld_cg_u16(
+                            reinterpret_cast<const unsigned short*>(e.residual) + cell.index))
+                      : 0.f;
+    return op;
+}
+
+__device__ __forceinline__ void store_output(const EpilogueCtx& e, const OutputCell& cell,
+                                             const EpilogueOperands& op, float acc,
+                                             float acc_pair) {
+    const float y = bf16_round(acc + op.bias);
     float result;
     switch (e.epilogue) {
-        case MB_EPI_RESIDUAL: {
-            const float res = bf16_bits_to_float(
-                ld_cg_u16(reinterpret_cast<const unsigned short*>(e.residual) + index));
-            result = res + y;
+        case MB_EPI_RESIDUAL:
+            result = op.residual + y;
             break;
-        }
         case MB_EPI_SILU_MUL:
             result = bf16_round(silu_f32(y)) * bf16_round(acc_pair);
             break;
@@ -315,121 +468,134 @@ __device__ __forceinline__ void store_output(const EpilogueCtx& e, int token, in
             result = y;
             break;
     }
-    reinterpret_cast<unsigned short*>(out)[index] = float_to_bf16_bits(result);
+    cell.out[cell.index] = float_to_bf16_bits(result);
 }
 
+// All consumer warps work on every stage together, in ring order (so no warp is ever more
+// than one mbarrier phase behind the slot it waits on): a stage holds 8 weight rows x k_chunk
+// elements, its 32-element groups are dealt round-robin to the 8 warps.  A = activations
+// (row = token), B = weights (n = weight row); the reduction index is permuted identically in
+// both so that every lane reads 16 contiguous bytes per group.  Each warp parks its partial
+// sums of a row block in shared memory; once a group of row blocks is through, one CTA barrier
+// lets warp w add up the eight partials of block w and run that block's epilogue.  That is one
+// barrier pair per 8 (paired: 4) row blocks instead of a reduction per stage.
 template <int NMAT>
-__device__ __noinline__ bool gemv_consume(const KernelParams& p, const mb_phase* P, int ph, SharedCtl* sc,
-                             const __nv_bfloat16* xs, float* red, const char* ring,
-                             unsigned int& it, int tid) {
+__device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseEntry* E, int ph,
+                                             SharedCtl* sc, const __nv_bfloat16* xs, float* red,
+                                             const char* ring, unsigned int& it, int tid) {
+    constexpr int NB = NMAT == 1 ? 8 : 4;  // row blocks per reduction group
+    constexpr int PV = 2 * NMAT;           // partial values per lane and block
     const int cta = blockIdx.x, ctas = gridDim.x;
-    const GemvGeom g = gemv_geometry(P, cta, ctas);
+    const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
     const int warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tq = lane & 3;
-    const int row_groups = g.row_tile / 8;
-    const int ksplit = kConsumerWarps / row_groups;
-    const int rg = warp % row_groups;
-    const int ks = warp / row_groups;
-    const int xpitch = g.K + 8;
-    const __nv_bfloat16* xrow = xs + static_cast<size_t>(min(gid, g.rows - 1)) * xpitch;
+    const int xpitch = g.K + 32;
+    const __nv_bfloat16* xrow = xs + static_cast<size_t>(min(gid, g.rows - 1)) * xpitch + 8 * tq;
 
     EpilogueCtx e;
-    e.P = P;
-    e.rows = g.rows;
-    e.epilogue = P->i[MB_GV_I_EPILOGUE];
+    e.epilogue = E->rec.i[MB_GV_I_EPILOGUE];
 #pragma unroll
     for (int s = 0; s < 3; ++s) {
         e.n[s] = g.n[s];
-        e.out[s] = s < g.nseg ? reinterpret_cast<char*>(slot_address(p, P->slot[MB_GV_S_OUT0 + s]))
+        e.out[s] = s < g.nseg ? reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_OUT0 + s))
                               : nullptr;
-        e.bias[s] = (s < g.nseg && P->slot[MB_GV_S_BIAS0 + s] >= 0)
-                        ? reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_BIAS0 + s]))
+        e.bias[s] = (s < g.nseg && E->rec.slot[MB_GV_S_BIAS0 + s] >= 0)
+                        ? reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_BIAS0 + s))
                         : nullptr;
     }
     e.residual = e.epilogue == MB_EPI_RESIDUAL
-                     ? reinterpret_cast<const char*>(slot_address(p, P->slot[MB_GV_S_RESIDUAL]))
+                     ? reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_RESIDUAL))
                      : nullptr;
 
-    int parity_red = 0;
-    for (int block0 = g.r0; block0 < g.r1; block0 += g.row_tile) {
-        float acc[NMAT][4];
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) acc[m][q] = 0.f;
-
-        for (int c = 0; c < g.n_chunks; ++c) {
-            const int stage = it % p.stages;
-            const unsigned int parity = (it / p.stages) & 1u;
-            if (!mbar_wait_bounded(&sc->full[stage], parity, &sc->abort_flag)) {
-                if (!sc->abort_flag) {
-                    record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
-                    sc->abort_flag = 1;
-                }
-                return false;
-            }
-            const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
-            const char* st = ring + static_cast<size_t>(stage) * kStageBytes;
-            const char* wrow = st + static_cast<size_t>(rg * 8 + gid) * g.pitch;
-            const __nv_bfloat16* xk = xrow + c * g.k_chunk;
-            const int kblocks = kc >> 4;
-#pragma unroll 4
-            for (int b = ks; b < kblocks; b += ksplit) {
-                const unsigned int a0 =
-                    *reinterpret_cast<const unsigned int*>(xk + b * 16 + 2 * tq);
-                const unsigned int a2 =
-                    *reinterpret_cast<const unsigned int*>(xk + b * 16 + 8 + 2 * tq);
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    const char* wm = wrow + static_cast<size_t>(m) * g.row_tile * g.pitch;
-                    const unsigned int b0 =
-                        *reinterpret_cast<const unsigned int*>(wm + (b * 16 + 2 * tq) * 2);
-                    const unsigned int b1 =
-                        *reinterpret_cast<const unsigned int*>(wm + (b * 16 + 8 + 2 * tq) * 2);
-                    mma_bf16_16816(acc[m], a0, 0u, a2, 0u, b0, b1);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sc->empty[stage]);
-            ++it;
-            if (tid == 0) sc->consumed = it;
+    bool dead = false;
+    for (int group0 = 0; group0 < g.n_blocks; group0 += NB) {
+        const int nb = min(NB, g.n_blocks - group0);
+        // The block this warp finalises, this lane's two output cells in it (token gid, rows
+        // v0 and v0 + 1) and their global epilogue operands: requested now, used after the
+        // reduction.
+        const int v0 = g.r0 + (group0 + warp) * kRowTile + 2 * tq;
+        const bool finalises = warp < nb && gid < g.rows;
+        const bool live0 = finalises && v0 < g.r1, live1 = finalises && v0 + 1 < g.r1;
+        OutputCell cell0 = {}, cell1 = {};
+        EpilogueOperands op0 = {0.f, 0.f}, op1 = {0.f, 0.f};
+        if (live0) {
+            cell0 = locate_output(e, gid, v0);
+            op0 = fetch_epilogue(e, cell0);
+        }
+        if (live1) {
+            cell1 = locate_output(e, gid, v0 + 1);
+            op1 = fetch_epilogue(e, cell1);
         }
 
-        // Cross-warp reduction over the k-split, then the epilogue in the ks == 0 warps.
-        if (ksplit > 1) {
-            float* slab = red + parity_red * (kReduceBytes / 8);
-            if (ks > 0) {
-                float* cell = slab + ((static_cast<size_t>(ks - 1) * row_groups + rg) * 32 + lane) *
-                                         (2 * NMAT);
+        for (int b = 0; b < nb; ++b) {
+            // two accumulator sets per matrix keep the MMA dependency chains short
+            float acc[NMAT][2][4];
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    cell[2 * m] = acc[m][0];
-                    cell[2 * m + 1] = acc[m][1];
+            for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) acc[m][u][q] = 0.f;
+
+            for (int c = 0; c < g.n_chunks; ++c) {
+                const int stage = it % p.stages;
+                const unsigned int parity = (it / p.stages) & 1u;
+                ++it;
+                // A wait that runs out must not make this warp leave: the others would hang
+                // at the next CTA barrier.  It records the fault, and every warp then falls
+                // through the remaining loops without waiting or computing.
+                if (dead || sc->abort_flag ||
+                    !mbar_wait_bounded(&sc->full[stage], parity, &sc->abort_flag)) {
+                    if (!dead && !sc->abort_flag) {
+                        record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
+                        sc->abort_flag = 1;
+                    }
+                    dead = true;
+                    continue;
                 }
-            }
-            named_barrier(kBarReduce, kConsumerThreads);
-            if (ks == 0) {
-                for (int other = 1; other < ksplit; ++other) {
-                    const float* cell =
-                        slab + ((static_cast<size_t>(other - 1) * row_groups + rg) * 32 + lane) *
-                                   (2 * NMAT);
+                const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
+                const char* wrow = ring + static_cast<size_t>(stage) * kStageBytes +
+                                   static_cast<size_t>(gid) * g.pitch + 16 * tq;
+                const __nv_bfloat16* xk = xrow + c * g.k_chunk;
+                const int groups = kc >> 5;  // 32 reduction elements per group
+                for (int grp = warp; grp < groups; grp += kConsumerWarps) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(xk + 32 * grp);
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) {
-                        acc[m][0] += cell[2 * m];
-                        acc[m][1] += cell[2 * m + 1];
+                        const uint4 w = *reinterpret_cast<const uint4*>(
+                            wrow + static_cast<size_t>(m) * kRowTile * g.pitch + 64 * grp);
+                        mma_bf16_16816(acc[m][0], a.x, 0u, a.y, 0u, w.x, w.y);
+                        mma_bf16_16816(acc[m][1], a.z, 0u, a.w, 0u, w.z, w.w);
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sc->empty[stage]);
             }
-            parity_red ^= 1;
+            float* cell = red + (static_cast<size_t>(b * kConsumerWarps + warp) * 32 + lane) * PV;
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                cell[2 * m] = acc[m][0][0] + acc[m][1][0];
+                cell[2 * m + 1] = acc[m][0][1] + acc[m][1][1];
+            }
         }
-        if (ks == 0 && gid < g.rows) {
-            const int v0 = block0 + rg * 8 + 2 * tq;
-            if (v0 < g.r1) store_output(e, gid, v0, acc[0][0], NMAT > 1 ? acc[NMAT - 1][0] : 0.f);
-            if (v0 + 1 < g.r1)
-                store_output(e, gid, v0 + 1, acc[0][1], NMAT > 1 ? acc[NMAT - 1][1] : 0.f);
+        named_barrier(kBarConsumers, kConsumerThreads);
+        if (warp < nb && !dead) {
+            float total[PV];
+#pragma unroll
+            for (int v = 0; v < PV; ++v) total[v] = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float* cell =
+                    red + (static_cast<size_t>(warp * kConsumerWarps + w) * 32 + lane) * PV;
+#pragma unroll
+                for (int v = 0; v < PV; ++v) total[v] += cell[v];
+            }
+            if (live0) store_output(e, cell0, op0, total[0], NMAT > 1 ? total[2] : 0.f);
+            if (live1) store_output(e, cell1, op1, total[1], NMAT > 1 ? total[3] : 0.f);
         }
+        if (group0 + NB < g.n_blocks) named_barrier(kBarConsumers, kConsumerThreads);
     }
-    return true;
+    return !dead && !sc->abort_flag;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -470,11 +636,25 @@ __device__ __forceinline__ int choose_chunks(int pairs, int nblocks, int ctas, i
 // Shared scratch of the attention body (carved from the activation region):
 //   qs       [8][D + 32] bf16   rotated query rows of one kv-head group
 //   cs       [D] fp32           cos (first half) and sin (second half), already bf16-rounded
+//   wstat    [2][8 warps][8] fp32   per-warp row maxima / row sums of the exact mode
+//   fold     [8][64] + [8] fp32     chunk weights and denominators of the cross-CTA fold
 //   merge    [merge_slots][group][D + 2] fp32   per-warp (max, sum, values) states
 //   running  [2][group][D + 2] fp32             CTA state, ping-pong over merge rounds
+//   scores   [group][exact_keys] fp32           score rows of the exact mode
+//
+// Two softmax modes.  The reference normalises the probabilities in fp32 and rounds them to
+// bf16 *before* the value product (ops/attention.py:82-84).
+//   exact  (one CTA owns all keys of a (row, kv head) and they fit `exact_keys`): three
+//          passes over the CTA's score rows in shared memory -- row max, exp and row sum,
+//          then bf16(exp / sum) feeds the value product -- which reproduces that rounding.
+//   split  (long contexts): online softmax per warp with unnormalised bf16 probabilities,
+//          states merged across warps and, through global partials, across CTAs by the last
+//          chunk to arrive.  With thousands of keys the rounding of single probabilities
+//          averages out far below one bf16 ulp of the result.
 template <int D>
-__device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_phase* P, int ph, SharedCtl* sc,
-                                 char* scratch, int tid) {
+__device__ __forceinline__ bool attention_decode(const KernelParams& p, const PhaseEntry* E, int ph,
+                                              SharedCtl* sc, char* scratch, int tid) {
+    const mb_phase* P = &E->rec;
     constexpr int QP = D + 32;  // bf16 pitch of the rotated query rows
     constexpr int DC = D / 32;  // 32-element chunks of the head dimension (QK^T)
     constexpr int DB = D / 64;  // 64-element blocks of the head dimension (PV)
@@ -485,6 +665,7 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
     const int cap = P->i[MB_AT_I_CAPACITY];
     const int max_chunks = P->i[MB_AT_I_MAX_CHUNKS];
     const int merge_slots = P->i[MB_AT_I_MERGE_SLOTS];
+    const int exact_keys = P->i[MB_AT_I_EXACT_KEYS];
     const int group = Hq / Hkv;  // query heads per kv head, <= 8
     const float scale = P->f[MB_AT_F_SCALE];
     const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
@@ -494,23 +675,23 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
     const int cta = blockIdx.x, ctas = gridDim.x;
 
     const unsigned short* qbuf =
-        reinterpret_cast<const unsigned short*>(slot_address(p, P->slot[MB_AT_S_Q]));
+        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_Q));
     const unsigned short* kbuf =
-        reinterpret_cast<const unsigned short*>(slot_address(p, P->slot[MB_AT_S_K]));
+        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_K));
     const unsigned short* vbuf =
-        reinterpret_cast<const unsigned short*>(slot_address(p, P->slot[MB_AT_S_V]));
+        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_V));
     unsigned short* kcache =
-        reinterpret_cast<unsigned short*>(slot_address(p, P->slot[MB_AT_S_KCACHE]));
+        reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_KCACHE));
     unsigned short* vcache =
-        reinterpret_cast<unsigned short*>(slot_address(p, P->slot[MB_AT_S_VCACHE]));
-    const int* lenp = reinterpret_cast<const int*>(slot_address(p, P->slot[MB_AT_S_LEN]));
+        reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_VCACHE));
+    const int* lenp = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
     const long long* pos =
-        reinterpret_cast<const long long*>(slot_address(p, P->slot[MB_AT_S_POS]));
-    const void* invf = reinterpret_cast<const void*>(slot_address(p, P->slot[MB_AT_S_INVFREQ]));
+        reinterpret_cast<const long long*>(entry_address(p, E, MB_AT_S_POS));
+    const void* invf = reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_INVFREQ));
     const bool invf_bf16 = P->i[MB_AT_I_INVFREQ_BF16] != 0;
-    unsigned short* out = reinterpret_cast<unsigned short*>(slot_address(p, P->slot[MB_AT_S_OUT]));
-    float* partial = reinterpret_cast<float*>(slot_address(p, P->slot[MB_AT_S_PARTIAL]));
-    int* counter = reinterpret_cast<int*>(slot_address(p, P->slot[MB_AT_S_COUNTER]));
+    unsigned short* out = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_OUT));
+    float* partial = reinterpret_cast<float*>(entry_address(p, E, MB_AT_S_PARTIAL));
+    int* counter = reinterpret_cast<int*>(entry_address(p, E, MB_AT_S_COUNTER));
 
     const int L = __ldcg(lenp);
     if (L < 0 || L + 1 > cap) {
@@ -524,19 +705,26 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
     const int nkeys = L + 1;
     const int nblocks = (nkeys + 15) >> 4;
     const int pairs = B * Hkv;
-    if (warp == 0) {
-        const int nc_pick = choose_chunks(pairs, nblocks, ctas, max_chunks, lane);
-        if (lane == 0) sc->bcast[0] = nc_pick;
+    const bool exact = nkeys <= exact_keys;
+    int nc = 1;
+    if (!exact) {
+        if (warp == 0) {
+            const int nc_pick = choose_chunks(pairs, nblocks, ctas, max_chunks, lane);
+            if (lane == 0) sc->bcast[0] = nc_pick;
+        }
+        named_barrier(kBarConsumers, kConsumerThreads);
+        nc = sc->bcast[0];
     }
-    named_barrier(kBarConsumers, kConsumerThreads);
-    const int nc = sc->bcast[0];
     const int items = pairs * nc;
 
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(scratch);
     float* cs = reinterpret_cast<float*>(scratch + 8 * QP * 2);
-    float* merge = cs + D;
+    float* wstat = cs + D;                      // [2][kConsumerWarps][8]
+    float* fold = wstat + 2 * kConsumerWarps * 8;  // [8][64] chunk weights + [8] denominators
+    float* merge = fold + kFoldFloats;
     float* running = merge + static_cast<size_t>(merge_slots) * group * SW;
-    const size_t key_stride = static_cast<size_t>(Hkv) * D;  // elements between keys
+    float* srow = running + 2 * static_cast<size_t>(group) * SW;  // [group][exact_keys]
+    const size_t key_stride = static_cast<size_t>(Hkv) * D;        // elements between keys
 
     for (int item = cta; item < items; item += ctas) {
         const int pair = item / nc, chunk = item - pair * nc;
@@ -559,9 +747,9 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
             const unsigned short* qrow = qbuf + (static_cast<size_t>(b) * Hq + h * group + gq) * D;
             const float x1 = bf16_bits_to_float(ld_cg_u16(qrow + i));
             const float x2 = bf16_bits_to_float(ld_cg_u16(qrow + i + D / 2));
-            const float c = cs[i], s = cs[D / 2 + i];
-            float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
-            float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+            const float c = cs[i], sn = cs[D / 2 + i];
+            float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * sn));
+            float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * sn));
             if (q_scale != 0.f && q_scale != 1.f) {
                 r1 = bf16_round(r1 * q_scale);
                 r2 = bf16_round(r2 * q_scale);
@@ -576,16 +764,15 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
             for (int i = tid; i < D / 2; i += kConsumerThreads) {
                 const float x1 = bf16_bits_to_float(ld_cg_u16(krow + i));
                 const float x2 = bf16_bits_to_float(ld_cg_u16(krow + i + D / 2));
-                const float c = cs[i], s = cs[D / 2 + i];
-                kcache[row + i] = float_to_bf16_bits(bf16_round(x1 * c) + bf16_round(-x2 * s));
+                const float c = cs[i], sn = cs[D / 2 + i];
+                kcache[row + i] = float_to_bf16_bits(bf16_round(x1 * c) + bf16_round(-x2 * sn));
                 kcache[row + i + D / 2] =
-                    float_to_bf16_bits(bf16_round(x2 * c) + bf16_round(x1 * s));
+                    float_to_bf16_bits(bf16_round(x2 * c) + bf16_round(x1 * sn));
             }
             for (int i = tid; i < D; i += kConsumerThreads) vcache[row + i] = ld_cg_u16(vrow + i);
         }
         named_barrier(kBarConsumers, kConsumerThreads);
 
-        // ---- main loop: each warp owns the 16-key blocks blk0 + warp, + 8, ...
         // QK^T: A = rotated queries (row = head of the group), B = keys (n = key).  The head
         // dimension is permuted identically in both operands so that every lane fetches 16
         // contiguous bytes of its key per 32-element chunk.
@@ -638,60 +825,31 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
                                   : make_uint4(0u, 0u, 0u, 0u);
             }
         };
-        constexpr bool kPrefetchKeys = D <= 128;
-        constexpr bool kPrefetchValues = D <= 64;
-
-        uint4 kt[2][DC], kt_next[2][DC];
-        uint4 vt[DB][4], vt_next[DB][4];
-        int blk = blk0 + warp;
-        if (blk < blk1) {
-            if (kPrefetchKeys) load_keys(blk, kt);
-            if (kPrefetchValues) load_values(blk, vt);
-        }
-        for (; blk < blk1; blk += kConsumerWarps) {
-            const int kb = blk << 4;
-            const int following = blk + kConsumerWarps;
-            if (!kPrefetchKeys) load_keys(blk, kt);
-            if (!kPrefetchValues) load_values(blk, vt);
-            if (following < blk1) {
-                if (kPrefetchKeys) load_keys(following, kt_next);
-                if (kPrefetchValues) load_values(following, vt_next);
-            }
-            float sc_[2][4];
+        // scores of one block: sv[2j + q] <-> head gid, key kb + 8j + 2tq + q; bf16-rounded
+        // product, scale applied in fp32, keys past the valid length masked
+        auto block_scores = [&](int kb, const uint4 (&kt)[2][DC], float (&sv)[4]) {
+            float frag[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                sc_[j][0] = sc_[j][1] = sc_[j][2] = sc_[j][3] = 0.f;
+                frag[j][0] = frag[j][1] = frag[j][2] = frag[j][3] = 0.f;
 #pragma unroll
                 for (int i = 0; i < DC; ++i) {
-                    mma_bf16_16816(sc_[j], qf[i].x, 0u, qf[i].y, 0u, kt[j][i].x, kt[j][i].y);
-                    mma_bf16_16816(sc_[j], qf[i].z, 0u, qf[i].w, 0u, kt[j][i].z, kt[j][i].w);
+                    mma_bf16_16816(frag[j], qf[i].x, 0u, qf[i].y, 0u, kt[j][i].x, kt[j][i].y);
+                    mma_bf16_16816(frag[j], qf[i].z, 0u, qf[i].w, 0u, kt[j][i].z, kt[j][i].w);
                 }
             }
-            // bf16-rounded score, fp32 scale, key mask; sv[2j+q] <-> key kb + 8j + 2tq + q
-            float sv[4];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                     const int key = kb + 8 * j + 2 * tq + q;
-                    const float s = bf16_round(sc_[j][q]) * scale;
+                    const float s = bf16_round(frag[j][q]) * scale;
                     sv[2 * j + q] = key < nkeys ? s : -INFINITY;
                 }
-            float bmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-            bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
-            bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
-            const float m_new = fmaxf(m_run, bmax);
-            const float alpha = expf(m_run - m_new);
-            float pv[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) pv[q] = expf(sv[q] - m_new);
-            l_run = l_run * alpha + ((pv[0] + pv[1]) + (pv[2] + pv[3]));
-            m_run = m_new;
-            const unsigned int pb0 = pack_bf16(pv[0], pv[1]);  // keys 2tq, 2tq+1 of head gid
-            const unsigned int pb1 = pack_bf16(pv[2], pv[3]);  // keys 8+2tq, 9+2tq
-            // rescale factors of the two heads this lane accumulates (columns 2tq, 2tq+1)
-            const float alpha0 = __shfl_sync(0xffffffffu, alpha, (2 * tq) * 4);
-            const float alpha1 = __shfl_sync(0xffffffffu, alpha, (2 * tq + 1) * 4);
+        };
+        // acc += V^T P^T for one block; pb0/pb1 = probabilities of keys (2tq, 2tq+1) and
+        // (8+2tq, 9+2tq) of head gid, packed bf16
+        auto block_values = [&](const uint4 (&vt)[DB][4], unsigned int pb0, unsigned int pb1) {
 #pragma unroll
             for (int x = 0; x < DB; ++x) {
                 const unsigned int ra[4] = {vt[x][0].x, vt[x][0].y, vt[x][0].z, vt[x][0].w};
@@ -700,10 +858,6 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
                 const unsigned int rd[4] = {vt[x][3].x, vt[x][3].y, vt[x][3].z, vt[x][3].w};
 #pragma unroll
                 for (int mt = 0; mt < 4; ++mt) {
-                    acc[x][mt][0] *= alpha0;
-                    acc[x][mt][1] *= alpha1;
-                    acc[x][mt][2] *= alpha0;
-                    acc[x][mt][3] *= alpha1;
                     const unsigned int a0 = __byte_perm(ra[mt], rb[mt], 0x5410u);
                     const unsigned int a1 = __byte_perm(ra[mt], rb[mt], 0x7632u);
                     const unsigned int a2 = __byte_perm(rc[mt], rd[mt], 0x5410u);
@@ -711,18 +865,130 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
                     mma_bf16_16816(acc[x][mt], a0, a1, a2, a3, pb0, pb1);
                 }
             }
-            if (following < blk1) {
-                if (kPrefetchKeys) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int i = 0; i < DC; ++i) kt[j][i] = kt_next[j][i];
+        };
+
+        uint4 kt[2][DC];
+        uint4 vt[DB][4];
+        if (exact) {
+            // ---- pass 1: scores into shared rows, row maxima
+            float rmax = -INFINITY;
+            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
+                const int kb = blk << 4;
+                float sv[4];
+                load_keys(blk, kt);
+                block_scores(kb, kt, sv);
+                if (gid < group) {
+                    float* row = srow + static_cast<size_t>(gid) * exact_keys + kb + 2 * tq;
+                    row[0] = sv[0];
+                    row[1] = sv[1];
+                    row[8] = sv[2];
+                    row[9] = sv[3];
                 }
-                if (kPrefetchValues) {
+                rmax = fmaxf(rmax, fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])));
+            }
+            rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+            rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+            if (tq == 0) wstat[warp * 8 + gid] = rmax;
+            named_barrier(kBarConsumers, kConsumerThreads);
+            float row_max = -INFINITY;
 #pragma unroll
-                    for (int x = 0; x < DB; ++x)
+            for (int w = 0; w < kConsumerWarps; ++w) row_max = fmaxf(row_max, wstat[w * 8 + gid]);
+            // ---- pass 2: exponentials in place, row sums
+            float rsum = 0.f;
+            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
+                if (gid < group) {
+                    float* row = srow + static_cast<size_t>(gid) * exact_keys + (blk << 4) + 2 * tq;
+                    const float e0 = expf(row[0] - row_max), e1 = expf(row[1] - row_max);
+                    const float e2 = expf(row[8] - row_max), e3 = expf(row[9] - row_max);
+                    row[0] = e0;
+                    row[1] = e1;
+                    row[8] = e2;
+                    row[9] = e3;
+                    rsum += (e0 + e1) + (e2 + e3);
+                }
+            }
+            rsum += __shfl_xor_sync(0xffffffffu, rsum, 1);
+            rsum += __shfl_xor_sync(0xffffffffu, rsum, 2);
+            if (tq == 0) wstat[(kConsumerWarps + warp) * 8 + gid] = rsum;
+            named_barrier(kBarConsumers, kConsumerThreads);
+            float row_sum = 0.f;
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) vt[x][q] = vt_next[x][q];
+            for (int w = 0; w < kConsumerWarps; ++w) row_sum += wstat[(kConsumerWarps + w) * 8 + gid];
+            // ---- pass 3: normalised probabilities rounded to bf16, value product
+            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
+                load_values(blk, vt);
+                float pv[4] = {0.f, 0.f, 0.f, 0.f};
+                if (gid < group) {
+                    const float* row =
+                        srow + static_cast<size_t>(gid) * exact_keys + (blk << 4) + 2 * tq;
+                    pv[0] = row[0] / row_sum;
+                    pv[1] = row[1] / row_sum;
+                    pv[2] = row[8] / row_sum;
+                    pv[3] = row[9] / row_sum;
+                }
+                block_values(vt, pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]));
+            }
+            // already normalised: merge as plain sums (max 0, total weight 1)
+            m_run = 0.f;
+            l_run = (warp == 0 && tq == 0) ? 1.f : 0.f;
+        } else {
+            // ---- online softmax, one 16-key block per iteration, next block prefetched
+            constexpr bool kPrefetchKeys = D <= 128;
+            constexpr bool kPrefetchValues = D <= 64;
+            uint4 kt_next[2][DC];
+            uint4 vt_next[DB][4];
+            int blk = blk0 + warp;
+            if (blk < blk1) {
+                if (kPrefetchKeys) load_keys(blk, kt);
+                if (kPrefetchValues) load_values(blk, vt);
+            }
+            for (; blk < blk1; blk += kConsumerWarps) {
+                const int kb = blk << 4;
+                const int following = blk + kConsumerWarps;
+                if (!kPrefetchKeys) load_keys(blk, kt);
+                if (!kPrefetchValues) load_values(blk, vt);
+                if (following < blk1) {
+                    if (kPrefetchKeys) load_keys(following, kt_next);
+                    if (kPrefetchValues) load_values(following, vt_next);
+                }
+                float sv[4];
+                block_scores(kb, kt, sv);
+                float bmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+                bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+                bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+                const float m_new = fmaxf(m_run, bmax);
+                const float alpha = expf(m_run - m_new);
+                float pv[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pv[q] = expf(sv[q] - m_new);
+                l_run = l_run * alpha + ((pv[0] + pv[1]) + (pv[2] + pv[3]));
+                m_run = m_new;
+                // rescale factors of the two heads this lane accumulates (columns 2tq, 2tq+1)
+                const float alpha0 = __shfl_sync(0xffffffffu, alpha, (2 * tq) * 4);
+                const float alpha1 = __shfl_sync(0xffffffffu, alpha, (2 * tq + 1) * 4);
+#pragma unroll
+                for (int x = 0; x < DB; ++x)
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        acc[x][mt][0] *= alpha0;
+                        acc[x][mt][1] *= alpha1;
+                        acc[x][mt][2] *= alpha0;
+                        acc[x][mt][3] *= alpha1;
+                    }
+                block_values(vt, pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]));
+                if (following < blk1) {
+                    if (kPrefetchKeys) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+#pragma unroll
+                            for (int i = 0; i < DC; ++i) kt[j][i] = kt_next[j][i];
+                    }
+                    if (kPrefetchValues) {
+#pragma unroll
+                        for (int x = 0; x < DB; ++x)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) vt[x][q] = vt_next[x][q];
+                    }
                 }
             }
         }
@@ -762,19 +1028,19 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
             for (int e = tid; e < group * SW; e += kConsumerThreads) {
                 const int gq = e / SW, col = e - gq * SW;
                 float mx = round == 0 ? -INFINITY : prev[gq * SW];
-                for (int s = 0; s < live; ++s)
-                    mx = fmaxf(mx, merge[(static_cast<size_t>(s) * group + gq) * SW]);
+                for (int w = 0; w < live; ++w)
+                    mx = fmaxf(mx, merge[(static_cast<size_t>(w) * group + gq) * SW]);
                 float sum_l = 0.f, sum_v = 0.f;
                 if (round > 0) {
-                    const float w = expf(prev[gq * SW] - mx);
-                    sum_l = prev[gq * SW + 1] * w;
-                    sum_v = prev[gq * SW + col] * w;
+                    const float wgt = expf(prev[gq * SW] - mx);
+                    sum_l = prev[gq * SW + 1] * wgt;
+                    sum_v = prev[gq * SW + col] * wgt;
                 }
-                for (int s = 0; s < live; ++s) {
-                    const float* st = merge + (static_cast<size_t>(s) * group + gq) * SW;
-                    const float w = expf(st[0] - mx);  // 0 for a warp that saw no block
-                    sum_l += st[1] * w;
-                    sum_v += st[col] * w;
+                for (int w = 0; w < live; ++w) {
+                    const float* st = merge + (static_cast<size_t>(w) * group + gq) * SW;
+                    const float wgt = expf(st[0] - mx);  // 0 for a warp that saw no block
+                    sum_l += st[1] * wgt;
+                    sum_v += st[col] * wgt;
                 }
                 next[e] = col == 0 ? mx : (col == 1 ? sum_l : sum_v);
             }
@@ -800,22 +1066,43 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
             }
             named_barrier(kBarConsumers, kConsumerThreads);
             if (sc->bcast[1] == nc - 1) {
-                // last chunk of this (row, kv head) to arrive: fold all chunks in chunk order
+                // Last chunk of this (row, kv head) to arrive folds all chunks, in chunk order.
+                // Step 1: the (max, sum) pairs of all chunks -> per-chunk weights in shared
+                // memory.
                 const float* all = partial + static_cast<size_t>(pair) * max_chunks * group * SW;
+                float* weight = fold;            // [group][nc] chunk maxima, then weights
+                float* denom = fold + 8 * 64;    // [group]
+                float* sums = merge;             // [group][nc] chunk sums (merge slots are free)
+                for (int e = tid; e < group * nc; e += kConsumerThreads) {
+                    const int gq = e / nc, c = e - gq * nc;
+                    const float* st = all + (static_cast<size_t>(c) * group + gq) * SW;
+                    weight[e] = ld_cg_f32(st);
+                    sums[e] = ld_cg_f32(st + 1);
+                }
+                named_barrier(kBarConsumers, kConsumerThreads);
+                if (tid < group) {
+                    float mx = -INFINITY;
+                    for (int c = 0; c < nc; ++c) mx = fmaxf(mx, weight[tid * nc + c]);
+                    float total = 0.f;
+                    for (int c = 0; c < nc; ++c) {
+                        const float wgt = expf(weight[tid * nc + c] - mx);
+                        weight[tid * nc + c] = wgt;
+                        total += sums[tid * nc + c] * wgt;
+                    }
+                    denom[tid] = total;
+                }
+                named_barrier(kBarConsumers, kConsumerThreads);
+                // Step 2: weighted sums of the value partials; loads are independent.
                 for (int e = tid; e < group * D; e += kConsumerThreads) {
                     const int gq = e / D, d = e - gq * D;
-                    float mx = -INFINITY;
+                    const float* col = all + static_cast<size_t>(gq) * SW + 2 + d;
+                    float sum_v = 0.f;
+#pragma unroll 8
                     for (int c = 0; c < nc; ++c)
-                        mx = fmaxf(mx, ld_cg_f32(all + (static_cast<size_t>(c) * group + gq) * SW));
-                    float sum_l = 0.f, sum_v = 0.f;
-                    for (int c = 0; c < nc; ++c) {
-                        const float* st = all + (static_cast<size_t>(c) * group + gq) * SW;
-                        const float w = expf(ld_cg_f32(st) - mx);
-                        sum_l += ld_cg_f32(st + 1) * w;
-                        sum_v += ld_cg_f32(st + 2 + d) * w;
-                    }
+                        sum_v += ld_cg_f32(col + static_cast<size_t>(c) * group * SW) *
+                                 weight[gq * nc + c];
                     out[(static_cast<size_t>(b) * Hq + h * group + gq) * D + d] =
-                        float_to_bf16_bits(sum_v / sum_l);
+                        float_to_bf16_bits(sum_v / denom[gq]);
                 }
                 if (tid == 0) counter[pair] = 0;  // ready for the next launch
             }
@@ -825,10 +1112,45 @@ __device__ __noinline__ bool attention_decode(const KernelParams& p, const mb_ph
     return true;
 }
 
+// The common shapes (head_dim 64, rows up to 2048 elements) are inlined into the phase loop;
+// the rare variants are kept out of line so that their register needs do not shape the
+// allocation of the common path.
+__device__ __noinline__ bool attention_decode_128(const KernelParams& p, const PhaseEntry* E,
+                                                  int ph, SharedCtl* sc, char* scratch, int tid) {
+    return attention_decode<128>(p, E, ph, sc, scratch, tid);
+}
+__device__ __noinline__ bool attention_decode_256(const KernelParams& p, const PhaseEntry* E,
+                                                  int ph, SharedCtl* sc, char* scratch, int tid) {
+    return attention_decode<256>(p, E, ph, sc, scratch, tid);
+}
+__device__ __noinline__ void activation_prologue_wide(const KernelParams& p, const PhaseEntry* E,
+                                                      int ph, SharedCtl* sc, __nv_bfloat16* xs,
+                                                      int tid) {
+    if (E->rec.i[MB_GV_I_K] <= 16 * kConsumerThreads)
+        activation_prologue<2>(p, E, ph, sc, xs, tid);
+    else
+        activation_prologue<0>(p, E, ph, sc, xs, tid);
+}
+
 // ---------------------------------------------------------------------------------------
 // The kernel.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const __grid_constant__ KernelParams p) {
+__device__ __forceinline__ void prefetch_entry(const PhaseEntry* src, PhaseEntry* dst, int tid) {
+    // 16-byte asynchronous copies global -> shared of one phase entry
+    if (tid < kEntryVectors) {
+        const unsigned int d = smem_u32(reinterpret_cast<char*>(dst) + 16 * tid);
+        const char* g = reinterpret_cast<const char*>(src) + 16 * tid;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(g) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void wait_entry() {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+decode_kernel(const __grid_constant__ KernelParams p) {
     extern __shared__ __align__(128) char smem[];
     SharedCtl* sc = reinterpret_cast<SharedCtl*>(smem);
     float* red = reinterpret_cast<float*>(smem + kCtlBytes);
@@ -843,8 +1165,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const __grid_consta
         }
         sc->abort_flag = peek_status(p.ctl) != 0 ? 1 : 0;  // a faulted plan runs nothing
         sc->issued = 0;
-        sc->consumed = 0;
         mbar_init_fence();
+    }
+    if (tid < kConsumerThreads) {
+        prefetch_entry(p.entries, &sc->entry[0], tid);
+        wait_entry();
     }
     __syncthreads();
     if (sc->abort_flag) return;
@@ -858,65 +1183,96 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const __grid_consta
         unsigned int it = 0;
         int barrier_index = 0;
         bool ok = true;
+        // Optional per-phase trace: thread 0 of every CTA stamps the global timer at phase
+        // start (0), after the activation prologue (1), after the body (2) and after the
+        // closing grid barrier (3).
+        auto stamp = [&](int ph, int event) {
+            if (p.trace != nullptr && tid == 0)
+                p.trace[(static_cast<size_t>(blockIdx.x) * p.n_phases + ph) * 4 + event] =
+                    global_timer_ns();
+        };
         for (int ph = 0; ph < p.n_phases && ok; ++ph) {
-            const mb_phase* P = p.phases + ph;
-            switch (P->body) {
+            // The entry of this phase is in shared memory already; fetch the next one now so
+            // that no phase starts with a dependent chain of global loads.
+            const PhaseEntry* E = &sc->entry[ph & 1];
+            const bool more = ph + 1 < p.n_phases;
+            if (more) prefetch_entry(p.entries + ph + 1, &sc->entry[(ph + 1) & 1], tid);
+            stamp(ph, 0);
+            switch (E->rec.body) {
                 case MB_BODY_NOP:
                     break;
-                case MB_BODY_GEMV:
-                    activation_prologue(p, P, ph, sc, reinterpret_cast<__nv_bfloat16*>(act), tid);
-                    if (P->i[MB_GV_I_NMAT] == 2)
-                        ok = gemv_consume<2>(p, P, ph, sc,
-                                             reinterpret_cast<const __nv_bfloat16*>(act), red, ring,
-                                             it, tid);
+                case MB_BODY_GEMV: {
+                    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(act);
+                    const int K = E->rec.i[MB_GV_I_K];
+                    if (K <= 8 * kConsumerThreads)
+                        activation_prologue<1>(p, E, ph, sc, xs, tid);
                     else
-                        ok = gemv_consume<1>(p, P, ph, sc,
-                                             reinterpret_cast<const __nv_bfloat16*>(act), red, ring,
-                                             it, tid);
+                        activation_prologue_wide(p, E, ph, sc, xs, tid);
+                    stamp(ph, 1);
+                    if (E->rec.i[MB_GV_I_NMAT] == 2)
+                        gemv_consume<2>(p, E, ph, sc, xs, red, ring, it, tid);
+                    else
+                        gemv_consume<1>(p, E, ph, sc, xs, red, ring, it, tid);
                     break;
+                }
                 case MB_BODY_ATTN_DECODE: {
-                    const int D = P->i[MB_AT_I_HEAD_DIM];
+                    const int D = E->rec.i[MB_AT_I_HEAD_DIM];
                     if (D == 64)
-                        ok = attention_decode<64>(p, P, ph, sc, act, tid);
+                        attention_decode<64>(p, E, ph, sc, act, tid);
                     else if (D == 128)
-                        ok = attention_decode<128>(p, P, ph, sc, act, tid);
+                        attention_decode_128(p, E, ph, sc, act, tid);
                     else
-                        ok = attention_decode<256>(p, P, ph, sc, act, tid);
+                        attention_decode_256(p, E, ph, sc, act, tid);
                     break;
                 }
                 default:
                     if (tid == 0) {
-                        record_status(p.ctl, MB_ST_BAD_PHASE, ph, P->body);
+                        record_status(p.ctl, MB_ST_BAD_PHASE, ph, E->rec.body);
                         sc->abort_flag = 1;
                     }
-                    ok = false;
                     break;
             }
-            if (!ok) break;
-            if (P->flags & MB_FLAG_BARRIER) {
+            // Whether to go on is decided once per CTA, by thread 0 inside the barrier below
+            // (a fault raises the CTA's abort flag; bodies never leave early on their own
+            // except for conditions every thread evaluates identically).
+            stamp(ph, 2);
+            const int flags = E->rec.flags;
+            const unsigned long long length_address =
+                (flags & MB_FLAG_BUMP_LENGTH) ? entry_address(p, E, MB_AT_S_LEN) : 0ull;
+            if (more) wait_entry();  // made visible to the CTA by the barrier below
+            if (flags & MB_FLAG_BARRIER) {
                 ++barrier_index;
                 ok = grid_barrier(p.ctl, base + barrier_index * gridDim.x, kBarConsumers,
-                                  kConsumerThreads, tid, &sc->abort_flag, ph);
-                if (ok && (P->flags & MB_FLAG_BUMP_LENGTH) && blockIdx.x == 0 && tid == 0) {
-                    int* lenp = reinterpret_cast<int*>(slot_address(p, P->slot[MB_AT_S_LEN]));
+                                  kConsumerThreads, tid, &sc->abort_flag, &sc->verdict, ph);
+                if (ok && length_address != 0ull && blockIdx.x == 0 && tid == 0) {
+                    int* lenp = reinterpret_cast<int*>(length_address);
                     *lenp = *lenp + 1;
                 }
+                stamp(ph, 3);
+            } else if (more) {
+                named_barrier(kBarConsumers, kConsumerThreads);
+                if (tid == 0) sc->verdict = sc->abort_flag == 0 ? 1 : 0;
+                named_barrier(kBarConsumers, kConsumerThreads);
+                ok = sc->verdict != 0;
             }
         }
         if (ok) {
             // Closing barrier: nobody may still read `calls` when CTA 0 advances it.
             ++barrier_index;
             ok = grid_barrier(p.ctl, base + barrier_index * gridDim.x, kBarConsumers,
-                              kConsumerThreads, tid, &sc->abort_flag, p.n_phases);
+                              kConsumerThreads, tid, &sc->abort_flag, &sc->verdict, p.n_phases);
             if (ok && blockIdx.x == 0 && tid == 0) p.ctl->calls = calls + 1;
         }
     }
 
-    // Drain: never leave while one of this CTA's bulk copies is still in flight.
+    // Drain: never leave while one of this CTA's bulk copies is still in flight.  After an
+    // abort the producer stopped issuing; wait (bounded) for every stage it armed.
     __syncthreads();
     if (sc->abort_flag && tid == 0) {
-        const unsigned int issued = sc->issued, consumed = sc->consumed;
-        for (unsigned int s = consumed; s < issued; ++s) {
+        const unsigned int issued = sc->issued;
+        const unsigned int first = issued > static_cast<unsigned int>(p.stages)
+                                       ? issued - p.stages : 0u;
+        for (unsigned int s = first; s < issued; ++s) {
             const int stage = s % p.stages;
             const unsigned int parity = (s / p.stages) & 1u;
             for (unsigned int tries = 0; tries < kDrainTryLimit; ++tries)
@@ -932,6 +1288,7 @@ int decode_fixed_smem() { return decode::kFixedBytes; }
 int decode_stage_bytes() { return decode::kStageBytes; }
 int decode_max_stages() { return decode::kMaxStages; }
 int decode_row_pad() { return decode::kRowPad; }
+int decode_row_tile() { return decode::kRowTile; }
 
 cudaError_t decode_configure(int smem_bytes) {
     return cudaFuncSetAttribute(decode::decode_kernel,

@@ -21,10 +21,21 @@ struct Control {
     unsigned int pad[2];
 };
 
+// One phase as the kernel reads it: the record plus the device address of every slot it
+// names, resolved by the host at bind time so that the kernel never chases a slot index
+// through a second table.  A per-launch (dynamic) slot holds kDynamicTag | ordinal instead.
+struct PhaseEntry {
+    mb_phase rec;
+    unsigned long long addr[MB_PHASE_SLOTS];
+    unsigned long long pad;  // keeps sizeof a multiple of 16 (copied in 16-byte vectors)
+};
+static_assert(sizeof(PhaseEntry) % 16 == 0, "PhaseEntry must be a whole number of 16-byte vectors");
+constexpr unsigned long long kDynamicTag = 1ull << 63;
+
 struct KernelParams {
-    const mb_phase* phases;
-    const unsigned long long* slots;  // device address table
+    const PhaseEntry* entries;
     Control* ctl;
+    unsigned long long* trace;  // optional [ctas][n_phases][4] global-timer stamps, or null
     unsigned long long dyn[MB_MAX_DYNAMIC];
     int n_phases;
     int n_dynamic;
@@ -43,18 +54,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
-}
-
-__device__ __forceinline__ unsigned long long slot_address(const KernelParams& p, int s) {
-    if (s < 0) return 0ull;
-    if (s < p.n_dynamic) {
-        unsigned long long a = p.dyn[0];
-#pragma unroll
-        for (int i = 1; i < MB_MAX_DYNAMIC; ++i)
-            if (s == i) a = p.dyn[i];
-        return a;
-    }
-    return __ldg(p.slots + s);
 }
 
 __device__ __forceinline__ void record_status(Control* ctl, int code, int phase, int detail) {
@@ -196,41 +195,50 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned int a0, u
 
 // ---------------------------------------------------------------------------------------
 // Counting grid barrier.  Called by `threads` threads of every CTA (named barrier `bar_id`).
-// `target` is the counter value that means "everybody arrived".  Returns false after a
-// timeout or when another CTA already recorded a fault; the caller then drains.
+// `target` is the counter value that means "everybody arrived".  Thread 0 decides for the
+// whole CTA -- go on, or drain because a wait ran out / a fault was recorded here or in
+// another CTA -- and publishes the decision through `verdict` in shared memory, so that every
+// thread of the CTA takes the same branch afterwards.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int target, int bar_id,
                                              int threads, int tid, volatile int* abort_flag,
-                                             int phase) {
+                                             volatile int* verdict, int phase) {
     named_barrier(bar_id, threads);
     if (tid == 0) {
-        __threadfence();
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ctl->barrier) : "memory");
-        const unsigned long long start = global_timer_ns();
-        unsigned int polls = 0;
-        for (;;) {
-            unsigned int seen;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
-                         : "=r"(seen)
-                         : "l"(&ctl->barrier)
+        bool go = *abort_flag == 0;
+        if (go) {
+            // release: orders every write this CTA made before the bar.sync above
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ctl->barrier)
                          : "memory");
-            if (static_cast<int>(seen - target) >= 0) break;
-            if ((++polls & 63u) == 0u) {
-                if (peek_status(ctl) != 0) {
-                    *abort_flag = 1;
-                    break;
-                }
-                if (global_timer_ns() - start > kBarrierTimeoutNs) {
-                    record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase, static_cast<int>(blockIdx.x));
-                    *abort_flag = 1;
-                    break;
+            unsigned long long start = 0;
+            unsigned int polls = 0;
+            for (;;) {
+                unsigned int seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
+                             : "=r"(seen)
+                             : "l"(&ctl->barrier)
+                             : "memory");
+                if (static_cast<int>(seen - target) >= 0) break;
+                if ((++polls & 63u) == 0u) {
+                    if (start == 0) start = global_timer_ns();
+                    if (peek_status(ctl) != 0 || *abort_flag != 0) {
+                        go = false;
+                        break;
+                    }
+                    if (global_timer_ns() - start > kBarrierTimeoutNs) {
+                        record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase,
+                                      static_cast<int>(blockIdx.x));
+                        go = false;
+                        break;
+                    }
                 }
             }
         }
-        __threadfence();
+        if (!go) *abort_flag = 1;
+        *verdict = go ? 1 : 0;
     }
     named_barrier(bar_id, threads);
-    return *abort_flag == 0;
+    return *verdict != 0;
 }
 
 }  // namespace mb

@@ -10,6 +10,7 @@ int decode_fixed_smem();
 int decode_stage_bytes();
 int decode_max_stages();
 int decode_row_pad();
+int decode_row_tile();
 cudaError_t decode_configure(int smem_bytes);
 cudaError_t decode_occupancy(int smem_bytes, int* blocks_per_sm);
 cudaError_t decode_launch(const KernelParams& params, int ctas, int smem_bytes,

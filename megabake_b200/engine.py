@@ -74,7 +74,7 @@ class BoundDecoder:
         for offset, nbytes in self.layout.zero_ranges:
             self.workspace[offset:offset + nbytes].zero_()
 
-    def _check_tensor(self, position: int, tensor: torch.Tensor) -> None:
+    def _check_tensor(self, position: int, tensor: torch.Tensor, align: int = 16) -> None:
         shape, dtype, device = self._expected[position]
         if not isinstance(tensor, torch.Tensor):
             fail("input-binding", f"argument {position} is not a tensor")
@@ -85,8 +85,8 @@ class BoundDecoder:
                  requirement="static shapes: recompile for new shapes")
         if not tensor.is_contiguous():
             fail("input-binding", f"argument {position} is not contiguous")
-        if tensor.data_ptr() % 16:
-            fail("input-binding", f"argument {position} is not 16-byte aligned")
+        if tensor.data_ptr() % align:
+            fail("input-binding", f"argument {position} is not {align}-byte aligned")
 
     def _rebind(self, args: Sequence[torch.Tensor], force: bool = False) -> None:
         changed = force
@@ -118,8 +118,8 @@ class BoundDecoder:
         p = self.program
         with self._lock:
             ids, positions = args[p.input_ids], args[p.position_ids]
-            self._check_tensor(p.input_ids, ids)
-            self._check_tensor(p.position_ids, positions)
+            self._check_tensor(p.input_ids, ids, align=8)
+            self._check_tensor(p.position_ids, positions, align=8)
             self._rebind(args)
             logits = torch.empty((p.batch, p.tokens, p.vocab), dtype=torch.bfloat16,
                                  device=self.device)

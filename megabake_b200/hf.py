@@ -27,6 +27,7 @@ import sys
 from typing import Any
 
 import torch
+from transformers.cache_utils import Cache, CacheLayerMixin
 
 from .ops import attention as _attention_op
 
@@ -116,39 +117,39 @@ def register_transformers_attention() -> str:
     return ATTENTION_IMPLEMENTATION
 
 
-def _pass_through_cache(layer_count: int, capacity: int):
-    from transformers.cache_utils import Cache, CacheLayerMixin
+class _PassThroughLayer(CacheLayerMixin):
+    """Stores nothing: the new key/value go straight to the attention call, which owns the
+    real cache."""
 
-    class PassThroughLayer(CacheLayerMixin):
-        """Stores nothing: the new key/value go straight to the attention call,
-        which owns the real cache."""
+    is_compileable = True
+    is_sliding = False
 
-        is_compileable = True
-        is_sliding = False
+    def __init__(self, capacity: int):
+        super().__init__()
+        self.capacity = capacity
+        self.is_initialized = True
 
-        def __init__(self):
-            super().__init__()
-            self.is_initialized = True
+    def lazy_initialization(self, *args, **kwargs) -> None:
+        pass
 
-        def lazy_initialization(self, *args, **kwargs) -> None:
-            pass
+    def update(self, key_states, value_states, *args, **kwargs):
+        return key_states, value_states
 
-        def update(self, key_states, value_states, *args, **kwargs):
-            return key_states, value_states
+    def get_mask_sizes(self, *args, **kwargs) -> tuple[int, int]:
+        return self.capacity, 0
 
-        def get_mask_sizes(self, *args, **kwargs) -> tuple[int, int]:
-            return capacity, 0
+    def get_seq_length(self, *args, **kwargs) -> int:
+        return 0
 
-        def get_seq_length(self, *args, **kwargs) -> int:
-            return 0
+    def get_max_cache_shape(self) -> int:
+        return self.capacity
 
-        def get_max_cache_shape(self) -> int:
-            return capacity
+    def get_max_length(self) -> int:
+        return self.capacity
 
-        def get_max_length(self) -> int:
-            return capacity
 
-    return Cache(layers=[PassThroughLayer() for _ in range(layer_count)])
+def _pass_through_cache(layer_count: int, capacity: int) -> Cache:
+    return Cache(layers=[_PassThroughLayer(capacity) for _ in range(layer_count)])
 
 
 def _text_config(model: torch.nn.Module):

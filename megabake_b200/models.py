@@ -114,17 +114,22 @@ def parameter_shapes(spec: ModelSpec) -> list[tuple[str, tuple[int, ...]]]:
 
 def fill_parameter(name: str, shape: tuple[int, ...], generator: torch.Generator,
                    norm_value: float) -> torch.Tensor:
+    device = generator.device
     if name.endswith("layernorm.weight") or name.endswith("norm.weight"):
-        return torch.full(shape, norm_value, dtype=torch.bfloat16)
-    values = torch.empty(shape, dtype=torch.float32)
+        return torch.full(shape, norm_value, dtype=torch.bfloat16, device=device)
+    values = torch.empty(shape, dtype=torch.float32, device=device)
     values.normal_(0.0, 0.02, generator=generator)
     return values.to(torch.bfloat16)
 
 
 def init_weights(spec: ModelSpec, seed: int = 0, device: str | torch.device = "cpu",
-                 ) -> dict[str, torch.Tensor]:
-    """Seeded random-init bf16 weights, generated on CPU (bit-reproducible) then moved."""
-    generator = torch.Generator().manual_seed(seed)
+                 on_device: bool = False) -> dict[str, torch.Tensor]:
+    """Seeded random-init bf16 weights.  By default they are drawn on CPU (bit-reproducible
+    everywhere, what the parity tests need) and then moved; ``on_device=True`` draws them with
+    the target device's generator instead (same distribution, seconds faster for the
+    billion-parameter benchmark shapes, not bit-equal to the CPU draw)."""
+    where = torch.device(device) if on_device else torch.device("cpu")
+    generator = torch.Generator(device=where).manual_seed(seed)
     norm_value = 0.0 if spec.family == "gemma" else 1.0
     weights = {}
     for name, shape in parameter_shapes(spec):
@@ -270,3 +275,68 @@ def build_hf_model(spec: ModelSpec, seed: int = 0, device: str | torch.device = 
                 spec.hidden**0.5, device=device).to(torch.bfloat16)
     model.config.use_cache = False
     return model.eval()
+
+
+# ---------------------------------------------------------------------------------------
+# Cache filling for long-context decode workloads (input preparation, never timed)
+# ---------------------------------------------------------------------------------------
+@torch.no_grad()
+def fill_cache_by_prefill(spec: ModelSpec, weights: dict[str, torch.Tensor],
+                          inv_freq: torch.Tensor, state: list[torch.Tensor], keys: int,
+                          seed: int = 0, chunk_rows: int = 2) -> None:
+    """Fill ``state`` with the keys (after RoPE) and values of a seeded causal prefill of ``keys``
+    uniform-random token ids per row, and set every valid length to ``keys``.
+
+    Plain library torch on the tensors' device (fused SDPA for the attention itself): this
+    prepares the benchmark's *input*, the same tensors then go to the kernel and to the CPU
+    baseline.  Rows are processed ``chunk_rows`` at a time to bound memory."""
+    device = state[0].device
+    batch = state[0].shape[0]
+    ids = torch.randint(0, spec.vocab, (batch, keys), generator=torch.Generator().manual_seed(seed))
+    positions = torch.arange(keys, device=device, dtype=torch.float32)
+    freqs = torch.outer(positions, inv_freq.to(device).float())
+    emb = torch.cat((freqs, freqs), dim=-1)
+    cos, sin = emb.cos().to(torch.bfloat16)[None, :, None], emb.sin().to(torch.bfloat16)[None, :, None]
+
+    def rope(x):
+        half = x.shape[-1] // 2
+        return x * cos + torch.cat((-x[..., half:], x[..., :half]), dim=-1) * sin
+
+    def norm(x, w):
+        wide = x.float()
+        scaled = wide * torch.rsqrt(wide.pow(2).mean(-1, keepdim=True) + spec.eps)
+        if spec.norm == "gemma":
+            return (scaled * (1.0 + w.float())).to(x.dtype)
+        return w * scaled.to(x.dtype)
+
+    lin = torch.nn.functional.linear
+    for start in range(0, batch, chunk_rows):
+        rows = slice(start, min(batch, start + chunk_rows))
+        hidden = torch.nn.functional.embedding(ids[rows].to(device), weights["model.embed_tokens.weight"])
+        if spec.embed_scale is not None:
+            hidden = hidden * torch.tensor(spec.embed_scale, dtype=hidden.dtype, device=device)
+        n = hidden.shape[0]
+        for index in range(spec.layers):
+            pre = f"model.layers.{index}."
+            x = norm(hidden, weights[pre + "input_layernorm.weight"])
+            q = lin(x, weights[pre + "self_attn.q_proj.weight"], weights.get(pre + "self_attn.q_proj.bias"))
+            k = lin(x, weights[pre + "self_attn.k_proj.weight"], weights.get(pre + "self_attn.k_proj.bias"))
+            v = lin(x, weights[pre + "self_attn.v_proj.weight"], weights.get(pre + "self_attn.v_proj.bias"))
+            q = rope(q.view(n, keys, spec.heads, spec.head_dim))
+            k = rope(k.view(n, keys, spec.kv_heads, spec.head_dim))
+            v = v.view(n, keys, spec.kv_heads, spec.head_dim)
+            state[3 * index][rows, :keys] = k
+            state[3 * index + 1][rows, :keys] = v
+            mixed = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                enable_gqa=spec.heads != spec.kv_heads)
+            mixed = mixed.transpose(1, 2).reshape(n, keys, spec.heads * spec.head_dim)
+            hidden = hidden + lin(mixed, weights[pre + "self_attn.o_proj.weight"])
+            x = norm(hidden, weights[pre + "post_attention_layernorm.weight"])
+            gate = lin(x, weights[pre + "mlp.gate_proj.weight"])
+            act = (torch.nn.functional.silu(gate) if spec.activation == "silu"
+                   else torch.nn.functional.gelu(gate, approximate="tanh"))
+            hidden = hidden + lin(act * lin(x, weights[pre + "mlp.up_proj.weight"]),
+                                  weights[pre + "mlp.down_proj.weight"])
+    for index in range(spec.layers):
+        state[3 * index + 2].fill_(keys)

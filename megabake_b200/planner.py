@@ -35,6 +35,7 @@ from .program import DecoderProgram
 DYN_INPUT_IDS, DYN_POSITION_IDS, DYN_LOGITS = 0, 1, 2
 N_DYNAMIC = 3
 CONSUMER_WARPS = 8
+EXACT_SOFTMAX_KEYS = 1024  # contexts up to here use the three-pass (reference-rounding) softmax
 MAX_GEMV_ROWS = 8
 
 
@@ -63,8 +64,9 @@ class PlanLayout:
 class PlannerOptions:
     ctas: int = 148  # CTAs the tile split is planned for (one per SM on B200)
     row_tile: int | None = None  # force the GEMV row tile (tuning sweeps)
-    max_chunks: int = 64
+    max_chunks: int = 32
     merge_slots: int | None = None
+    exact_keys: int = EXACT_SOFTMAX_KEYS
 
     @classmethod
     def from_env(cls, **overrides) -> "PlannerOptions":
@@ -107,38 +109,42 @@ class _Slots:
         return len(self.specs) - 1
 
 
+ROW_TILE = 8  # weight rows per pipeline stage (one n8 MMA tile); a consumer warp owns a block
+
+
 def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, row_pad: int,
                   forced_row_tile: int | None = None) -> tuple[int, int]:
     """(row_tile, k_chunk) of a skinny-GEMM phase.
 
-    A CTA owns ``ceil(n_total / ctas)`` consecutive weight rows and streams them in stages of
-    ``row_tile`` rows x ``k_chunk`` reduction elements (x ``nmat`` matrices) that must fit one
-    ring slot; the consumer warps not needed for rows split K.  Among row tiles 8/16/32/64 the
-    one needing the fewest stages wins (long contiguous row copies, few pipeline hand-offs);
-    ties go to the larger tile, which needs less cross-warp reduction.
+    A CTA owns ``ceil(n_total / ctas)`` consecutive weight rows and streams them as blocks of
+    8 rows; a block is cut along K into equal chunks (multiples of 32 elements, preferably of
+    64 so that staged rows stay bank-staggered) that fit one ring stage together with the
+    paired matrix.  Whole rows per copy whenever they fit: the bulk-copy engine is at its best
+    from 2 KB per copy upwards.
     """
-    rows_per_cta = max(1, math.ceil(n_total / ctas))
-
-    def max_chunk(tile: int) -> int:
-        return min(k, ((stage_bytes // (tile * nmat)) - row_pad) // 2 // 16 * 16)
-
-    def stages(tile: int) -> int:
-        return math.ceil(rows_per_cta / tile) * math.ceil(k / max_chunk(tile))
-
-    candidates = [tile for tile in (8, 16, 32, 64) if max_chunk(tile) >= 16]
-    if forced_row_tile is not None:
-        candidates = [forced_row_tile] if forced_row_tile in candidates else []
-    if not candidates:
-        fail("resource-admission", f"no GEMV row tile fits K={k} x {nmat} matrices in a stage")
-    row_tile = min(candidates, key=lambda tile: (stages(tile), -tile))
-    limit = max_chunk(row_tile)
-    chunks = math.ceil(k / limit)
-    k_chunk = min(_align(math.ceil(k / chunks), 16), limit)
-    return row_tile, k_chunk
+    del n_total, ctas, forced_row_tile
+    limit = ((stage_bytes // (ROW_TILE * nmat)) - row_pad) // 2 // 32 * 32
+    if limit < 32:
+        fail("resource-admission", f"a ring stage cannot hold 8 rows of {nmat} matrices")
+    chunks = math.ceil(k / min(limit, k))
+    k_chunk = _align(math.ceil(k / chunks), 64)
+    if k_chunk > limit:
+        k_chunk = _align(math.ceil(k / chunks), 32)
+    while k_chunk > limit:
+        chunks += 1
+        k_chunk = _align(math.ceil(k / chunks), 32)
+    return ROW_TILE, min(k_chunk, k)
 
 
-def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int) -> int:
-    return 16 * (head_dim + 32) + 4 * head_dim + 4 * (head_dim + 2) * group * (merge_slots + 2)
+def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int, exact_keys: int = 0) -> int:
+    """Shared-memory scratch of the decode attention body (mirrors the native layout)."""
+    stats = 4 * (2 * 8 * 8 + 8 * 64 + 16)
+    return (16 * (head_dim + 32) + 4 * head_dim + stats
+            + 4 * (head_dim + 2) * group * (merge_slots + 2) + 4 * group * exact_keys)
+
+
+def exact_softmax_keys(capacity: int, limit: int = EXACT_SOFTMAX_KEYS) -> int:
+    return min(_align(capacity, 16), limit)
 
 
 def _check_program(p: DecoderProgram) -> None:
@@ -155,8 +161,8 @@ def _check_program(p: DecoderProgram) -> None:
         fail("resource-admission",
              f"{p.heads} query heads over {p.kv_heads} kv heads (group size must divide, <= 8)")
     for name, value in (("hidden", p.hidden), ("intermediate", p.intermediate)):
-        if value % 16:
-            fail("resource-admission", f"{name} size {value} is not a multiple of 16")
+        if value % 32:
+            fail("resource-admission", f"{name} size {value} is not a multiple of 32")
     if p.norm not in ("llama", "gemma"):
         fail("planning", f"unknown norm kind {p.norm!r}")
     if p.activation not in ("silu", "gelu_tanh"):
@@ -170,7 +176,7 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
     stage_bytes = lib.mb_stage_bytes(rt.MODE_DECODE)
     fixed_bytes = lib.mb_fixed_smem_bytes(rt.MODE_DECODE)
     max_smem = lib.mb_max_smem_bytes()
-    row_pad = 16
+    row_pad = 64
     p = program
     B, H, D = p.batch, p.hidden, p.head_dim
     q_dim, kv_dim = p.heads * D, p.kv_heads * D
@@ -190,9 +196,10 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
     counters = slots.buffer(_align(pairs * 4, 16), "attention_arrivals", zero=True)
 
     merge_slots = options.merge_slots or CONSUMER_WARPS
-    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots) > 48 * 1024:
+    exact_keys = exact_softmax_keys(p.capacity, options.exact_keys)
+    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots, exact_keys) > 64 * 1024:
         merge_slots //= 2
-    activation = attention_scratch_bytes(D, p.group, merge_slots)
+    activation = attention_scratch_bytes(D, p.group, merge_slots, exact_keys)
 
     phases: list[rt.Phase] = []
 
@@ -230,7 +237,7 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
             if store_x >= 0:
                 phase.i[rt.GV_I_STORE_X] = 1
                 phase.slot[rt.GV_S_XSTORE] = store_x
-        activation = max(activation, B * (k + 8) * 2)
+        activation = max(activation, B * (k + 32) * 2)
         phases.append(phase)
 
     inv_freq = slots.arg(p.inv_freq, "inv_freq")
@@ -263,6 +270,7 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
         attention.i[rt.AT_I_INVFREQ_BF16] = 1 if p.inv_freq_dtype == "bf16" else 0
         attention.i[rt.AT_I_MAX_CHUNKS] = max_chunks
         attention.i[rt.AT_I_MERGE_SLOTS] = merge_slots
+        attention.i[rt.AT_I_EXACT_KEYS] = exact_keys
         attention.f[rt.AT_F_SCALE] = p.softmax_scale
         attention.f[rt.AT_F_ROPE_SCALE] = p.rope_scale
         attention.f[rt.AT_F_Q_SCALE] = float(p.q_scale or 0.0)
@@ -332,5 +340,6 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
         activation_bytes=activation,
         intervals=intervals,
         notes=[f"{len(phases)} phases in {intervals} barrier intervals",
-               f"attention: max_chunks={max_chunks} merge_slots={merge_slots}"],
+               f"attention: max_chunks={max_chunks} merge_slots={merge_slots} "
+               f"exact_keys={exact_keys}"],
     )

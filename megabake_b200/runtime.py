@@ -39,7 +39,7 @@ GV_S_W_PAIR, GV_S_RESIDUAL, GV_S_IDS, GV_S_XSTORE = 11, 12, 13, 14
 
 # MB_BODY_ATTN_DECODE field indices
 AT_I_BATCH, AT_I_HEADS, AT_I_KV_HEADS, AT_I_HEAD_DIM, AT_I_CAPACITY = 0, 1, 2, 3, 4
-AT_I_INVFREQ_BF16, AT_I_MAX_CHUNKS, AT_I_MERGE_SLOTS = 5, 6, 7
+AT_I_INVFREQ_BF16, AT_I_MAX_CHUNKS, AT_I_MERGE_SLOTS, AT_I_EXACT_KEYS = 5, 6, 7, 8
 AT_F_SCALE, AT_F_ROPE_SCALE, AT_F_Q_SCALE = 0, 1, 2
 (AT_S_Q, AT_S_K, AT_S_V, AT_S_KCACHE, AT_S_VCACHE, AT_S_LEN, AT_S_POS, AT_S_INVFREQ, AT_S_OUT,
  AT_S_PARTIAL, AT_S_COUNTER) = range(11)
@@ -110,7 +110,7 @@ LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / "libmegabake_b200.so"
 # Every symbol include/megabake_b200.h declares; the loader checks all of them.
 EXPORTS = (
     "mb_plan_create", "mb_plan_query", "mb_plan_bind", "mb_plan_launch", "mb_plan_status",
-    "mb_plan_reset", "mb_plan_destroy", "mb_strerror", "mb_status_string", "mb_last_cuda_error",
+    "mb_plan_reset", "mb_plan_set_trace", "mb_plan_destroy", "mb_strerror", "mb_status_string", "mb_last_cuda_error",
     "mb_abi_version", "mb_fixed_smem_bytes", "mb_stage_bytes", "mb_max_smem_bytes",
 )
 
@@ -150,10 +150,12 @@ def load_library(path: Path | None = None) -> ctypes.CDLL:
                                        ctypes.c_void_p]
         lib.mb_plan_status.argtypes = [plan_p, ctypes.POINTER(Status)]
         lib.mb_plan_reset.argtypes = [plan_p]
+        lib.mb_plan_set_trace.argtypes = [plan_p, ctypes.c_uint64, ctypes.c_size_t]
         lib.mb_plan_destroy.argtypes = [plan_p]
         lib.mb_plan_destroy.restype = None
         for name in ("mb_plan_create", "mb_plan_query", "mb_plan_bind", "mb_plan_launch",
-                     "mb_plan_status", "mb_plan_reset", "mb_abi_version", "mb_max_smem_bytes"):
+                     "mb_plan_status", "mb_plan_reset", "mb_plan_set_trace", "mb_abi_version",
+                     "mb_max_smem_bytes"):
             getattr(lib, name).restype = ctypes.c_int
         for name in ("mb_fixed_smem_bytes", "mb_stage_bytes"):
             getattr(lib, name).argtypes = [ctypes.c_int]
@@ -244,6 +246,12 @@ class Plan:
                 f"device status {name}: {text} (phase {status.phase}, detail {status.detail})",
             ))
         return status
+
+    def set_trace(self, device_address: int, nbytes: int) -> None:
+        """Point the kernel's per-phase timer stamps at a device buffer of
+        ``ctas * n_phases * 4`` uint64 (0 switches tracing off)."""
+        _check(self._lib, self._lib.mb_plan_set_trace(self._handle, device_address, nbytes),
+               "runtime-binding", "mb_plan_set_trace")
 
     def reset(self) -> None:
         _check(self._lib, self._lib.mb_plan_reset(self._handle), "runtime", "mb_plan_reset")

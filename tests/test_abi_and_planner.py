@@ -55,9 +55,9 @@ def test_decode_plan_tables(name, batch):
     for phase in layout.phases:
         if phase.body == rt.BODY_GEMV:
             tile, chunk, nmat = phase.i[rt.GV_I_ROW_TILE], phase.i[rt.GV_I_K_CHUNK], phase.i[rt.GV_I_NMAT]
-            assert tile in (8, 16, 32, 64) and chunk % 16 == 0 and chunk <= phase.i[rt.GV_I_K]
-            assert tile * nmat * (chunk * 2 + 16) <= stage
-            assert batch * (phase.i[rt.GV_I_K] + 8) * 2 <= layout.activation_bytes
+            assert tile == 8 and chunk % 32 == 0 and chunk <= phase.i[rt.GV_I_K]
+            assert tile * nmat * (chunk * 2 + 64) <= stage
+            assert batch * (phase.i[rt.GV_I_K] + 32) * 2 <= layout.activation_bytes
         for slot in phase.slot:
             assert -1 <= slot < len(layout.slots)
     kinds = [s.kind for s in layout.slots]
@@ -69,12 +69,16 @@ def test_decode_plan_tables(name, batch):
     assert fixed + layout.activation_bytes + 2 * stage <= lib.mb_max_smem_bytes()
 
 
-def test_geometry_prefers_few_stages():
-    # 14 rows per CTA of a 2048-wide matrix: one 16-row tile, K in whole-row copies if it fits
-    tile, chunk = planner.gemv_geometry(2048, 2048, 1, 148, 34816, 16)
-    assert tile == 16 and chunk == 1024
-    tile, chunk = planner.gemv_geometry(128256, 2048, 1, 148, 34816, 16)
-    assert tile * (chunk * 2 + 16) <= 34816
+def test_geometry_whole_rows_when_they_fit():
+    stage = rt.load_library().mb_stage_bytes(rt.MODE_DECODE)
+    # a 2048-wide matrix: 8 rows of 4 KB do not fit one stage, two equal chunks do
+    assert planner.gemv_geometry(2048, 2048, 1, 148, stage, 64) == (8, 1024)
+    # Qwen2's paired gate/up rows (K = 896) travel as whole rows
+    assert planner.gemv_geometry(4864, 896, 2, 148, stage, 64) == (8, 896)
+    for k in (576, 896, 1536, 2048, 4864, 8192, 16384):
+        for nmat in (1, 2):
+            tile, chunk = planner.gemv_geometry(4096, k, nmat, 148, stage, 64)
+            assert chunk % 32 == 0 and tile * nmat * (chunk * 2 + 64) <= stage
 
 
 def test_planner_refusals():
