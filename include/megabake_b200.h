@@ -166,9 +166,9 @@ typedef struct mb_phase {
 #define MB_AT_I_INVFREQ_BF16 5 /* 1 if the inv_freq buffer is bf16, 0 if fp32             */
 #define MB_AT_I_MAX_CHUNKS 6 /* key chunks per (batch, kv head) the workspace is sized for */
 #define MB_AT_I_MERGE_SLOTS 7 /* per-warp states that fit the shared scratch at once      */
-#define MB_AT_I_EXACT_KEYS 8 /* contexts up to this many keys (multiple of 16, 0 = never)
-                                use the three-pass softmax that rounds normalised
-                                probabilities to bf16 like the eager operator          */
+#define MB_AT_I_EXACT_KEYS 8 /* contexts up to this many keys (<= 128, 0 = never) use the
+                                softmax that rounds normalised probabilities to bf16
+                                like the eager operator                                */
 #define MB_AT_F_SCALE 0      /* head_dim ** -0.5, applied in fp32                          */
 #define MB_AT_F_ROPE_SCALE 1 /* attention_scaling multiplied into cos/sin                  */
 #define MB_AT_F_Q_SCALE 2    /* 0 or 1 = none; else q = bf16(q * this) after RoPE          */
@@ -220,8 +220,9 @@ int mb_plan_status(mb_plan* plan, mb_status* out);
 int mb_plan_reset(mb_plan* plan);
 /* Per-phase trace (no counterpart in the reference API; its MEGABAKE_PHASE_TIMER build flag,
  * src/megabake/runtime.py:22-47, is the same idea): `device_address` points at
- * ctas * n_phases * 4 uint64 the kernel fills with global-timer stamps (phase start,
- * prologue done, body done, barrier passed) on every later launch; 0 switches it off. */
+ * ctas * n_phases * 8 uint64 the kernel fills with global-timer stamps (0 phase start,
+ * 1 prologue done, 2 body done, 3 barrier passed, 4..7 body-specific) on every later
+ * launch; 0 switches it off. */
 int mb_plan_set_trace(mb_plan* plan, uint64_t device_address, size_t bytes);
 void mb_plan_destroy(mb_plan* plan);
 

@@ -71,13 +71,13 @@ struct mb_plan {
 namespace {
 
 // Shared-memory scratch the decode attention body carves from the activation region.
-long long attention_scratch_bytes(int head_dim, int group, int merge_slots, int exact_keys) {
+long long attention_scratch_bytes(int head_dim, int group, int merge_slots) {
     const long long qs = 8LL * (head_dim + 32) * 2;
+    const long long new_rows = 2LL * head_dim * 2;
     const long long cs = 4LL * head_dim;
     const long long stats = 4LL * (2 * 8 * 8 + 8 * 64 + 16);
     const long long states = 4LL * (head_dim + 2) * group * (merge_slots + 2);
-    const long long scores = 4LL * group * exact_keys;
-    return qs + cs + stats + states + scores;
+    return qs + new_rows + cs + stats + states;
 }
 
 int check_slot(const mb_plan_desc* d, int s, bool required) {
@@ -99,7 +99,9 @@ int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     if (static_cast<long long>(rt) * nmat * (kc * 2 + mb::decode_row_pad()) >
         mb::decode_stage_bytes())
         return MB_ERR_RESOURCE;
-    if (static_cast<long long>(rows) * (K + 32) * 2 > d->activation_bytes) return MB_ERR_RESOURCE;
+    // activation rows, plus one staged row of norm weights when the phase normalises
+    const long long staged_rows = rows + (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE ? 1 : 0);
+    if (staged_rows * (K + 32) * 2 > d->activation_bytes) return MB_ERR_RESOURCE;
     if (pro < MB_PRO_NONE || pro > MB_PRO_RMS_GEMMA) return MB_ERR_INVALID;
     if (epi < MB_EPI_NONE || epi > MB_EPI_GELU_TANH_MUL) return MB_ERR_INVALID;
     const bool paired_epi = epi == MB_EPI_SILU_MUL || epi == MB_EPI_GELU_TANH_MUL;
@@ -134,8 +136,8 @@ int validate_attention(const mb_plan_desc* d, const mb_phase& P) {
     if (chunks < 1 || chunks > 64) return MB_ERR_INVALID;
     if (slots < 1 || slots > 8) return MB_ERR_INVALID;
     const int exact = P.i[MB_AT_I_EXACT_KEYS];
-    if (exact < 0 || exact % 16 != 0) return MB_ERR_INVALID;
-    if (attention_scratch_bytes(D, Hq / Hkv, slots, exact) > d->activation_bytes)
+    if (exact < 0 || exact > 128) return MB_ERR_INVALID;
+    if (attention_scratch_bytes(D, Hq / Hkv, slots) > d->activation_bytes)
         return MB_ERR_RESOURCE;
     for (int s = MB_AT_S_Q; s <= MB_AT_S_COUNTER; ++s)
         if (check_slot(d, P.slot[s], true)) return MB_ERR_INVALID;
@@ -348,7 +350,7 @@ int mb_plan_status(mb_plan* plan, mb_status* out) {
 int mb_plan_set_trace(mb_plan* plan, uint64_t device_address, size_t bytes) {
     if (plan == nullptr) return MB_ERR_INVALID;
     if (device_address != 0) {
-        const size_t need = static_cast<size_t>(plan->ctas) * plan->phases.size() * 4 * sizeof(uint64_t);
+        const size_t need = static_cast<size_t>(plan->ctas) * plan->phases.size() * 8 * sizeof(uint64_t);
         if (bytes < need || (device_address & 7ull) != 0) return MB_ERR_INVALID;
     }
     plan->trace = device_address;

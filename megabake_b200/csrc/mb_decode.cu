@@ -29,13 +29,21 @@ constexpr int kRowTile = 8;          // weight rows per stage = one n8 MMA tile
 constexpr int kRowPad = 64;          // bytes added to each staged row: with row lengths that are
                                      // multiples of 128 B this makes 16-byte fragment loads of
                                      // two neighbouring rows hit disjoint banks
-constexpr int kStageBytes = 30720;   // 8 rows x 2 matrices x (896 * 2 + 64) B and change
+constexpr int kStageBytes = 34816;   // 8 rows x (2048 * 2 + 64) B plus slack: whole 4 KB rows
 constexpr int kCtlBytes = 2048;
 constexpr int kReduceBytes = 16384;  // partial sums of one reduction group of row blocks
 constexpr int kFixedBytes = kCtlBytes + kReduceBytes;
 constexpr int kBarConsumers = 1;     // named barrier id of the consumer warps
 constexpr int kFoldFloats = 8 * 64 + 16;  // attention: chunk weights + denominators
 constexpr int kEntryVectors = sizeof(PhaseEntry) / 16;
+constexpr int kTraceEvents = 8;  // stamps per phase and CTA in the optional trace buffer
+
+// Trace stamp from inside a body (events 4..7 are body-specific); thread 0 only.
+__device__ __forceinline__ void trace_stamp(const KernelParams& p, int ph, int event, int tid) {
+    if (p.trace != nullptr && tid == 0)
+        p.trace[(static_cast<size_t>(blockIdx.x) * p.n_phases + ph) * kTraceEvents + event] =
+            global_timer_ns();
+}
 
 struct SharedCtl {
     unsigned long long full[kMaxStages];
@@ -46,6 +54,7 @@ struct SharedCtl {
     volatile int verdict;            // thread 0's go / drain decision at a barrier
     float red[kConsumerWarps][8];    // per-warp partials of the activation prologue
     __align__(16) PhaseEntry entry[2];  // current / next phase record with resolved addresses
+    __align__(16) PhaseEntry producer_entry;  // the producer warp's own copy of its phase
 };
 static_assert(sizeof(SharedCtl) <= kCtlBytes, "control block too large");
 static_assert(sizeof(PhaseEntry) % 16 == 0, "phase entries are copied in 16-byte vectors");
@@ -86,8 +95,11 @@ __device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, in
     g.k_chunk = P.i[MB_GV_I_K_CHUNK];
     g.n_chunks = (g.K + g.k_chunk - 1) / g.k_chunk;
     g.pitch = g.k_chunk * 2 + kRowPad;
-    g.r0 = static_cast<int>((static_cast<long long>(cta) * g.ntotal) / ctas);
-    g.r1 = static_cast<int>((static_cast<long long>(cta + 1) * g.ntotal) / ctas);
+    // cta * ntotal stays far below 2^32 (148 CTAs, vocabularies of a few hundred thousand rows)
+    g.r0 = static_cast<int>(static_cast<unsigned int>(cta) * static_cast<unsigned int>(g.ntotal) /
+                            static_cast<unsigned int>(ctas));
+    g.r1 = static_cast<int>(static_cast<unsigned int>(cta + 1) *
+                            static_cast<unsigned int>(g.ntotal) / static_cast<unsigned int>(ctas));
     g.n_blocks = (g.r1 - g.r0 + kRowTile - 1) / kRowTile;
     return g;
 }
@@ -100,10 +112,51 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                                            int lane) {
     const int cta = blockIdx.x, ctas = gridDim.x;
     unsigned int it = 0;
+    // The producer runs phases ahead of the consumers, so it would meet every phase entry
+    // cold in DRAM and chase its fields one dependent load at a time.  Instead: pull the whole
+    // table into L2 once, and per phase fetch the entry with one coalesced 16-byte load per
+    // lane (the next entry's load is already in flight while this one is worked on).
+    {
+        const char* table = reinterpret_cast<const char*>(p.entries);
+        const size_t bytes = sizeof(PhaseEntry) * static_cast<size_t>(p.n_phases);
+        for (size_t off = static_cast<size_t>(lane) * 128; off < bytes; off += 32 * 128)
+            prefetch_l2(table + off);
+    }
+    PhaseEntry* mine = &sc->producer_entry;
+    uint4 next_vector = make_uint4(0u, 0u, 0u, 0u);
+    if (lane < kEntryVectors)
+        next_vector = __ldg(reinterpret_cast<const uint4*>(p.entries) + lane);
     for (int ph = 0; ph < p.n_phases; ++ph) {
-        const PhaseEntry* E = p.entries + ph;
+        __syncwarp();  // everybody is done with the previous entry
+        if (lane < kEntryVectors) {
+            reinterpret_cast<uint4*>(mine)[lane] = next_vector;
+            if (ph + 1 < p.n_phases)
+                next_vector = __ldg(reinterpret_cast<const uint4*>(p.entries + ph + 1) + lane);
+        }
+        __syncwarp();
+        const PhaseEntry* E = mine;
+        if (E->rec.body == MB_BODY_ATTN_DECODE) {
+            // the few scalars the attention body starts from: pull them into L2 ahead of time
+            if (lane == 0) prefetch_l2(reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_LEN)));
+            if (lane == 1) prefetch_l2(reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_POS)));
+            if (lane == 2)
+                prefetch_l2(reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_INVFREQ)));
+            continue;
+        }
         if (E->rec.body != MB_BODY_GEMV) continue;
         const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
+        if (E->rec.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
+            // norm weights are read by every CTA right after the barrier: have them in L2
+            const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+            for (int line = lane; line * 128 < g.K * 2; line += 32) prefetch_l2(nw + line * 128);
+        }
+        if (E->rec.slot[MB_GV_S_BIAS0] >= 0 && g.nseg == 1 && lane < 8) {
+            // this CTA's slice of a single-segment bias (a few lines at most per 8 lanes)
+            const char* bias = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_BIAS0));
+            const int stop = g.r1 * 2;  // byte range [r0 * 2, r1 * 2) of the vector
+            for (int off = (g.r0 * 2 / 128 + lane) * 128; off < stop; off += 8 * 128)
+                prefetch_l2(bias + off);
+        }
         const char* w0 = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_W0));
         const char* w1 = g.nseg > 1
                              ? reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_W0 + 1))
@@ -225,12 +278,53 @@ __device__ __forceinline__ uint4 normalise_vector(uint4 x, uint4 w, float inv, i
     return make_uint4(xv[0], xv[1], xv[2], xv[3]);
 }
 
-// NV = 16-byte vectors of a row each thread keeps in registers between the two passes of the
-// norm (K <= NV * 2048); NV == 0 re-reads shared memory instead (any K).
-template <int NV>
-__device__ __forceinline__ void activation_prologue(const KernelParams& p, const PhaseEntry* E,
-                                                 int ph, SharedCtl* sc, __nv_bfloat16* xs,
-                                                 int tid) {
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)),
+                 "l"(src_gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// One global round trip: every activation row (and the norm weight vector, staged as one
+// extra row) is copied global -> shared with 16-byte asynchronous copies that are all in
+// flight together; scaling, sums of squares and the normalisation then run out of shared
+// memory.  Kept out of line and free of unrolled row loops: the phase loop must stay small
+// enough for the instruction cache.
+// Part 1 (activation_issue) only starts the copies; part 2 (activation_finish) waits for them
+// and normalises.  The GEMV body runs its own address arithmetic and epilogue-operand loads
+// between the two, under the latency of the copies.
+__device__ __noinline__ void activation_issue(const KernelParams& p, const PhaseEntry* E, int ph,
+                                              __nv_bfloat16* xs, int tid) {
+    const mb_phase& P = E->rec;
+    const int rows = P.i[MB_GV_I_ROWS];
+    const int K = P.i[MB_GV_I_K];
+    const int xpitch = K + 32;
+    const bool gather = P.i[MB_GV_I_GATHER] != 0;
+    const char* xbase = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X));
+    const long long* ids =
+        gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
+    const int vec_per_row = K / 8;  // 16-byte vectors
+    bool bad_token = false;
+    for (int r = 0; r < rows; ++r) {
+        const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
+        __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
+        for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+            cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
+    }
+    if (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
+        __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
+        const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+        for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+            cp_async16(wrow + v * 8, nw + static_cast<size_t>(v) * 16);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
+}
+
+__device__ __noinline__ void activation_finish(const KernelParams& p, const PhaseEntry* E,
+                                               SharedCtl* sc, __nv_bfloat16* xs, int tid) {
     const mb_phase& P = E->rec;
     const int rows = P.i[MB_GV_I_ROWS];
     const int K = P.i[MB_GV_I_K];
@@ -239,152 +333,51 @@ __device__ __forceinline__ void activation_prologue(const KernelParams& p, const
     const bool gather = P.i[MB_GV_I_GATHER] != 0;
     const float embed_scale = P.f[MB_GV_F_EMBED_SCALE];
     const bool scaled = gather && embed_scale != 0.f;
-    const char* xbase = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X));
-    const long long* ids =
-        gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
+    const bool store_x = gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0;
     const int warp = tid >> 5, lane = tid & 31;
     const int vec_per_row = K / 8;  // 16-byte vectors
-    bool bad_token = false;
-    constexpr int NVR = NV > 0 ? NV : 1;
+    __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-    // norm weights first: their latency overlaps the activation loads
-    uint4 wreg[NVR];
-    if (NV > 0 && pro != MB_PRO_NONE) {
-        const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int v = tid + j * kConsumerThreads;
-            wreg[j] = v < vec_per_row ? __ldg(reinterpret_cast<const uint4*>(nw) + v)
-                                      : make_uint4(0u, 0u, 0u, 0u);
-        }
-    }
-
-    float ss[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) ss[r] = 0.f;
-
-    if (NV > 0) {
-        // ---- register path: one global round trip, two CTA barriers
-        uint4 xreg[8][NVR];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r >= rows) break;
-            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int v = tid + j * kConsumerThreads;
-                xreg[r][j] = v < vec_per_row ? ld_cg_u4(src + static_cast<size_t>(v) * 16)
-                                             : make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r >= rows) break;
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                if (scaled) xreg[r][j] = scale_vector(xreg[r][j], embed_scale);
-                ss[r] += sum_squares(xreg[r][j]);
-            }
-        }
-        if (gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0) {
-            // the residual stream needs the un-normalised rows in global memory
-            char* store = reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE));
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r >= rows) break;
-#pragma unroll
-                for (int j = 0; j < NV; ++j) {
-                    const int v = tid + j * kConsumerThreads;
-                    if (v < vec_per_row)
-                        *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) =
-                            xreg[r][j];
+    if (scaled || store_x || pro != MB_PRO_NONE) {
+        // every thread works on the vectors it copied itself, so no barrier is needed yet
+        char* store = store_x ? reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE))
+                              : nullptr;
+        for (int r = 0; r < rows; ++r) {
+            float ss = 0.f;
+            for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
+                uint4* cell = reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
+                uint4 raw = *cell;
+                if (scaled) {
+                    raw = scale_vector(raw, embed_scale);
+                    *cell = raw;
                 }
+                ss += sum_squares(raw);
+                if (store_x)  // the residual stream needs the un-normalised rows
+                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) = raw;
+            }
+            if (pro != MB_PRO_NONE) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) sc->red[warp][r] = ss;
             }
         }
-        float inv[8];
         if (pro != MB_PRO_NONE) {
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                float v = ss[r];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) sc->red[warp][r] = v;
-            }
             named_barrier(kBarConsumers, kConsumerThreads);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
+            for (int r = 0; r < rows; ++r) {
                 float total = 0.f;
 #pragma unroll
                 for (int w = 0; w < kConsumerWarps; ++w) total += sc->red[w][r];
-                inv[r] = 1.0f / sqrtf(total / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r >= rows) break;
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int v = tid + j * kConsumerThreads;
-                if (v < vec_per_row) {
-                    const uint4 value = pro != MB_PRO_NONE
-                                            ? normalise_vector(xreg[r][j], wreg[j], inv[r], pro)
-                                            : xreg[r][j];
-                    *reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8) = value;
-                }
-            }
-        }
-    } else {
-        // ---- shared-memory path for long rows
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r >= rows) break;
-            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
-            for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-                uint4 raw = ld_cg_u4(src + static_cast<size_t>(v) * 16);
-                if (scaled) raw = scale_vector(raw, embed_scale);
-                ss[r] += sum_squares(raw);
-                *reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8) = raw;
-            }
-        }
-        if (gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0) {
-            char* store = reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE));
-            for (int r = 0; r < rows; ++r)
-                for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) =
-                        *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
-        }
-        if (pro != MB_PRO_NONE) {
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                float v = ss[r];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) sc->red[warp][r] = v;
-            }
-            named_barrier(kBarConsumers, kConsumerThreads);
-            float inv[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                float total = 0.f;
-#pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) total += sc->red[w][r];
-                inv[r] = 1.0f / sqrtf(total / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
-            }
-            const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
-            // each thread rescales the vectors it wrote itself
-            for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
-                const uint4 w = __ldg(reinterpret_cast<const uint4*>(nw) + v);
-#pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    if (r >= rows) break;
+                const float inv = 1.0f / sqrtf(total / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
+                for (int v = tid; v < vec_per_row; v += kConsumerThreads) {
                     uint4* cell =
                         reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * xpitch + v * 8);
-                    *cell = normalise_vector(*cell, w, inv[r], pro);
+                    *cell = normalise_vector(*cell, *reinterpret_cast<const uint4*>(wrow + v * 8),
+                                             inv, pro);
                 }
             }
         }
     }
-    if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
     named_barrier(kBarConsumers, kConsumerThreads);
 }
 
@@ -480,13 +473,14 @@ __device__ __forceinline__ void store_output(const EpilogueCtx& e, const OutputC
 // lets warp w add up the eight partials of block w and run that block's epilogue.  That is one
 // barrier pair per 8 (paired: 4) row blocks instead of a reduction per stage.
 template <int NMAT>
-__device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseEntry* E, int ph,
+__device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntry* E, int ph,
                                              SharedCtl* sc, const __nv_bfloat16* xs, float* red,
                                              const char* ring, unsigned int& it, int tid) {
     constexpr int NB = NMAT == 1 ? 8 : 4;  // row blocks per reduction group
     constexpr int PV = 2 * NMAT;           // partial values per lane and block
     const int cta = blockIdx.x, ctas = gridDim.x;
     const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
+    trace_stamp(p, ph, 7, tid);
     const int warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tq = lane & 3;
     const int xpitch = g.K + 32;
@@ -508,6 +502,7 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
                      : nullptr;
 
     bool dead = false;
+    bool staged = false;  // activation rows not yet waited for / normalised
     for (int group0 = 0; group0 < g.n_blocks; group0 += NB) {
         const int nb = min(NB, g.n_blocks - group0);
         // The block this warp finalises, this lane's two output cells in it (token gid, rows
@@ -527,13 +522,17 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
             op1 = fetch_epilogue(e, cell1);
         }
 
+        if (!staged) {
+            activation_finish(p, E, sc, const_cast<__nv_bfloat16*>(xs), tid);
+            staged = true;
+        }
         for (int b = 0; b < nb; ++b) {
             // two accumulator sets per matrix keep the MMA dependency chains short
-            float acc[NMAT][2][4];
+            float acc[NMAT][4][4];
 #pragma unroll
             for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
+                for (int u = 0; u < 4; ++u)
 #pragma unroll
                     for (int q = 0; q < 4; ++q) acc[m][u][q] = 0.f;
 
@@ -541,6 +540,7 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
                 const int stage = it % p.stages;
                 const unsigned int parity = (it / p.stages) & 1u;
                 ++it;
+                if (group0 == 0 && b == 0 && c == 0) trace_stamp(p, ph, 6, tid);
                 // A wait that runs out must not make this warp leave: the others would hang
                 // at the next CTA barrier.  It records the fault, and every warp then falls
                 // through the remaining loops without waiting or computing.
@@ -553,19 +553,30 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
                     dead = true;
                     continue;
                 }
+                if (group0 == 0 && b == 0 && c == 0) trace_stamp(p, ph, 4, tid);
                 const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
                 const char* wrow = ring + static_cast<size_t>(stage) * kStageBytes +
                                    static_cast<size_t>(gid) * g.pitch + 16 * tq;
                 const __nv_bfloat16* xk = xrow + c * g.k_chunk;
                 const int groups = kc >> 5;  // 32 reduction elements per group
-                for (int grp = warp; grp < groups; grp += kConsumerWarps) {
+                // groups are taken two at a time onto four independent accumulator sets: the
+                // tensor-core latency of this MMA shape is long, the dependent chain must be short
+                for (int grp = warp; grp < groups; grp += 2 * kConsumerWarps) {
+                    const int grp2 = grp + kConsumerWarps;
+                    const bool second = grp2 < groups;
                     const uint4 a = *reinterpret_cast<const uint4*>(xk + 32 * grp);
+                    const uint4 a2 = second ? *reinterpret_cast<const uint4*>(xk + 32 * grp2)
+                                            : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) {
-                        const uint4 w = *reinterpret_cast<const uint4*>(
-                            wrow + static_cast<size_t>(m) * kRowTile * g.pitch + 64 * grp);
+                        const char* wm = wrow + static_cast<size_t>(m) * kRowTile * g.pitch;
+                        const uint4 w = *reinterpret_cast<const uint4*>(wm + 64 * grp);
+                        const uint4 w2 = second ? *reinterpret_cast<const uint4*>(wm + 64 * grp2)
+                                                : make_uint4(0u, 0u, 0u, 0u);
                         mma_bf16_16816(acc[m][0], a.x, 0u, a.y, 0u, w.x, w.y);
                         mma_bf16_16816(acc[m][1], a.z, 0u, a.w, 0u, w.z, w.w);
+                        mma_bf16_16816(acc[m][2], a2.x, 0u, a2.y, 0u, w2.x, w2.y);
+                        mma_bf16_16816(acc[m][3], a2.z, 0u, a2.w, 0u, w2.z, w2.w);
                     }
                 }
                 __syncwarp();
@@ -574,10 +585,11 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
             float* cell = red + (static_cast<size_t>(b * kConsumerWarps + warp) * 32 + lane) * PV;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
-                cell[2 * m] = acc[m][0][0] + acc[m][1][0];
-                cell[2 * m + 1] = acc[m][0][1] + acc[m][1][1];
+                cell[2 * m] = (acc[m][0][0] + acc[m][1][0]) + (acc[m][2][0] + acc[m][3][0]);
+                cell[2 * m + 1] = (acc[m][0][1] + acc[m][1][1]) + (acc[m][2][1] + acc[m][3][1]);
             }
         }
+        if (group0 == 0) trace_stamp(p, ph, 5, tid);
         named_barrier(kBarConsumers, kConsumerThreads);
         if (warp < nb && !dead) {
             float total[PV];
@@ -595,6 +607,7 @@ __device__ __forceinline__ bool gemv_consume(const KernelParams& p, const PhaseE
         }
         if (group0 + NB < g.n_blocks) named_barrier(kBarConsumers, kConsumerThreads);
     }
+    if (!staged) activation_finish(p, E, sc, const_cast<__nv_bfloat16*>(xs), tid);  // no rows here
     return !dead && !sc->abort_flag;
 }
 
@@ -635,37 +648,41 @@ __device__ __forceinline__ int choose_chunks(int pairs, int nblocks, int ctas, i
 
 // Shared scratch of the attention body (carved from the activation region):
 //   qs       [8][D + 32] bf16   rotated query rows of one kv-head group
+//   kn, vn   [D] bf16 each      the new (rotated) key row and the new value row
 //   cs       [D] fp32           cos (first half) and sin (second half), already bf16-rounded
 //   wstat    [2][8 warps][8] fp32   per-warp row maxima / row sums of the exact mode
-//   fold     [8][64] + [8] fp32     chunk weights and denominators of the cross-CTA fold
+//   fold     [8][64] + [16] fp32    chunk weights and denominators of the cross-CTA fold
 //   merge    [merge_slots][group][D + 2] fp32   per-warp (max, sum, values) states
 //   running  [2][group][D + 2] fp32             CTA state, ping-pong over merge rounds
-//   scores   [group][exact_keys] fp32           score rows of the exact mode
 //
 // Two softmax modes.  The reference normalises the probabilities in fp32 and rounds them to
 // bf16 *before* the value product (ops/attention.py:82-84).
-//   exact  (one CTA owns all keys of a (row, kv head) and they fit `exact_keys`): three
-//          passes over the CTA's score rows in shared memory -- row max, exp and row sum,
-//          then bf16(exp / sum) feeds the value product -- which reproduces that rounding.
-//   split  (long contexts): online softmax per warp with unnormalised bf16 probabilities,
+//   exact  (contexts of at most `exact_keys` <= 128 keys: one CTA per (row, kv head), one
+//          16-key block per warp, scores stay in registers): row max and row sum are
+//          exchanged through shared memory, then bf16(exp / sum) feeds the value product --
+//          the reference's rounding.
+//   split  (longer contexts): online softmax per warp with unnormalised bf16 probabilities,
 //          states merged across warps and, through global partials, across CTAs by the last
-//          chunk to arrive.  With thousands of keys the rounding of single probabilities
+//          chunk to arrive.  With hundreds of keys the rounding of single probabilities
 //          averages out far below one bf16 ulp of the result.
-template <int D>
-__device__ __forceinline__ bool attention_decode(const KernelParams& p, const PhaseEntry* E, int ph,
-                                              SharedCtl* sc, char* scratch, int tid) {
-    const mb_phase* P = &E->rec;
+// The new key/value row is appended to the cache in global memory and, for this launch's own
+// arithmetic, taken from shared memory, so nothing waits on that store.
+template <int D, bool EXACT>
+__device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEntry* E, int L,
+                                            SharedCtl* sc, char* scratch, int tid) {
     constexpr int QP = D + 32;  // bf16 pitch of the rotated query rows
     constexpr int DC = D / 32;  // 32-element chunks of the head dimension (QK^T)
     constexpr int DB = D / 64;  // 64-element blocks of the head dimension (PV)
     constexpr int SW = D + 2;   // floats per head state: max, sum, D values
+    constexpr bool kEarlyKeys = D <= 64;    // first / next key tile requested ahead of use
+    constexpr bool kEarlyValues = D <= 64;  // same for the value tile
+    const mb_phase* P = &E->rec;
     const int B = P->i[MB_AT_I_BATCH];
     const int Hq = P->i[MB_AT_I_HEADS];
     const int Hkv = P->i[MB_AT_I_KV_HEADS];
     const int cap = P->i[MB_AT_I_CAPACITY];
     const int max_chunks = P->i[MB_AT_I_MAX_CHUNKS];
     const int merge_slots = P->i[MB_AT_I_MERGE_SLOTS];
-    const int exact_keys = P->i[MB_AT_I_EXACT_KEYS];
     const int group = Hq / Hkv;  // query heads per kv head, <= 8
     const float scale = P->f[MB_AT_F_SCALE];
     const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
@@ -680,32 +697,19 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
         reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_K));
     const unsigned short* vbuf =
         reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_V));
-    unsigned short* kcache =
-        reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_KCACHE));
-    unsigned short* vcache =
-        reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_VCACHE));
-    const int* lenp = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
-    const long long* pos =
-        reinterpret_cast<const long long*>(entry_address(p, E, MB_AT_S_POS));
+    unsigned short* kcache = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_KCACHE));
+    unsigned short* vcache = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_VCACHE));
+    const long long* pos = reinterpret_cast<const long long*>(entry_address(p, E, MB_AT_S_POS));
     const void* invf = reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_INVFREQ));
     const bool invf_bf16 = P->i[MB_AT_I_INVFREQ_BF16] != 0;
     unsigned short* out = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_OUT));
     float* partial = reinterpret_cast<float*>(entry_address(p, E, MB_AT_S_PARTIAL));
     int* counter = reinterpret_cast<int*>(entry_address(p, E, MB_AT_S_COUNTER));
 
-    const int L = __ldcg(lenp);
-    if (L < 0 || L + 1 > cap) {
-        if (tid == 0) {
-            record_status(p.ctl, MB_ST_KV_OVERFLOW, ph, L);
-            sc->abort_flag = 1;
-        }
-        named_barrier(kBarConsumers, kConsumerThreads);
-        return false;
-    }
     const int nkeys = L + 1;
     const int nblocks = (nkeys + 15) >> 4;
     const int pairs = B * Hkv;
-    const bool exact = nkeys <= exact_keys;
+    constexpr bool exact = EXACT;  // contexts of at most 128 keys: nblocks <= 8
     int nc = 1;
     if (!exact) {
         if (warp == 0) {
@@ -718,58 +722,125 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
     const int items = pairs * nc;
 
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(scratch);
-    float* cs = reinterpret_cast<float*>(scratch + 8 * QP * 2);
-    float* wstat = cs + D;                      // [2][kConsumerWarps][8]
-    float* fold = wstat + 2 * kConsumerWarps * 8;  // [8][64] chunk weights + [8] denominators
+    __nv_bfloat16* kn = qs + 8 * QP;
+    __nv_bfloat16* vn = kn + D;
+    float* cs = reinterpret_cast<float*>(vn + D);
+    float* wstat = cs + D;                         // [2][kConsumerWarps][8]
+    float* fold = wstat + 2 * kConsumerWarps * 8;  // [8][64] chunk weights + denominators
     float* merge = fold + kFoldFloats;
     float* running = merge + static_cast<size_t>(merge_slots) * group * SW;
-    float* srow = running + 2 * static_cast<size_t>(group) * SW;  // [group][exact_keys]
-    const size_t key_stride = static_cast<size_t>(Hkv) * D;        // elements between keys
+    const size_t key_stride = static_cast<size_t>(Hkv) * D;  // elements between keys
 
     for (int item = cta; item < items; item += ctas) {
         const int pair = item / nc, chunk = item - pair * nc;
         const int b = pair / Hkv, h = pair - b * Hkv;
         const int blk0 = static_cast<int>((static_cast<long long>(chunk) * nblocks) / nc);
         const int blk1 = static_cast<int>((static_cast<long long>(chunk + 1) * nblocks) / nc);
+        const unsigned short* kc0 = kcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
+        const unsigned short* vc0 = vcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
 
-        // ---- prologue: cos/sin, RoPE of the group's query heads, append of the new key/value
+        // Register tiles of one 16-key block.  kt[j][i]: key kb + 8j + gid, dims 32i + 8tq..+7.
+        // vt[x][q]: key kb + {2tq, 2tq+1, 2tq+8, 2tq+9}[q], dims 64x + 8gid..+7.  Only keys
+        // already in the cache (< L) come from global memory; the new key (== L) is patched in
+        // from shared memory and later keys are zeros (their probabilities are zero too).
+        auto load_keys = [&](int blk, uint4 (&kt)[2][DC]) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = (blk << 4) + 8 * j + gid;
+                const bool ok = key < L;
+                const unsigned short* kp = kc0 + static_cast<size_t>(ok ? key : 0) * key_stride;
+#pragma unroll
+                for (int i = 0; i < DC; ++i)
+                    kt[j][i] = ok ? *reinterpret_cast<const uint4*>(kp + 32 * i + 8 * tq)
+                                  : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        auto load_values = [&](int blk, uint4 (&vt)[DB][4]) {
+            const int k0 = (blk << 4) + 2 * tq;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int key = k0 + (q & 1) + ((q >> 1) << 3);
+                const bool ok = key < L;
+                const unsigned short* vp =
+                    vc0 + static_cast<size_t>(ok ? key : 0) * key_stride + 8 * gid;
+#pragma unroll
+                for (int x = 0; x < DB; ++x)
+                    vt[x][q] = ok ? *reinterpret_cast<const uint4*>(vp + 64 * x)
+                                  : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        auto patch_new_row = [&](int blk, uint4 (&kt)[2][DC], uint4 (&vt)[DB][4]) {
+            if ((L >> 4) != blk) return;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                if ((blk << 4) + 8 * j + gid == L) {
+#pragma unroll
+                    for (int i = 0; i < DC; ++i)
+                        kt[j][i] = *reinterpret_cast<const uint4*>(kn + 32 * i + 8 * tq);
+                }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if ((blk << 4) + 2 * tq + (q & 1) + ((q >> 1) << 3) == L) {
+#pragma unroll
+                    for (int x = 0; x < DB; ++x)
+                        vt[x][q] = *reinterpret_cast<const uint4*>(vn + 64 * x + 8 * gid);
+                }
+        };
+
+        // ---- request the first tiles before anything else: they only depend on L
+        uint4 kt[2][DC];
+        uint4 vt[DB][4];
+        const int first = blk0 + warp;
+        if (first < blk1) {
+            if (kEarlyKeys) load_keys(first, kt);
+            if (kEarlyValues) load_values(first, vt);
+        }
+
+        // ---- cos/sin, RoPE of the group's query heads and of the new key, new value row
         if (tid < D / 2) {
             const float f =
                 invf_bf16 ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(invf)[tid])
                           : reinterpret_cast<const float*>(invf)[tid];
             const float angle = static_cast<float>(pos[b]) * f;
-            cs[tid] = bf16_round(cosf(angle) * rope_scale);
-            cs[D / 2 + tid] = bf16_round(sinf(angle) * rope_scale);
+            float sn, cn;
+            sincosf(angle, &sn, &cn);
+            cs[tid] = bf16_round(cn * rope_scale);
+            cs[D / 2 + tid] = bf16_round(sn * rope_scale);
         }
         named_barrier(kBarConsumers, kConsumerThreads);
-        for (int e = tid; e < group * (D / 2); e += kConsumerThreads) {
+        const bool appends = chunk == nc - 1;  // the chunk that holds key L stores the new row
+        const size_t new_row = ((static_cast<size_t>(b) * cap + L) * Hkv + h) * D;
+        for (int e = tid; e < (group + 1) * (D / 2); e += kConsumerThreads) {
             const int gq = e / (D / 2), i = e - gq * (D / 2);
-            const unsigned short* qrow = qbuf + (static_cast<size_t>(b) * Hq + h * group + gq) * D;
-            const float x1 = bf16_bits_to_float(ld_cg_u16(qrow + i));
-            const float x2 = bf16_bits_to_float(ld_cg_u16(qrow + i + D / 2));
+            const bool is_key = gq == group;
+            const unsigned short* row =
+                is_key ? kbuf + (static_cast<size_t>(b) * Hkv + h) * D
+                       : qbuf + (static_cast<size_t>(b) * Hq + h * group + gq) * D;
+            const float x1 = bf16_bits_to_float(ld_cg_u16(row + i));
+            const float x2 = bf16_bits_to_float(ld_cg_u16(row + i + D / 2));
             const float c = cs[i], sn = cs[D / 2 + i];
             float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * sn));
             float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * sn));
-            if (q_scale != 0.f && q_scale != 1.f) {
-                r1 = bf16_round(r1 * q_scale);
-                r2 = bf16_round(r2 * q_scale);
+            if (is_key) {
+                kn[i] = __float2bfloat16_rn(r1);
+                kn[i + D / 2] = __float2bfloat16_rn(r2);
+                if (appends) {
+                    kcache[new_row + i] = float_to_bf16_bits(r1);
+                    kcache[new_row + i + D / 2] = float_to_bf16_bits(r2);
+                }
+            } else {
+                if (q_scale != 0.f && q_scale != 1.f) {
+                    r1 = bf16_round(r1 * q_scale);
+                    r2 = bf16_round(r2 * q_scale);
+                }
+                qs[gq * QP + i] = __float2bfloat16_rn(r1);
+                qs[gq * QP + i + D / 2] = __float2bfloat16_rn(r2);
             }
-            qs[gq * QP + i] = __float2bfloat16_rn(r1);
-            qs[gq * QP + i + D / 2] = __float2bfloat16_rn(r2);
         }
-        if (chunk == nc - 1) {
-            const size_t row = ((static_cast<size_t>(b) * cap + L) * Hkv + h) * D;
-            const unsigned short* krow = kbuf + (static_cast<size_t>(b) * Hkv + h) * D;
-            const unsigned short* vrow = vbuf + (static_cast<size_t>(b) * Hkv + h) * D;
-            for (int i = tid; i < D / 2; i += kConsumerThreads) {
-                const float x1 = bf16_bits_to_float(ld_cg_u16(krow + i));
-                const float x2 = bf16_bits_to_float(ld_cg_u16(krow + i + D / 2));
-                const float c = cs[i], sn = cs[D / 2 + i];
-                kcache[row + i] = float_to_bf16_bits(bf16_round(x1 * c) + bf16_round(-x2 * sn));
-                kcache[row + i + D / 2] =
-                    float_to_bf16_bits(bf16_round(x2 * c) + bf16_round(x1 * sn));
-            }
-            for (int i = tid; i < D; i += kConsumerThreads) vcache[row + i] = ld_cg_u16(vrow + i);
+        for (int i = tid; i < D; i += kConsumerThreads) {
+            const unsigned short v = ld_cg_u16(vbuf + (static_cast<size_t>(b) * Hkv + h) * D + i);
+            reinterpret_cast<unsigned short*>(vn)[i] = v;
+            if (appends) vcache[new_row + i] = v;
         }
         named_barrier(kBarConsumers, kConsumerThreads);
 
@@ -793,49 +864,17 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
 #pragma unroll
                 for (int q = 0; q < 4; ++q) acc[x][mt][q] = 0.f;
 
-        const unsigned short* kc0 = kcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
-        const unsigned short* vc0 = vcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
-
-        // Register tiles of one 16-key block.  kt[j][i]: key kb + 8j + gid, dims 32i + 8tq..+7.
-        // vt[x][q]: key kb + {2tq, 2tq+1, 2tq+8, 2tq+9}[q], dims 64x + 8gid..+7.
-        // Keys past the valid length load as zeros (their probabilities are zero as well).
-        auto load_keys = [&](int blk, uint4 (&kt)[2][DC]) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int key = (blk << 4) + 8 * j + gid;
-                const bool ok = key < nkeys;
-                const unsigned short* kp = kc0 + static_cast<size_t>(ok ? key : 0) * key_stride;
-#pragma unroll
-                for (int i = 0; i < DC; ++i)
-                    kt[j][i] = ok ? *reinterpret_cast<const uint4*>(kp + 32 * i + 8 * tq)
-                                  : make_uint4(0u, 0u, 0u, 0u);
-            }
-        };
-        auto load_values = [&](int blk, uint4 (&vt)[DB][4]) {
-            const int k0 = (blk << 4) + 2 * tq;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int key = k0 + (q & 1) + ((q >> 1) << 3);
-                const bool ok = key < nkeys;
-                const unsigned short* vp =
-                    vc0 + static_cast<size_t>(ok ? key : 0) * key_stride + 8 * gid;
-#pragma unroll
-                for (int x = 0; x < DB; ++x)
-                    vt[x][q] = ok ? *reinterpret_cast<const uint4*>(vp + 64 * x)
-                                  : make_uint4(0u, 0u, 0u, 0u);
-            }
-        };
         // scores of one block: sv[2j + q] <-> head gid, key kb + 8j + 2tq + q; bf16-rounded
         // product, scale applied in fp32, keys past the valid length masked
-        auto block_scores = [&](int kb, const uint4 (&kt)[2][DC], float (&sv)[4]) {
+        auto block_scores = [&](int kb, const uint4 (&kt_)[2][DC], float (&sv)[4]) {
             float frag[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 frag[j][0] = frag[j][1] = frag[j][2] = frag[j][3] = 0.f;
 #pragma unroll
                 for (int i = 0; i < DC; ++i) {
-                    mma_bf16_16816(frag[j], qf[i].x, 0u, qf[i].y, 0u, kt[j][i].x, kt[j][i].y);
-                    mma_bf16_16816(frag[j], qf[i].z, 0u, qf[i].w, 0u, kt[j][i].z, kt[j][i].w);
+                    mma_bf16_16816(frag[j], qf[i].x, 0u, qf[i].y, 0u, kt_[j][i].x, kt_[j][i].y);
+                    mma_bf16_16816(frag[j], qf[i].z, 0u, qf[i].w, 0u, kt_[j][i].z, kt_[j][i].w);
                 }
             }
 #pragma unroll
@@ -843,19 +882,19 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                     const int key = kb + 8 * j + 2 * tq + q;
-                    const float s = bf16_round(frag[j][q]) * scale;
-                    sv[2 * j + q] = key < nkeys ? s : -INFINITY;
+                    const float sval = bf16_round(frag[j][q]) * scale;
+                    sv[2 * j + q] = key < nkeys ? sval : -INFINITY;
                 }
         };
         // acc += V^T P^T for one block; pb0/pb1 = probabilities of keys (2tq, 2tq+1) and
         // (8+2tq, 9+2tq) of head gid, packed bf16
-        auto block_values = [&](const uint4 (&vt)[DB][4], unsigned int pb0, unsigned int pb1) {
+        auto block_values = [&](const uint4 (&vt_)[DB][4], unsigned int pb0, unsigned int pb1) {
 #pragma unroll
             for (int x = 0; x < DB; ++x) {
-                const unsigned int ra[4] = {vt[x][0].x, vt[x][0].y, vt[x][0].z, vt[x][0].w};
-                const unsigned int rb[4] = {vt[x][1].x, vt[x][1].y, vt[x][1].z, vt[x][1].w};
-                const unsigned int rc[4] = {vt[x][2].x, vt[x][2].y, vt[x][2].z, vt[x][2].w};
-                const unsigned int rd[4] = {vt[x][3].x, vt[x][3].y, vt[x][3].z, vt[x][3].w};
+                const unsigned int ra[4] = {vt_[x][0].x, vt_[x][0].y, vt_[x][0].z, vt_[x][0].w};
+                const unsigned int rb[4] = {vt_[x][1].x, vt_[x][1].y, vt_[x][1].z, vt_[x][1].w};
+                const unsigned int rc[4] = {vt_[x][2].x, vt_[x][2].y, vt_[x][2].z, vt_[x][2].w};
+                const unsigned int rd[4] = {vt_[x][3].x, vt_[x][3].y, vt_[x][3].z, vt_[x][3].w};
 #pragma unroll
                 for (int mt = 0; mt < 4; ++mt) {
                     const unsigned int a0 = __byte_perm(ra[mt], rb[mt], 0x5410u);
@@ -867,25 +906,17 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
             }
         };
 
-        uint4 kt[2][DC];
-        uint4 vt[DB][4];
         if (exact) {
-            // ---- pass 1: scores into shared rows, row maxima
-            float rmax = -INFINITY;
-            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
-                const int kb = blk << 4;
-                float sv[4];
-                load_keys(blk, kt);
-                block_scores(kb, kt, sv);
-                if (gid < group) {
-                    float* row = srow + static_cast<size_t>(gid) * exact_keys + kb + 2 * tq;
-                    row[0] = sv[0];
-                    row[1] = sv[1];
-                    row[8] = sv[2];
-                    row[9] = sv[3];
-                }
-                rmax = fmaxf(rmax, fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3])));
+            // one block per warp at most; warps without a block still join the two exchanges
+            const bool has = first < blk1;
+            float sv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (has) {
+                if (!kEarlyKeys) load_keys(first, kt);
+                if (!kEarlyValues) load_values(first, vt);
+                patch_new_row(first, kt, vt);
+                block_scores(first << 4, kt, sv);
             }
+            float rmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
             rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
             rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
             if (tq == 0) wstat[warp * 8 + gid] = rmax;
@@ -893,64 +924,38 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
             float row_max = -INFINITY;
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) row_max = fmaxf(row_max, wstat[w * 8 + gid]);
-            // ---- pass 2: exponentials in place, row sums
-            float rsum = 0.f;
-            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
-                if (gid < group) {
-                    float* row = srow + static_cast<size_t>(gid) * exact_keys + (blk << 4) + 2 * tq;
-                    const float e0 = expf(row[0] - row_max), e1 = expf(row[1] - row_max);
-                    const float e2 = expf(row[8] - row_max), e3 = expf(row[9] - row_max);
-                    row[0] = e0;
-                    row[1] = e1;
-                    row[8] = e2;
-                    row[9] = e3;
-                    rsum += (e0 + e1) + (e2 + e3);
-                }
-            }
+            float ev[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) ev[q] = expf(sv[q] - row_max);  // 0 for masked keys
+            float rsum = (ev[0] + ev[1]) + (ev[2] + ev[3]);
             rsum += __shfl_xor_sync(0xffffffffu, rsum, 1);
             rsum += __shfl_xor_sync(0xffffffffu, rsum, 2);
             if (tq == 0) wstat[(kConsumerWarps + warp) * 8 + gid] = rsum;
             named_barrier(kBarConsumers, kConsumerThreads);
             float row_sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) row_sum += wstat[(kConsumerWarps + w) * 8 + gid];
-            // ---- pass 3: normalised probabilities rounded to bf16, value product
-            for (int blk = blk0 + warp; blk < blk1; blk += kConsumerWarps) {
-                load_values(blk, vt);
-                float pv[4] = {0.f, 0.f, 0.f, 0.f};
-                if (gid < group) {
-                    const float* row =
-                        srow + static_cast<size_t>(gid) * exact_keys + (blk << 4) + 2 * tq;
-                    pv[0] = row[0] / row_sum;
-                    pv[1] = row[1] / row_sum;
-                    pv[2] = row[8] / row_sum;
-                    pv[3] = row[9] / row_sum;
-                }
-                block_values(vt, pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]));
-            }
+            for (int w = 0; w < kConsumerWarps; ++w)
+                row_sum += wstat[(kConsumerWarps + w) * 8 + gid];
+            if (has)  // normalised probabilities rounded to bf16, as the eager operator does
+                block_values(vt, pack_bf16(ev[0] / row_sum, ev[1] / row_sum),
+                             pack_bf16(ev[2] / row_sum, ev[3] / row_sum));
             // already normalised: merge as plain sums (max 0, total weight 1)
             m_run = 0.f;
             l_run = (warp == 0 && tq == 0) ? 1.f : 0.f;
         } else {
-            // ---- online softmax, one 16-key block per iteration, next block prefetched
-            constexpr bool kPrefetchKeys = D <= 128;
-            constexpr bool kPrefetchValues = D <= 64;
+            // online softmax, one 16-key block per iteration, the next block requested ahead
             uint4 kt_next[2][DC];
             uint4 vt_next[DB][4];
-            int blk = blk0 + warp;
-            if (blk < blk1) {
-                if (kPrefetchKeys) load_keys(blk, kt);
-                if (kPrefetchValues) load_values(blk, vt);
-            }
-            for (; blk < blk1; blk += kConsumerWarps) {
+            for (int blk = first; blk < blk1; blk += kConsumerWarps) {
                 const int kb = blk << 4;
                 const int following = blk + kConsumerWarps;
-                if (!kPrefetchKeys) load_keys(blk, kt);
-                if (!kPrefetchValues) load_values(blk, vt);
+                if (!kEarlyKeys) load_keys(blk, kt);
+                if (!kEarlyValues) load_values(blk, vt);
                 if (following < blk1) {
-                    if (kPrefetchKeys) load_keys(following, kt_next);
-                    if (kPrefetchValues) load_values(following, vt_next);
+                    if (kEarlyKeys) load_keys(following, kt_next);
+                    if (kEarlyValues) load_values(following, vt_next);
                 }
+                patch_new_row(blk, kt, vt);
                 float sv[4];
                 block_scores(kb, kt, sv);
                 float bmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
@@ -977,13 +982,13 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
                     }
                 block_values(vt, pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]));
                 if (following < blk1) {
-                    if (kPrefetchKeys) {
+                    if (kEarlyKeys) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
 #pragma unroll
                             for (int i = 0; i < DC; ++i) kt[j][i] = kt_next[j][i];
                     }
-                    if (kPrefetchValues) {
+                    if (kEarlyValues) {
 #pragma unroll
                         for (int x = 0; x < DB; ++x)
 #pragma unroll
@@ -998,9 +1003,9 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
         // ---- merge the warp states into one CTA state, `merge_slots` warps per round
         const int rounds = (kConsumerWarps + merge_slots - 1) / merge_slots;
         for (int round = 0; round < rounds; ++round) {
-            const int first = round * merge_slots;
-            if (warp >= first && warp < first + merge_slots) {
-                float* base = merge + static_cast<size_t>(warp - first) * group * SW;
+            const int lead = round * merge_slots;
+            if (warp >= lead && warp < lead + merge_slots) {
+                float* base = merge + static_cast<size_t>(warp - lead) * group * SW;
                 if (tq == 0 && gid < group) {
                     base[gid * SW] = m_run;
                     base[gid * SW + 1] = l_run;
@@ -1022,7 +1027,7 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
                     }
             }
             named_barrier(kBarConsumers, kConsumerThreads);
-            const int live = min(merge_slots, kConsumerWarps - first);
+            const int live = min(merge_slots, kConsumerWarps - lead);
             const float* prev = running + static_cast<size_t>((round & 1) ^ 1) * group * SW;
             float* next = running + static_cast<size_t>(round & 1) * group * SW;
             for (int e = tid; e < group * SW; e += kConsumerThreads) {
@@ -1067,12 +1072,12 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
             named_barrier(kBarConsumers, kConsumerThreads);
             if (sc->bcast[1] == nc - 1) {
                 // Last chunk of this (row, kv head) to arrive folds all chunks, in chunk order.
-                // Step 1: the (max, sum) pairs of all chunks -> per-chunk weights in shared
-                // memory.
+                // Step 1: (max, sum) of every chunk into shared memory, all loads in flight
+                // together, then the per-chunk weights and the denominator.
                 const float* all = partial + static_cast<size_t>(pair) * max_chunks * group * SW;
-                float* weight = fold;            // [group][nc] chunk maxima, then weights
-                float* denom = fold + 8 * 64;    // [group]
-                float* sums = merge;             // [group][nc] chunk sums (merge slots are free)
+                float* weight = fold;          // [group][nc] chunk maxima, then weights
+                float* denom = fold + 8 * 64;  // [group]
+                float* sums = merge;           // [group][nc] chunk sums (merge slots are free)
                 for (int e = tid; e < group * nc; e += kConsumerThreads) {
                     const int gq = e / nc, c = e - gq * nc;
                     const float* st = all + (static_cast<size_t>(c) * group + gq) * SW;
@@ -1109,27 +1114,28 @@ __device__ __forceinline__ bool attention_decode(const KernelParams& p, const Ph
         }
         named_barrier(kBarConsumers, kConsumerThreads);  // scratch is reused by the next item
     }
-    return true;
 }
 
-// The common shapes (head_dim 64, rows up to 2048 elements) are inlined into the phase loop;
-// the rare variants are kept out of line so that their register needs do not shape the
-// allocation of the common path.
-__device__ __noinline__ bool attention_decode_128(const KernelParams& p, const PhaseEntry* E,
-                                                  int ph, SharedCtl* sc, char* scratch, int tid) {
-    return attention_decode<128>(p, E, ph, sc, scratch, tid);
-}
-__device__ __noinline__ bool attention_decode_256(const KernelParams& p, const PhaseEntry* E,
-                                                  int ph, SharedCtl* sc, char* scratch, int tid) {
-    return attention_decode<256>(p, E, ph, sc, scratch, tid);
-}
-__device__ __noinline__ void activation_prologue_wide(const KernelParams& p, const PhaseEntry* E,
-                                                      int ph, SharedCtl* sc, __nv_bfloat16* xs,
-                                                      int tid) {
-    if (E->rec.i[MB_GV_I_K] <= 16 * kConsumerThreads)
-        activation_prologue<2>(p, E, ph, sc, xs, tid);
+// Reads the valid length once, refuses a full cache (every thread of every CTA sees the same
+// length, so all of them take the same branch) and picks the softmax mode.  The two modes are
+// separate functions so that a launch only ever executes one of them: instruction-cache
+// footprint matters more here than code sharing.
+template <int D>
+__device__ __forceinline__ void attention_decode(const KernelParams& p, const PhaseEntry* E,
+                                                 int ph, SharedCtl* sc, char* scratch, int tid) {
+    const int* lenp = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
+    const int L = __ldcg(lenp);
+    if (L < 0 || L + 1 > E->rec.i[MB_AT_I_CAPACITY]) {
+        if (tid == 0) {
+            record_status(p.ctl, MB_ST_KV_OVERFLOW, ph, L);
+            sc->abort_flag = 1;
+        }
+        return;
+    }
+    if (L + 1 <= E->rec.i[MB_AT_I_EXACT_KEYS])
+        attention_body<D, true>(p, E, L, sc, scratch, tid);
     else
-        activation_prologue<0>(p, E, ph, sc, xs, tid);
+        attention_body<D, false>(p, E, L, sc, scratch, tid);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1188,7 +1194,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         // closing grid barrier (3).
         auto stamp = [&](int ph, int event) {
             if (p.trace != nullptr && tid == 0)
-                p.trace[(static_cast<size_t>(blockIdx.x) * p.n_phases + ph) * 4 + event] =
+                p.trace[(static_cast<size_t>(blockIdx.x) * p.n_phases + ph) * kTraceEvents + event] =
                     global_timer_ns();
         };
         for (int ph = 0; ph < p.n_phases && ok; ++ph) {
@@ -1203,11 +1209,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
                     break;
                 case MB_BODY_GEMV: {
                     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(act);
-                    const int K = E->rec.i[MB_GV_I_K];
-                    if (K <= 8 * kConsumerThreads)
-                        activation_prologue<1>(p, E, ph, sc, xs, tid);
-                    else
-                        activation_prologue_wide(p, E, ph, sc, xs, tid);
+                    activation_issue(p, E, ph, xs, tid);
                     stamp(ph, 1);
                     if (E->rec.i[MB_GV_I_NMAT] == 2)
                         gemv_consume<2>(p, E, ph, sc, xs, red, ring, it, tid);
@@ -1220,9 +1222,9 @@ decode_kernel(const __grid_constant__ KernelParams p) {
                     if (D == 64)
                         attention_decode<64>(p, E, ph, sc, act, tid);
                     else if (D == 128)
-                        attention_decode_128(p, E, ph, sc, act, tid);
+                        attention_decode<128>(p, E, ph, sc, act, tid);
                     else
-                        attention_decode_256(p, E, ph, sc, act, tid);
+                        attention_decode<256>(p, E, ph, sc, act, tid);
                     break;
                 }
                 default:

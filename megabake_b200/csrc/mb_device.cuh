@@ -171,6 +171,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
     }
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // 1-D bulk async copy global -> shared, completion counted in bytes on an mbarrier.
 // Source, destination and size must be multiples of 16 bytes.
 __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem,

@@ -15,6 +15,7 @@ import torch
 
 from . import runtime as rt
 
+EVENTS = 8  # stamps per phase and CTA (0..3 common, 4..7 body-specific)
 BODY_NAMES = {rt.BODY_GEMV: "gemv", rt.BODY_ATTN_DECODE: "attention", rt.BODY_NOP: "nop"}
 
 
@@ -32,10 +33,10 @@ class PhaseTiming:
 
 def capture(decoder, launch, launches: int = 3) -> torch.Tensor:
     """Run ``launch()`` ``launches`` times with tracing on; returns the stamps of the last
-    one as an int64 tensor ``[ctas, phases, 4]`` (nanoseconds)."""
+    one as an int64 tensor ``[ctas, phases, 8]`` (nanoseconds)."""
     plan = decoder.plan
     phases = len(decoder.layout.phases)
-    buffer = torch.zeros(plan.ctas * phases * 4, dtype=torch.int64, device=decoder.device)
+    buffer = torch.zeros(plan.ctas * phases * EVENTS, dtype=torch.int64, device=decoder.device)
     plan.set_trace(buffer.data_ptr(), buffer.numel() * 8)
     try:
         for _ in range(launches):
@@ -43,7 +44,7 @@ def capture(decoder, launch, launches: int = 3) -> torch.Tensor:
         torch.cuda.synchronize(decoder.device)
     finally:
         plan.set_trace(0, 0)
-    return buffer.view(plan.ctas, phases, 4).cpu()
+    return buffer.view(plan.ctas, phases, EVENTS).cpu()
 
 
 def summarise(stamps: torch.Tensor, layout) -> list[PhaseTiming]:

@@ -35,7 +35,7 @@ from .program import DecoderProgram
 DYN_INPUT_IDS, DYN_POSITION_IDS, DYN_LOGITS = 0, 1, 2
 N_DYNAMIC = 3
 CONSUMER_WARPS = 8
-EXACT_SOFTMAX_KEYS = 1024  # contexts up to here use the three-pass (reference-rounding) softmax
+EXACT_SOFTMAX_KEYS = 128  # contexts up to here use the reference-rounding softmax (one CTA)
 MAX_GEMV_ROWS = 8
 
 
@@ -136,15 +136,15 @@ def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, 
     return ROW_TILE, min(k_chunk, k)
 
 
-def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int, exact_keys: int = 0) -> int:
+def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int) -> int:
     """Shared-memory scratch of the decode attention body (mirrors the native layout)."""
     stats = 4 * (2 * 8 * 8 + 8 * 64 + 16)
-    return (16 * (head_dim + 32) + 4 * head_dim + stats
-            + 4 * (head_dim + 2) * group * (merge_slots + 2) + 4 * group * exact_keys)
+    return (16 * (head_dim + 32) + 4 * head_dim + 4 * head_dim + stats
+            + 4 * (head_dim + 2) * group * (merge_slots + 2))
 
 
 def exact_softmax_keys(capacity: int, limit: int = EXACT_SOFTMAX_KEYS) -> int:
-    return min(_align(capacity, 16), limit)
+    return min(capacity, limit, 128)
 
 
 def _check_program(p: DecoderProgram) -> None:
@@ -197,9 +197,9 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
 
     merge_slots = options.merge_slots or CONSUMER_WARPS
     exact_keys = exact_softmax_keys(p.capacity, options.exact_keys)
-    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots, exact_keys) > 64 * 1024:
+    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots) > 48 * 1024:
         merge_slots //= 2
-    activation = attention_scratch_bytes(D, p.group, merge_slots, exact_keys)
+    activation = attention_scratch_bytes(D, p.group, merge_slots)
 
     phases: list[rt.Phase] = []
 
@@ -237,7 +237,8 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
             if store_x >= 0:
                 phase.i[rt.GV_I_STORE_X] = 1
                 phase.slot[rt.GV_S_XSTORE] = store_x
-        activation = max(activation, B * (k + 32) * 2)
+        staged_rows = B + (1 if prologue != rt.PRO_NONE else 0)  # + the norm weight row
+        activation = max(activation, staged_rows * (k + 32) * 2)
         phases.append(phase)
 
     inv_freq = slots.arg(p.inv_freq, "inv_freq")

@@ -70,6 +70,7 @@ class DecoderProgram:
     lm_head_weight: int
     layers: tuple[LayerBinding, ...] = field(default_factory=tuple)
     lm_head_bias: int | None = None
+    embed_scale_arg: int | None = None  # graph input holding the embedding scale (read at bind)
     causal: bool = True  # prefill mask kind
 
     @property

@@ -249,7 +249,7 @@ class Plan:
 
     def set_trace(self, device_address: int, nbytes: int) -> None:
         """Point the kernel's per-phase timer stamps at a device buffer of
-        ``ctas * n_phases * 4`` uint64 (0 switches tracing off)."""
+        ``ctas * n_phases * 8`` uint64 (0 switches tracing off)."""
         _check(self._lib, self._lib.mb_plan_set_trace(self._handle, device_address, nbytes),
                "runtime-binding", "mb_plan_set_trace")
 

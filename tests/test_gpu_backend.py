@@ -1,0 +1,125 @@
+"""The drop-in path on the GPU: ``torch.compile(wrapper, backend=make_backend(mode="decode"))``
+captures, recognises, plans and launches the megakernel; results against the CPU oracle and
+against the same module run eagerly on the GPU.  Reads like the reference's
+``tests/gpu/test_table_gemm.py:65-120`` (compiled vs eager, logits and KV state) and
+``:226-270`` (CUDA-graphed decode)."""
+
+import threading
+
+import pytest
+import torch
+
+from megabake_b200 import DecodeStep, StatefulDecoder, graphed, make_backend, models
+from megabake_b200.engine import BoundDecoder
+from oracle import decoder_oracle as oracle
+from oracle.adapters import oracle_config, oracle_weights
+from tests.helpers import LOGIT_COSINE, LOGIT_MAX_ABS, cosine, greedy_pick_matches, logits_close, max_abs
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(name, kind, batch, capacity, seed=2):
+    spec = models.get_spec(name)
+    weights = models.init_weights(spec, seed)
+    model = models.build_hf_model(spec, seed, device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    wrapper = (DecodeStep(model, capacity) if kind == "decode_step"
+               else StatefulDecoder(model, capacity)).eval()
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    return spec, wrapper, cfg, ow
+
+
+@pytest.mark.parametrize("name,kind,batch", [
+    ("tiny-llama", "stateful", 2), ("tiny-llama", "decode_step", 1), ("tiny-qwen2", "stateful", 4),
+    ("tiny-gemma", "decode_step", 2), ("tiny-mha", "stateful", 8),
+])
+def test_compiled_decode_matches_oracle(name, kind, batch):
+    capacity, calls = 12, 6
+    spec, wrapper, cfg, ow = _setup(name, kind, batch, capacity)
+    backend = make_backend(mode="decode")
+    torch._dynamo.reset()
+    step = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    state = wrapper.make_state(batch, device="cuda")
+    ref_state = oracle.make_state(cfg, batch, capacity)
+    generator = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for call in range(calls):
+            ids = torch.randint(0, spec.vocab, (batch, 1), generator=generator)
+            pos = torch.full((batch, 1), call, dtype=torch.int64)
+            ref = oracle.decode_step(cfg, ow, ids, pos, ref_state)
+            got = step(ids.cuda(), pos.cuda(), *state)
+            torch.cuda.synchronize()
+            assert got.shape == ref.shape and got.dtype == torch.bfloat16
+            assert logits_close(got, ref)[0], (call, max_abs(got, ref))
+            assert cosine(got, ref) >= LOGIT_COSINE
+            assert greedy_pick_matches(got[:, -1], ref[:, -1])[0]
+    decoder = backend.megabake_last_callable
+    assert isinstance(decoder, BoundDecoder) and decoder.launches == calls  # one launch per call
+    decoder.check()
+    assert backend.megabake_last_compiled is not None
+    for index in range(spec.layers):
+        assert int(state[3 * index + 2]) == calls
+        assert max_abs(state[3 * index][:, :calls], ref_state[3 * index][:, :calls]) <= 6e-2
+        assert torch.equal(state[3 * index][:, calls:].cpu(), ref_state[3 * index][:, calls:])
+
+
+def test_graphed_decode_replays():
+    batch, capacity = 2, 16
+    spec, wrapper, cfg, ow = _setup("tiny-llama", "stateful", batch, capacity)
+    backend = make_backend(mode="decode")
+    torch._dynamo.reset()
+    step = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    state = wrapper.make_state(batch, device="cuda")
+    ids = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+    pos = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+    with torch.no_grad():
+        call = graphed(step, ids, pos, *state)
+    assert all(int(t) == 0 for t in state[2::3])  # warm-up and capture left the state untouched
+    ref_state = oracle.make_state(cfg, batch, capacity)
+    generator = torch.Generator().manual_seed(9)
+    for index in range(5):
+        token = torch.randint(0, spec.vocab, (batch, 1), generator=generator)
+        position = torch.full((batch, 1), index, dtype=torch.int64)
+        ref = oracle.decode_step(cfg, ow, token, position, ref_state)
+        ids.copy_(token)
+        pos.copy_(position)
+        got = call(ids, pos, *state)
+        torch.cuda.synchronize()
+        assert logits_close(got, ref)[0], max_abs(got, ref)
+        assert greedy_pick_matches(got[:, -1], ref[:, -1])[0]
+    assert all(int(t) == 5 for t in state[2::3])
+
+
+def test_two_threads_share_one_compiled_callable():
+    """Calls are serialised per bound callable; both threads must get right answers
+    (reference ``tests/gpu/test_task29_transformer_block.py:118-124``)."""
+    batch, capacity = 1, 64
+    spec, wrapper, cfg, ow = _setup("tiny-llama", "stateful", batch, capacity)
+    backend = make_backend(mode="decode")
+    torch._dynamo.reset()
+    step = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    state = wrapper.make_state(batch, device="cuda")
+    ids = torch.full((batch, 1), 7, dtype=torch.int64, device="cuda")
+    with torch.no_grad():
+        step(ids, torch.zeros(batch, 1, dtype=torch.int64, device="cuda"), *state)  # compile
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker():
+        try:
+            with torch.no_grad():
+                for _ in range(10):
+                    length = int(state[2])
+                    step(ids, torch.full((batch, 1), length, dtype=torch.int64, device="cuda"), *state)
+                    torch.cuda.synchronize()
+        except Exception as error:  # noqa: BLE001
+            errors.append(error)
+
+    threads = [threading.Thread(target=worker) for _ in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert int(state[2]) == 21  # every call appended exactly one key
+    backend.megabake_last_callable.check()
