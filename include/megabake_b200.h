@@ -143,6 +143,8 @@ typedef struct mb_phase {
 #define MB_GV_I_GATHER 11  /* 1: activation rows are gathered from an embedding table     */
 #define MB_GV_I_VOCAB 12   /* rows of that table (range check)                            */
 #define MB_GV_I_STORE_X 13 /* 1: CTA 0 also stores the un-normalised rows at S_XSTORE     */
+#define MB_GV_I_SPLIT_Q 14 /* filled by mb_plan_create: output rows per CTA (floor) ...      */
+#define MB_GV_I_SPLIT_R 15 /* ... and how many leading CTAs take one row more               */
 /* floats */
 #define MB_GV_F_EPS 0
 #define MB_GV_F_EMBED_SCALE 1 /* 0 = none; else gathered rows are bf16(row * scale)       */

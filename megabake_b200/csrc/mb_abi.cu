@@ -245,6 +245,14 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     plan->device = desc->device;
     plan->mode = desc->mode;
     plan->phases.assign(desc->phases, desc->phases + desc->n_phases);
+    for (mb_phase& P : plan->phases) {
+        if (P.body != MB_BODY_GEMV) continue;
+        // balanced split of the output rows over the CTAs, so the kernel needs no division
+        int total = 0;
+        for (int s = 0; s < P.i[MB_GV_I_NSEG]; ++s) total += P.i[MB_GV_I_N0 + s];
+        P.i[MB_GV_I_SPLIT_Q] = total / ctas;
+        P.i[MB_GV_I_SPLIT_R] = total % ctas;
+    }
     plan->slots.assign(desc->n_slots, 0ull);
     plan->n_dynamic = desc->n_dynamic;
     plan->activation_bytes = desc->activation_bytes;

@@ -59,9 +59,15 @@ struct SharedCtl {
 static_assert(sizeof(SharedCtl) <= kCtlBytes, "control block too large");
 static_assert(sizeof(PhaseEntry) % 16 == 0, "phase entries are copied in 16-byte vectors");
 
-__device__ __forceinline__ unsigned long long entry_address(const KernelParams& p,
+// Entries reach the bodies with per-launch (dynamic) slots already replaced by their addresses
+// (patch_dynamic below), so reading an address is one shared-memory load.
+__device__ __forceinline__ unsigned long long entry_address(const KernelParams&,
                                                             const PhaseEntry* e, int j) {
-    const unsigned long long v = e->addr[j];
+    return e->addr[j];
+}
+
+__device__ __forceinline__ unsigned long long resolve_dynamic(const KernelParams& p,
+                                                              unsigned long long v) {
     if (v >> 63) {  // dynamic slot: the address comes with the launch
         const int s = static_cast<int>(v & 0xffu);
         unsigned long long a = p.dyn[0];
@@ -71,6 +77,11 @@ __device__ __forceinline__ unsigned long long entry_address(const KernelParams& 
         return a;
     }
     return v;
+}
+
+// One thread per slot rewrites the tagged slots of an entry that sits in shared memory.
+__device__ __forceinline__ void patch_dynamic(const KernelParams& p, PhaseEntry* e, int lane) {
+    if (lane < MB_PHASE_SLOTS) e->addr[lane] = resolve_dynamic(p, e->addr[lane]);
 }
 
 // Geometry of one GEMV phase for one CTA; producer and consumers derive it identically.
@@ -93,13 +104,13 @@ __device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, in
     g.n[2] = g.nseg > 2 ? P.i[MB_GV_I_N0 + 2] : 0;
     g.ntotal = g.n[0] + g.n[1] + g.n[2];
     g.k_chunk = P.i[MB_GV_I_K_CHUNK];
-    g.n_chunks = (g.K + g.k_chunk - 1) / g.k_chunk;
+    g.n_chunks = (g.K + g.k_chunk - 1) / g.k_chunk;  // small operands: cheap
     g.pitch = g.k_chunk * 2 + kRowPad;
-    // cta * ntotal stays far below 2^32 (148 CTAs, vocabularies of a few hundred thousand rows)
-    g.r0 = static_cast<int>(static_cast<unsigned int>(cta) * static_cast<unsigned int>(g.ntotal) /
-                            static_cast<unsigned int>(ctas));
-    g.r1 = static_cast<int>(static_cast<unsigned int>(cta + 1) *
-                            static_cast<unsigned int>(g.ntotal) / static_cast<unsigned int>(ctas));
+    // balanced split precomputed by the host: the first `rem` CTAs own one row more
+    const int q = P.i[MB_GV_I_SPLIT_Q], rem = P.i[MB_GV_I_SPLIT_R];
+    (void)ctas;
+    g.r0 = cta * q + min(cta, rem);
+    g.r1 = g.r0 + q + (cta < rem ? 1 : 0);
     g.n_blocks = (g.r1 - g.r0 + kRowTile - 1) / kRowTile;
     return g;
 }
@@ -133,6 +144,8 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
             if (ph + 1 < p.n_phases)
                 next_vector = __ldg(reinterpret_cast<const uint4*>(p.entries + ph + 1) + lane);
         }
+        __syncwarp();
+        patch_dynamic(p, mine, lane);
         __syncwarp();
         const PhaseEntry* E = mine;
         if (E->rec.body == MB_BODY_ATTN_DECODE) {
@@ -627,7 +640,9 @@ __device__ __forceinline__ int choose_chunks(int pairs, int nblocks, int ctas, i
             const int waves = (pairs * nc + ctas - 1) / ctas;
             const int blocks = (nblocks + nc - 1) / nc;
             const int rounds = (blocks + kConsumerWarps - 1) / kConsumerWarps;
-            const int cost = waves * (rounds + 3);
+            // per wave: block rounds + fixed prologue/merge; plus the last arriver's fold, whose
+            // dependent batches of L2 loads grow with the chunk count
+            const int cost = 4 * waves * (rounds + 3) + nc;
             if (cost < best_cost) {
                 best_cost = cost;
                 best_nc = nc;
@@ -669,42 +684,27 @@ __device__ __forceinline__ int choose_chunks(int pairs, int nblocks, int ctas, i
 // arithmetic, taken from shared memory, so nothing waits on that store.
 template <int D, bool EXACT>
 __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEntry* E, int L,
-                                            SharedCtl* sc, char* scratch, int tid) {
+                                            int ph, SharedCtl* sc, char* scratch, int tid) {
     constexpr int QP = D + 32;  // bf16 pitch of the rotated query rows
     constexpr int DC = D / 32;  // 32-element chunks of the head dimension (QK^T)
     constexpr int DB = D / 64;  // 64-element blocks of the head dimension (PV)
     constexpr int SW = D + 2;   // floats per head state: max, sum, D values
-    constexpr bool kEarlyKeys = D <= 64;    // first / next key tile requested ahead of use
-    constexpr bool kEarlyValues = D <= 64;  // same for the value tile
+    constexpr bool kEarlyKeys = false;      // register prefetch spills at 168 registers: off
+    constexpr bool kEarlyValues = false;    // same for the value tile
     const mb_phase* P = &E->rec;
     const int B = P->i[MB_AT_I_BATCH];
     const int Hq = P->i[MB_AT_I_HEADS];
     const int Hkv = P->i[MB_AT_I_KV_HEADS];
-    const int cap = P->i[MB_AT_I_CAPACITY];
-    const int max_chunks = P->i[MB_AT_I_MAX_CHUNKS];
     const int merge_slots = P->i[MB_AT_I_MERGE_SLOTS];
     const int group = Hq / Hkv;  // query heads per kv head, <= 8
     const float scale = P->f[MB_AT_F_SCALE];
-    const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
-    const float q_scale = P->f[MB_AT_F_Q_SCALE];
     const int warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tq = lane & 3;
     const int cta = blockIdx.x, ctas = gridDim.x;
 
-    const unsigned short* qbuf =
-        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_Q));
-    const unsigned short* kbuf =
-        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_K));
-    const unsigned short* vbuf =
-        reinterpret_cast<const unsigned short*>(entry_address(p, E, MB_AT_S_V));
-    unsigned short* kcache = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_KCACHE));
-    unsigned short* vcache = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_VCACHE));
-    const long long* pos = reinterpret_cast<const long long*>(entry_address(p, E, MB_AT_S_POS));
-    const void* invf = reinterpret_cast<const void*>(entry_address(p, E, MB_AT_S_INVFREQ));
-    const bool invf_bf16 = P->i[MB_AT_I_INVFREQ_BF16] != 0;
-    unsigned short* out = reinterpret_cast<unsigned short*>(entry_address(p, E, MB_AT_S_OUT));
-    float* partial = reinterpret_cast<float*>(entry_address(p, E, MB_AT_S_PARTIAL));
-    int* counter = reinterpret_cast<int*>(entry_address(p, E, MB_AT_S_COUNTER));
+    // Addresses and rarely used scalars are read from the phase entry (shared memory) where
+    // they are needed instead of being kept in registers across the key loop.
+    auto slot = [&](int j) { return entry_address(p, E, j); };
 
     const int nkeys = L + 1;
     const int nblocks = (nkeys + 15) >> 4;
@@ -713,7 +713,7 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     int nc = 1;
     if (!exact) {
         if (warp == 0) {
-            const int nc_pick = choose_chunks(pairs, nblocks, ctas, max_chunks, lane);
+            const int nc_pick = choose_chunks(pairs, nblocks, ctas, P->i[MB_AT_I_MAX_CHUNKS], lane);
             if (lane == 0) sc->bcast[0] = nc_pick;
         }
         named_barrier(kBarConsumers, kConsumerThreads);
@@ -734,10 +734,17 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     for (int item = cta; item < items; item += ctas) {
         const int pair = item / nc, chunk = item - pair * nc;
         const int b = pair / Hkv, h = pair - b * Hkv;
-        const int blk0 = static_cast<int>((static_cast<long long>(chunk) * nblocks) / nc);
-        const int blk1 = static_cast<int>((static_cast<long long>(chunk + 1) * nblocks) / nc);
-        const unsigned short* kc0 = kcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
-        const unsigned short* vc0 = vcache + (static_cast<size_t>(b) * cap * Hkv + h) * D;
+        // chunk * nblocks stays far below 2^32: 32-bit division is enough
+        const int blk0 = static_cast<int>(static_cast<unsigned>(chunk) * static_cast<unsigned>(nblocks) /
+                                          static_cast<unsigned>(nc));
+        const int blk1 = static_cast<int>(static_cast<unsigned>(chunk + 1) *
+                                          static_cast<unsigned>(nblocks) / static_cast<unsigned>(nc));
+        const size_t cache_row0 =
+            (static_cast<size_t>(b) * P->i[MB_AT_I_CAPACITY] * Hkv + h) * D;  // (b, key 0, h)
+        const unsigned short* kc0 =
+            reinterpret_cast<const unsigned short*>(slot(MB_AT_S_KCACHE)) + cache_row0;
+        const unsigned short* vc0 =
+            reinterpret_cast<const unsigned short*>(slot(MB_AT_S_VCACHE)) + cache_row0;
 
         // Register tiles of one 16-key block.  kt[j][i]: key kb + 8j + gid, dims 32i + 8tq..+7.
         // vt[x][q]: key kb + {2tq, 2tq+1, 2tq+8, 2tq+9}[q], dims 64x + 8gid..+7.  Only keys
@@ -787,7 +794,45 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 }
         };
 
-        // ---- request the first tiles before anything else: they only depend on L
+        // ---- prologue in one memory round trip.  The raw query rows, the new key row and the
+        // new value row go global -> shared with asynchronous 16-byte copies (no registers are
+        // held across the trigonometry below); cos/sin are computed meanwhile; the first K/V
+        // tiles are requested right after, so they fly during the barrier and the rotation.
+        constexpr int kRowVectors = D / 8;  // 16-byte vectors per head row
+        for (int v = tid; v < (group + 2) * kRowVectors; v += kConsumerThreads) {
+            const int row = v / kRowVectors, part = v - row * kRowVectors;
+            const unsigned short* src;
+            __nv_bfloat16* dst;
+            if (row < group) {
+                src = reinterpret_cast<const unsigned short*>(slot(MB_AT_S_Q)) +
+                      (static_cast<size_t>(b) * Hq + h * group + row) * D;
+                dst = qs + row * QP;
+            } else if (row == group) {
+                src = reinterpret_cast<const unsigned short*>(slot(MB_AT_S_K)) +
+                      (static_cast<size_t>(b) * Hkv + h) * D;
+                dst = kn;
+            } else {
+                src = reinterpret_cast<const unsigned short*>(slot(MB_AT_S_V)) +
+                      (static_cast<size_t>(b) * Hkv + h) * D;
+                dst = vn;
+            }
+            cp_async16(dst + part * 8, src + part * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (tid < D / 2) {
+            const void* invf = reinterpret_cast<const void*>(slot(MB_AT_S_INVFREQ));
+            const float f =
+                P->i[MB_AT_I_INVFREQ_BF16] != 0
+                    ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(invf)[tid])
+                    : reinterpret_cast<const float*>(invf)[tid];
+            const float angle =
+                static_cast<float>(reinterpret_cast<const long long*>(slot(MB_AT_S_POS))[b]) * f;
+            const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
+            float sn, cn;
+            sincosf(angle, &sn, &cn);
+            cs[tid] = bf16_round(cn * rope_scale);
+            cs[D / 2 + tid] = bf16_round(sn * rope_scale);
+        }
         uint4 kt[2][DC];
         uint4 vt[DB][4];
         const int first = blk0 + warp;
@@ -795,54 +840,37 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             if (kEarlyKeys) load_keys(first, kt);
             if (kEarlyValues) load_values(first, vt);
         }
-
-        // ---- cos/sin, RoPE of the group's query heads and of the new key, new value row
-        if (tid < D / 2) {
-            const float f =
-                invf_bf16 ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(invf)[tid])
-                          : reinterpret_cast<const float*>(invf)[tid];
-            const float angle = static_cast<float>(pos[b]) * f;
-            float sn, cn;
-            sincosf(angle, &sn, &cn);
-            cs[tid] = bf16_round(cn * rope_scale);
-            cs[D / 2 + tid] = bf16_round(sn * rope_scale);
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         named_barrier(kBarConsumers, kConsumerThreads);
+        // rotate in place: thread e owns the element pair (i, i + D/2) of row e / (D/2); rows
+        // 0..group-1 are query heads, row `group` is the new key
         const bool appends = chunk == nc - 1;  // the chunk that holds key L stores the new row
-        const size_t new_row = ((static_cast<size_t>(b) * cap + L) * Hkv + h) * D;
+        const size_t new_row = cache_row0 + static_cast<size_t>(L) * key_stride;
+        const float q_scale = P->f[MB_AT_F_Q_SCALE];
+        unsigned short* kcache = reinterpret_cast<unsigned short*>(slot(MB_AT_S_KCACHE));
         for (int e = tid; e < (group + 1) * (D / 2); e += kConsumerThreads) {
             const int gq = e / (D / 2), i = e - gq * (D / 2);
-            const bool is_key = gq == group;
-            const unsigned short* row =
-                is_key ? kbuf + (static_cast<size_t>(b) * Hkv + h) * D
-                       : qbuf + (static_cast<size_t>(b) * Hq + h * group + gq) * D;
-            const float x1 = bf16_bits_to_float(ld_cg_u16(row + i));
-            const float x2 = bf16_bits_to_float(ld_cg_u16(row + i + D / 2));
+            __nv_bfloat16* row = gq == group ? kn : qs + gq * QP;
+            const float x1 = __bfloat162float(row[i]), x2 = __bfloat162float(row[i + D / 2]);
             const float c = cs[i], sn = cs[D / 2 + i];
             float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * sn));
             float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * sn));
-            if (is_key) {
-                kn[i] = __float2bfloat16_rn(r1);
-                kn[i + D / 2] = __float2bfloat16_rn(r2);
-                if (appends) {
-                    kcache[new_row + i] = float_to_bf16_bits(r1);
-                    kcache[new_row + i + D / 2] = float_to_bf16_bits(r2);
-                }
-            } else {
-                if (q_scale != 0.f && q_scale != 1.f) {
-                    r1 = bf16_round(r1 * q_scale);
-                    r2 = bf16_round(r2 * q_scale);
-                }
-                qs[gq * QP + i] = __float2bfloat16_rn(r1);
-                qs[gq * QP + i + D / 2] = __float2bfloat16_rn(r2);
+            if (gq != group && q_scale != 0.f && q_scale != 1.f) {
+                r1 = bf16_round(r1 * q_scale);
+                r2 = bf16_round(r2 * q_scale);
+            }
+            row[i] = __float2bfloat16_rn(r1);
+            row[i + D / 2] = __float2bfloat16_rn(r2);
+            if (gq == group && appends) {
+                kcache[new_row + i] = float_to_bf16_bits(r1);
+                kcache[new_row + i + D / 2] = float_to_bf16_bits(r2);
             }
         }
-        for (int i = tid; i < D; i += kConsumerThreads) {
-            const unsigned short v = ld_cg_u16(vbuf + (static_cast<size_t>(b) * Hkv + h) * D + i);
-            reinterpret_cast<unsigned short*>(vn)[i] = v;
-            if (appends) vcache[new_row + i] = v;
-        }
+        if (appends && tid < D)
+            reinterpret_cast<unsigned short*>(slot(MB_AT_S_VCACHE))[new_row + tid] =
+                reinterpret_cast<unsigned short*>(vn)[tid];
         named_barrier(kBarConsumers, kConsumerThreads);
+        trace_stamp(p, ph, 4, tid);
 
         // QK^T: A = rotated queries (row = head of the group), B = keys (n = key).  The head
         // dimension is permuted identically in both operands so that every lane fetches 16
@@ -867,15 +895,23 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         // scores of one block: sv[2j + q] <-> head gid, key kb + 8j + 2tq + q; bf16-rounded
         // product, scale applied in fp32, keys past the valid length masked
         auto block_scores = [&](int kb, const uint4 (&kt_)[2][DC], float (&sv)[4]) {
-            float frag[2][4];
+            float frag[2][4], frag2[2][4];  // two independent chains per tile, added at the end
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 frag[j][0] = frag[j][1] = frag[j][2] = frag[j][3] = 0.f;
+                frag2[j][0] = frag2[j][1] = frag2[j][2] = frag2[j][3] = 0.f;
+            }
 #pragma unroll
-                for (int i = 0; i < DC; ++i) {
+            for (int i = 0; i < DC; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
                     mma_bf16_16816(frag[j], qf[i].x, 0u, qf[i].y, 0u, kt_[j][i].x, kt_[j][i].y);
-                    mma_bf16_16816(frag[j], qf[i].z, 0u, qf[i].w, 0u, kt_[j][i].z, kt_[j][i].w);
+                    mma_bf16_16816(frag2[j], qf[i].z, 0u, qf[i].w, 0u, kt_[j][i].z, kt_[j][i].w);
                 }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                frag[j][0] += frag2[j][0];
+                frag[j][1] += frag2[j][1];
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -999,6 +1035,7 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         }
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        trace_stamp(p, ph, 5, tid);
 
         // ---- merge the warp states into one CTA state, `merge_slots` warps per round
         const int rounds = (kConsumerWarps + merge_slots - 1) / merge_slots;
@@ -1052,7 +1089,9 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             named_barrier(kBarConsumers, kConsumerThreads);
         }
         const float* state = running + static_cast<size_t>((rounds - 1) & 1) * group * SW;
+        trace_stamp(p, ph, 6, tid);
 
+        unsigned short* out = reinterpret_cast<unsigned short*>(slot(MB_AT_S_OUT));
         if (nc == 1) {
             for (int e = tid; e < group * D; e += kConsumerThreads) {
                 const int gq = e / D, d = e - gq * D;
@@ -1060,6 +1099,9 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 out[(static_cast<size_t>(b) * Hq + h * group + gq) * D + d] = float_to_bf16_bits(v);
             }
         } else {
+            float* partial = reinterpret_cast<float*>(slot(MB_AT_S_PARTIAL));
+            int* counter = reinterpret_cast<int*>(slot(MB_AT_S_COUNTER));
+            const int max_chunks = P->i[MB_AT_I_MAX_CHUNKS];
             float* mine = partial + (static_cast<size_t>(pair) * max_chunks + chunk) * group * SW;
             for (int e = tid; e < group * SW; e += kConsumerThreads) mine[e] = state[e];
             __threadfence();
@@ -1070,6 +1112,7 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 sc->bcast[1] = arrived;
             }
             named_barrier(kBarConsumers, kConsumerThreads);
+            trace_stamp(p, ph, 7, tid);
             if (sc->bcast[1] == nc - 1) {
                 // Last chunk of this (row, kv head) to arrive folds all chunks, in chunk order.
                 // Step 1: (max, sum) of every chunk into shared memory, all loads in flight
@@ -1102,10 +1145,17 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                     const int gq = e / D, d = e - gq * D;
                     const float* col = all + static_cast<size_t>(gq) * SW + 2 + d;
                     float sum_v = 0.f;
-#pragma unroll 8
-                    for (int c = 0; c < nc; ++c)
-                        sum_v += ld_cg_f32(col + static_cast<size_t>(c) * group * SW) *
-                                 weight[gq * nc + c];
+                    for (int c0 = 0; c0 < nc; c0 += 8) {  // eight loads in flight per batch
+                        float part[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            part[u] = c0 + u < nc
+                                          ? ld_cg_f32(col + static_cast<size_t>(c0 + u) * group * SW)
+                                          : 0.f;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (c0 + u < nc) sum_v += part[u] * weight[gq * nc + c0 + u];
+                    }
                     out[(static_cast<size_t>(b) * Hq + h * group + gq) * D + d] =
                         float_to_bf16_bits(sum_v / denom[gq]);
                 }
@@ -1133,9 +1183,9 @@ __device__ __forceinline__ void attention_decode(const KernelParams& p, const Ph
         return;
     }
     if (L + 1 <= E->rec.i[MB_AT_I_EXACT_KEYS])
-        attention_body<D, true>(p, E, L, sc, scratch, tid);
+        attention_body<D, true>(p, E, L, ph, sc, scratch, tid);
     else
-        attention_body<D, false>(p, E, L, sc, scratch, tid);
+        attention_body<D, false>(p, E, L, ph, sc, scratch, tid);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1151,8 +1201,20 @@ __device__ __forceinline__ void prefetch_entry(const PhaseEntry* src, PhaseEntry
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-__device__ __forceinline__ void wait_entry() {
+// Every thread waits for its own copies; the 16-byte vectors of one address pair (two slots)
+// were copied by one thread, which then patches them -- no extra barrier is needed before the
+// CTA barrier that publishes the entry.
+__device__ __forceinline__ void wait_entry(const KernelParams& p, PhaseEntry* dst, int tid) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    constexpr int kFirstAddrVector = offsetof(PhaseEntry, addr) / 16;
+    static_assert(offsetof(PhaseEntry, addr) % 16 == 8, "addr[] starts mid-vector");
+    // vector kFirstAddrVector holds addr[0] in its upper half; vector v > that holds
+    // addr[2 (v - first) - 1] and addr[2 (v - first)]
+    if (tid >= kFirstAddrVector && tid < kEntryVectors) {
+        const int hi = 2 * (tid - kFirstAddrVector), lo = hi - 1;
+        if (lo >= 0 && lo < MB_PHASE_SLOTS) dst->addr[lo] = resolve_dynamic(p, dst->addr[lo]);
+        if (hi < MB_PHASE_SLOTS) dst->addr[hi] = resolve_dynamic(p, dst->addr[hi]);
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -1175,7 +1237,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
     }
     if (tid < kConsumerThreads) {
         prefetch_entry(p.entries, &sc->entry[0], tid);
-        wait_entry();
+        wait_entry(p, &sc->entry[0], tid);
     }
     __syncthreads();
     if (sc->abort_flag) return;
@@ -1241,7 +1303,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             const int flags = E->rec.flags;
             const unsigned long long length_address =
                 (flags & MB_FLAG_BUMP_LENGTH) ? entry_address(p, E, MB_AT_S_LEN) : 0ull;
-            if (more) wait_entry();  // made visible to the CTA by the barrier below
+            if (more) wait_entry(p, &sc->entry[(ph + 1) & 1], tid);  // published by the barrier below
             if (flags & MB_FLAG_BARRIER) {
                 ++barrier_index;
                 ok = grid_barrier(p.ctl, base + barrier_index * gridDim.x, kBarConsumers,

@@ -32,7 +32,7 @@ EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_GELU_TANH_MUL = 0, 1, 2, 3
 # MB_BODY_GEMV field indices
 GV_I_ROWS, GV_I_K, GV_I_NSEG, GV_I_N0 = 0, 1, 2, 3
 GV_I_NMAT, GV_I_PROLOGUE, GV_I_EPILOGUE, GV_I_ROW_TILE, GV_I_K_CHUNK = 6, 7, 8, 9, 10
-GV_I_GATHER, GV_I_VOCAB, GV_I_STORE_X = 11, 12, 13
+GV_I_GATHER, GV_I_VOCAB, GV_I_STORE_X, GV_I_SPLIT_Q, GV_I_SPLIT_R = 11, 12, 13, 14, 15
 GV_F_EPS, GV_F_EMBED_SCALE = 0, 1
 GV_S_X, GV_S_NORM_W, GV_S_W0, GV_S_BIAS0, GV_S_OUT0 = 0, 1, 2, 5, 8
 GV_S_W_PAIR, GV_S_RESIDUAL, GV_S_IDS, GV_S_XSTORE = 11, 12, 13, 14
