@@ -9,9 +9,10 @@ number of keys (filled by a seeded prefill of uniform-random token ids).  Prints
 
 * ``value``      decode microseconds per generated token with inputs resident in HBM:
                  max-over-ranks device time of K back-to-back launches / (K * batch * N)
-* ``e2e``        the same metric through the public call (``BoundDecoder.__call__``, what
-                 ``make_backend`` returns) with HOST buffers: per step a pinned host->device copy
-                 of token and position ids, the launch, a device argmax of the logits and a
+* ``e2e``        the same metric through the public API -- ``torch.compile(StatefulDecoder(model),
+                 backend=make_backend(mode="decode"))`` captured with ``megabake_b200.graphed`` --
+                 with HOST buffers: per step a pinned host->device copy of token and position ids,
+                 the graph replay (one megakernel launch), a device argmax of the logits and a
                  device->host read of the picked ids, synchronised every step
 * ``roofline``   HBM roofline of the megakernel: algorithmic bytes per launch (weights once +
                  the valid KV rows) / mean launch time, against the measured copy bandwidth
@@ -243,7 +244,7 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=device)
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    total_calls = 2 * (steps + warmup) + 8
+    total_calls = 2 * (steps + warmup) + 16
     spec, batch, keys, capacity, weights, inv_freq, state = build_workload(
         args.workload, rank, total_calls, device, args.cache_fill)
     program = models.direct_program(spec, batch, capacity)
@@ -281,20 +282,41 @@ def run_ours(args) -> None:
     device_ms = start.elapsed_time(stop)
     mean_keys = first_key + (steps - 1) / 2 + 1
 
-    # ---- end-to-end timing: host buffers in, picked ids out, synchronised per step ---------
+    # ---- end-to-end timing through the public API -------------------------------------------
+    # torch.compile(wrapper, backend=make_backend(mode="decode")) captured once in a CUDA graph
+    # with megabake_b200.graphed (the reference's own recipe for steady-state decode).  Per
+    # step: pinned host -> device copy of token and position ids, graph replay (one megakernel
+    # launch), device argmax, device -> host read of the picked ids, synchronised every step.
+    from megabake_b200 import StatefulDecoder, graphed, make_backend
+
+    if args.skip_e2e:
+        return _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, None,
+                       mean_keys, {"ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages},
+                       sampler, rank, world, distributed, device)
+    plan_info = {"ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages}
+    decoder.close()
+    del decoder
+    model = models.build_hf_model(spec, device=device, weights=weights)
+    del weights, call_args
+    torch.cuda.empty_cache()
+    wrapper = StatefulDecoder(model, capacity).eval()
+    backend = make_backend(mode="decode")
+    step_fn = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
     host_ids = ids.clone().pin_memory()
     host_pos = torch.zeros(batch, 1, dtype=torch.int64).pin_memory()
     host_pick = torch.zeros(batch, dtype=torch.int64).pin_memory()
     dev_ids = torch.empty_like(ids_dev)
-    dev_pos = torch.empty(batch, 1, dtype=torch.int64, device=device)
-    e2e_args = list(call_args)
-    e2e_args[program.input_ids], e2e_args[program.position_ids] = dev_ids, dev_pos
+    dev_pos = torch.full((batch, 1), keys + call, dtype=torch.int64, device=device)
+    dev_ids.copy_(ids_dev)
+    with torch.no_grad():
+        graph_call = graphed(step_fn, dev_ids, dev_pos, *state)
+    compiled_decoder = backend.megabake_last_callable
 
     def e2e_step(index: int):
         host_pos.fill_(keys + index)
         dev_ids.copy_(host_ids, non_blocking=True)
         dev_pos.copy_(host_pos, non_blocking=True)
-        out = decoder(*e2e_args)
+        out = graph_call(dev_ids, dev_pos, *state)
         host_pick.copy_(out[:, -1].argmax(-1), non_blocking=True)
         torch.cuda.synchronize()
 
@@ -308,10 +330,19 @@ def run_ours(args) -> None:
         call += 1
     barrier()
     e2e_s = time.perf_counter() - t0
-    decoder.check()
+    compiled_decoder.check()
 
-    times = torch.tensor([device_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    return _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s,
+                   mean_keys, plan_info, sampler, rank, world, distributed, device)
+
+
+def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s, mean_keys,
+            plan_info, sampler, rank, world, distributed, device) -> None:
+    import torch
+
+    times = torch.tensor([device_ms, (e2e_s or 0.0) * 1e3], dtype=torch.float64, device=device)
     if distributed:
+        import torch.distributed as dist
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     device_ms, e2e_ms = (float(x) for x in times.cpu())
 
@@ -334,7 +365,7 @@ def run_ours(args) -> None:
                       f"{bytes_per_launch / 1e6:.0f} MB vs 126 MB L2",
                 "tokens_per_s": batch * world / (ms_per_step * 1e-3),
                 "phases": len(layout.phases), "barrier_intervals": layout.intervals,
-                "ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages,
+                "ctas": plan_info["ctas"], "ring_stages": plan_info["ring_stages"],
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -342,11 +373,12 @@ def run_ours(args) -> None:
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": bytes_per_launch,
             },
-            "e2e": {
+            "e2e": None if e2e_s is None else {
                 "value": e2e_ms * 1e3 / steps / (batch * world), "unit": UNIT,
                 "h2d_bytes_per_step": 2 * batch * 8, "d2h_bytes_per_step": batch * 8,
                 "ms_per_step": e2e_ms / steps,
-                "path": "BoundDecoder.__call__ + torch argmax, synchronised every step",
+                "path": "torch.compile(StatefulDecoder, backend=make_backend(mode='decode')) under "
+                        "megabake_b200.graphed + torch argmax, synchronised every step",
             },
             "gpu_launches": steps,
             "clocks": sampler.summary(),
@@ -356,6 +388,7 @@ def run_ours(args) -> None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     if distributed:
+        import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
 
@@ -368,6 +401,8 @@ def main() -> None:
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--skip-e2e", action="store_true",
+                        help="profiler runs: only the resident-input loop (e2e is reported null)")
     parser.add_argument("--cache-fill", default="prefill", choices=["prefill", "random"],
                         help="how the KV cache gets its cached keys (random: for profiler runs)")
     args = parser.parse_args()
