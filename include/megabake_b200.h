@@ -228,6 +228,41 @@ int mb_plan_reset(mb_plan* plan);
 int mb_plan_set_trace(mb_plan* plan, uint64_t device_address, size_t bytes);
 void mb_plan_destroy(mb_plan* plan);
 
+/* ---- decode attention that allocates nothing ---------------------------------------------
+ * No counterpart in the reference (its attention body only exists inside a compiled plan).
+ * For callers that must not allocate device memory where they need an attention step (a
+ * plugin inside a foreign stream-ordered pipeline, a process living on a memory budget fixed
+ * at start-up, a region where cudaMalloc would synchronise the device): the same decode
+ * attention as MB_BODY_ATTN_DECODE -- RoPE of q and the new k, append at valid_length,
+ * valid_length += 1, attention over every valid key -- with its scratch (split-key partials,
+ * arrival counters, status) in a fixed 4 MiB array inside the library's device image instead
+ * of allocated memory.  It calls no cudaMalloc/cudaFree or allocating library routine.
+ *
+ * Limits: batch * kv_heads <= 1024 and batch * heads * (head_dim + 2) * 4 B must fit the array
+ * (MB_ERR_RESOURCE otherwise); heads / kv_heads <= 8; head_dim in {64, 128, 256}.
+ * The first call on a device does the one-time set-up (address of the array on that device,
+ * kernel attribute): make it before any stream capture.  Every call shares the array: calls
+ * that may overlap on the GPU race on it and must be serialised by the caller.  Non-blocking:
+ * a device-side fault (KV cache full = MB_ST_KV_OVERFLOW) is written to `status` if given.  */
+typedef struct mb_attention_args {
+    int32_t batch, heads, kv_heads, head_dim, capacity;
+    int32_t inv_freq_is_bf16;  /* 1: inv_freq holds bf16, 0: fp32                              */
+    float rope_scale;          /* attention_scaling multiplied into cos/sin (usually 1)        */
+    float query_scale;         /* 0 or 1 = none; else q = bf16(q * this) after RoPE            */
+    uint64_t query;            /* [batch, heads * head_dim] bf16, before RoPE                  */
+    uint64_t key;              /* [batch, kv_heads * head_dim] bf16, before RoPE               */
+    uint64_t value;            /* [batch, kv_heads * head_dim] bf16                            */
+    uint64_t key_cache;        /* [batch, capacity, kv_heads, head_dim] bf16, appended to      */
+    uint64_t value_cache;
+    uint64_t valid_length;     /* int32 [1], incremented                                       */
+    uint64_t position_ids;     /* int64 [batch]                                                */
+    uint64_t inv_freq;         /* [head_dim / 2]                                               */
+    uint64_t out;              /* [batch, heads * head_dim] bf16                               */
+    uint64_t status;           /* optional int32 [1] receiving enum mb_status_code, or 0       */
+} mb_attention_args;
+
+int mb_attention_decode_static(const mb_attention_args* args, void* stream);
+
 const char* mb_strerror(int code);
 const char* mb_status_string(int status_code);
 const char* mb_last_cuda_error(void);

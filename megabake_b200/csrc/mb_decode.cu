@@ -15,6 +15,10 @@
 // map bodies used for RMSNorm, RoPE, residual and gated activations
 // (src/megabake/bodies/cuda/generic.py:175-613) and the counting grid barrier
 // (src/megabake/runtime.py:153-190).
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
 #include "mb_device.cuh"
 #include "mb_kernels.h"
 
@@ -1374,3 +1378,200 @@ cudaError_t decode_launch(const KernelParams& params, int ctas, int smem_bytes,
 }
 
 }  // namespace mb
+
+// =======================================================================================
+// Decode attention without any allocation.
+//
+// Some hosts may not allocate device memory at the point where they need one attention
+// step: a plugin called from inside someone else's stream-ordered pipeline, a process that
+// runs with a fixed memory budget handed out at start-up, a caller inside a region where
+// cudaMalloc would synchronise the device.  For them this entry point runs the same
+// attention body as the plan path, but everything the plan path keeps in allocated memory
+// (phase table, control block, split-key partials, arrival counters) lives either in the
+// kernel parameters or in one fixed-size array inside this library's device image.
+//
+// The array is a file-scope `static __device__` object of kStaticScratchBytes (4 MiB); every
+// GPU that loads the library holds it until the process exits.  In host code its name is only
+// a host-side stand-in, not a device address: the address the kernel gets is asked for once
+// per device with cudaGetSymbolAddress, with that device current.
+//
+// All calls share the array.  The arrival counters and the control words are cleared on the
+// stream before every launch; the partials need no clearing (they are written before they
+// are read).  Two calls that overlap on the GPU (different streams, no dependency) race on
+// it -- callers serialise them.
+// =======================================================================================
+namespace mb {
+namespace decode {
+
+constexpr size_t kStaticScratchBytes = 4u << 20;
+constexpr size_t kStaticControlBytes = 256;        // Control + "CTAs done" counter
+constexpr size_t kStaticCounterBytes = 4096;       // arrival counters: up to 1024 (row, kv head)
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+__global__ void __launch_bounds__(kConsumerThreads, 1)
+attention_static_kernel(const __grid_constant__ PhaseEntry entry, Control* ctl, int* done,
+                        int* status_out) {
+    extern __shared__ __align__(128) char smem[];
+    SharedCtl* sc = reinterpret_cast<SharedCtl*>(smem);
+    char* scratch = smem + kCtlBytes;
+    const int tid = threadIdx.x;
+    if (tid < kEntryVectors)
+        reinterpret_cast<uint4*>(&sc->entry[0])[tid] = reinterpret_cast<const uint4*>(&entry)[tid];
+    if (tid == 0) sc->abort_flag = 0;
+    __syncthreads();
+    KernelParams p;
+    p.entries = nullptr;
+    p.ctl = ctl;
+    p.trace = nullptr;
+    p.n_phases = 1;
+    p.n_dynamic = 0;
+    p.barriers_per_launch = 0;
+    p.stages = 0;
+    p.activation_bytes = 0;
+    const PhaseEntry* E = &sc->entry[0];
+    const int D = E->rec.i[MB_AT_I_HEAD_DIM];
+    if (D == 64)
+        attention_decode<64>(p, E, 0, sc, scratch, tid);
+    else if (D == 128)
+        attention_decode<128>(p, E, 0, sc, scratch, tid);
+    else
+        attention_decode<256>(p, E, 0, sc, scratch, tid);
+    __syncthreads();
+    if (tid == 0) {
+        // The valid length may only move once every CTA has read it: the last CTA to finish
+        // advances it, reports the status and re-arms the counter for the next call.
+        __threadfence();
+        const int finished = atomicAdd(done, 1);
+        if (finished == static_cast<int>(gridDim.x) - 1) {
+            __threadfence();
+            const int code = *reinterpret_cast<volatile int*>(&ctl->status[0]);
+            if (code == 0) {
+                int* lenp = reinterpret_cast<int*>(E->addr[MB_AT_S_LEN]);
+                *lenp = *lenp + 1;
+            }
+            if (status_out != nullptr) *status_out = code;
+            *done = 0;
+        }
+    }
+}
+
+struct StaticDevice {
+    unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+    int max_smem = 0;
+    bool ready = false;
+};
+
+}  // namespace decode
+}  // namespace mb
+
+namespace {
+mb::decode::StaticDevice g_static_devices[64];
+std::mutex g_static_mutex;
+
+long long static_attention_smem(int head_dim, int group, int merge_slots) {
+    return mb::decode::kCtlBytes + 8LL * (head_dim + 32) * 2 + 2LL * head_dim * 2 + 4LL * head_dim +
+           4LL * (2 * 8 * 8 + mb::decode::kFoldFloats) +
+           4LL * (head_dim + 2) * group * (merge_slots + 2);
+}
+}  // namespace
+
+// Declared in include/megabake_b200.h.  The first call on a device performs the one-time
+// set-up (symbol address, kernel attribute); make that call before any stream capture.
+extern "C" int mb_attention_decode_static(const mb_attention_args* a, void* stream) {
+    using namespace mb::decode;
+    if (a == nullptr) return MB_ERR_INVALID;
+    if (a->batch < 1 || a->heads < 1 || a->kv_heads < 1 || a->capacity < 1) return MB_ERR_INVALID;
+    if (a->heads % a->kv_heads != 0 || a->heads / a->kv_heads > 8) return MB_ERR_UNSUPPORTED;
+    if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return MB_ERR_UNSUPPORTED;
+    const unsigned long long pointers[] = {a->query, a->key, a->value, a->key_cache,
+                                           a->value_cache, a->valid_length, a->position_ids,
+                                           a->inv_freq, a->out};
+    for (unsigned long long ptr : pointers)
+        if (ptr == 0) return MB_ERR_INVALID;
+    if ((a->query | a->key | a->value | a->key_cache | a->value_cache | a->out) & 15ull)
+        return MB_ERR_INVALID;
+
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return MB_ERR_CUDA;
+    StaticDevice& dev = g_static_devices[device];
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!dev.ready) {
+            void* address = nullptr;
+            cudaError_t err = cudaGetSymbolAddress(&address, g_static_scratch);
+            if (err != cudaSuccess || address == nullptr) return MB_ERR_CUDA;
+            cudaDeviceProp prop;
+            if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return MB_ERR_CUDA;
+            if (prop.major != 10) return MB_ERR_UNSUPPORTED;
+            dev.max_smem = 100 * 1024;
+            if (cudaFuncSetAttribute(attention_static_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     dev.max_smem) != cudaSuccess)
+                return MB_ERR_CUDA;
+            dev.scratch = static_cast<unsigned char*>(address);
+            dev.sm_count = prop.multiProcessorCount;
+            dev.ready = true;
+        }
+    }
+
+    const int group = a->heads / a->kv_heads;
+    const int pairs = a->batch * a->kv_heads;
+    int merge_slots = 8;
+    while (merge_slots > 1 &&
+           static_attention_smem(a->head_dim, group, merge_slots) - kCtlBytes > 48 * 1024)
+        merge_slots /= 2;
+    if (static_attention_smem(a->head_dim, group, merge_slots) > dev.max_smem) return MB_ERR_RESOURCE;
+    // What fits the fixed array: arrival counters for every (row, kv head) and at least one
+    // key chunk of partials each; more chunks if there is room, up to 32.
+    if (static_cast<size_t>(pairs) * 4 > kStaticCounterBytes) return MB_ERR_RESOURCE;
+    const size_t per_chunk = static_cast<size_t>(pairs) * group * (a->head_dim + 2) * 4;
+    const size_t room = kStaticScratchBytes - kStaticControlBytes - kStaticCounterBytes;
+    if (per_chunk > room) return MB_ERR_RESOURCE;  // shapes beyond the 4 MiB scratch
+    int max_chunks = static_cast<int>(room / per_chunk);
+    if (max_chunks > 32) max_chunks = 32;
+    const int by_capacity = (a->capacity + 15) / 16;
+    if (max_chunks > by_capacity) max_chunks = by_capacity;
+
+    mb::PhaseEntry entry;
+    std::memset(&entry, 0, sizeof(entry));
+    entry.rec.body = MB_BODY_ATTN_DECODE;
+    entry.rec.i[MB_AT_I_BATCH] = a->batch;
+    entry.rec.i[MB_AT_I_HEADS] = a->heads;
+    entry.rec.i[MB_AT_I_KV_HEADS] = a->kv_heads;
+    entry.rec.i[MB_AT_I_HEAD_DIM] = a->head_dim;
+    entry.rec.i[MB_AT_I_CAPACITY] = a->capacity;
+    entry.rec.i[MB_AT_I_INVFREQ_BF16] = a->inv_freq_is_bf16 ? 1 : 0;
+    entry.rec.i[MB_AT_I_MAX_CHUNKS] = max_chunks;
+    entry.rec.i[MB_AT_I_MERGE_SLOTS] = merge_slots;
+    entry.rec.i[MB_AT_I_EXACT_KEYS] = a->capacity < 128 ? a->capacity : 128;
+    entry.rec.f[MB_AT_F_SCALE] = 1.0f / sqrtf(static_cast<float>(a->head_dim));
+    entry.rec.f[MB_AT_F_ROPE_SCALE] = a->rope_scale;
+    entry.rec.f[MB_AT_F_Q_SCALE] = a->query_scale;
+    unsigned char* control = dev.scratch;
+    unsigned char* counters = dev.scratch + kStaticControlBytes;
+    unsigned char* partials = counters + kStaticCounterBytes;
+    entry.addr[MB_AT_S_Q] = a->query;
+    entry.addr[MB_AT_S_K] = a->key;
+    entry.addr[MB_AT_S_V] = a->value;
+    entry.addr[MB_AT_S_KCACHE] = a->key_cache;
+    entry.addr[MB_AT_S_VCACHE] = a->value_cache;
+    entry.addr[MB_AT_S_LEN] = a->valid_length;
+    entry.addr[MB_AT_S_POS] = a->position_ids;
+    entry.addr[MB_AT_S_INVFREQ] = a->inv_freq;
+    entry.addr[MB_AT_S_OUT] = a->out;
+    entry.addr[MB_AT_S_PARTIAL] = reinterpret_cast<unsigned long long>(partials);
+    entry.addr[MB_AT_S_COUNTER] = reinterpret_cast<unsigned long long>(counters);
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // control words + arrival counters start every call at zero (a faulted earlier call may
+    // have left them set); the partials are always written before they are read
+    if (cudaMemsetAsync(control, 0, kStaticControlBytes + kStaticCounterBytes, s) != cudaSuccess)
+        return MB_ERR_CUDA;
+    mb::Control* ctl = reinterpret_cast<mb::Control*>(control);
+    int* done = reinterpret_cast<int*>(control + 128);
+    const int smem = static_cast<int>(static_attention_smem(a->head_dim, group, merge_slots));
+    attention_static_kernel<<<dev.sm_count, kConsumerThreads, smem, s>>>(
+        entry, ctl, done, reinterpret_cast<int*>(a->status));
+    return cudaGetLastError() == cudaSuccess ? MB_OK : MB_ERR_CUDA;
+}

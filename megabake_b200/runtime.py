@@ -96,6 +96,21 @@ class PlanInfo(ctypes.Structure):
     ]
 
 
+class AttentionArgs(ctypes.Structure):
+    """``mb_attention_args`` of the allocation-free attention entry point."""
+
+    _fields_ = [
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32), ("capacity", ctypes.c_int32),
+        ("inv_freq_is_bf16", ctypes.c_int32),
+        ("rope_scale", ctypes.c_float), ("query_scale", ctypes.c_float),
+        ("query", ctypes.c_uint64), ("key", ctypes.c_uint64), ("value", ctypes.c_uint64),
+        ("key_cache", ctypes.c_uint64), ("value_cache", ctypes.c_uint64),
+        ("valid_length", ctypes.c_uint64), ("position_ids", ctypes.c_uint64),
+        ("inv_freq", ctypes.c_uint64), ("out", ctypes.c_uint64), ("status", ctypes.c_uint64),
+    ]
+
+
 class Status(ctypes.Structure):
     _fields_ = [
         ("code", ctypes.c_int32),
@@ -112,6 +127,7 @@ EXPORTS = (
     "mb_plan_create", "mb_plan_query", "mb_plan_bind", "mb_plan_launch", "mb_plan_status",
     "mb_plan_reset", "mb_plan_set_trace", "mb_plan_destroy", "mb_strerror", "mb_status_string", "mb_last_cuda_error",
     "mb_abi_version", "mb_fixed_smem_bytes", "mb_stage_bytes", "mb_max_smem_bytes",
+    "mb_attention_decode_static",
 )
 
 _library = None
@@ -164,6 +180,8 @@ def load_library(path: Path | None = None) -> ctypes.CDLL:
             getattr(lib, name).argtypes = [ctypes.c_int]
             getattr(lib, name).restype = ctypes.c_char_p
         lib.mb_last_cuda_error.restype = ctypes.c_char_p
+        lib.mb_attention_decode_static.argtypes = [ctypes.POINTER(AttentionArgs), ctypes.c_void_p]
+        lib.mb_attention_decode_static.restype = ctypes.c_int
         if lib.mb_abi_version() != MB_ABI_VERSION:
             raise _native_error(
                 f"{target} speaks ABI {lib.mb_abi_version()}, the host expects {MB_ABI_VERSION}"
