@@ -186,6 +186,58 @@ typedef struct mb_phase {
 #define MB_AT_S_PARTIAL 9    /* fp32 [B*Hkv, max_chunks, Hq/Hkv, D+2]                      */
 #define MB_AT_S_COUNTER 10   /* int32 [B*Hkv], zero before the first launch                */
 
+/* ---- prefill bodies (MB_MODE_PREFILL plans: one kernel launch per phase, in order) ----- */
+/* MB_BODY_EMBED_ROWS: out[r, :] = table[ids[r], :] (x scale, rounded to bf16)              */
+#define MB_EM_I_ROWS 0
+#define MB_EM_I_K 1
+#define MB_EM_I_VOCAB 2
+#define MB_EM_F_SCALE 0      /* 0 = none                                                   */
+#define MB_EM_S_TABLE 0      /* [vocab, K] bf16                                            */
+#define MB_EM_S_IDS 1        /* int64 [rows]                                               */
+#define MB_EM_S_OUT 2        /* [rows, K] bf16                                             */
+/* MB_BODY_RMSNORM_ROWS: out[r, :] = rmsnorm(x[r, :]) in the spelling MB_RN_I_KIND names    */
+#define MB_RN_I_ROWS 0
+#define MB_RN_I_K 1          /* multiple of 8                                              */
+#define MB_RN_I_KIND 2       /* enum mb_prologue, not NONE                                 */
+#define MB_RN_F_EPS 0
+#define MB_RN_S_X 0
+#define MB_RN_S_W 1
+#define MB_RN_S_OUT 2
+/* MB_BODY_GEMM_TC: the MB_BODY_GEMV record (MB_GV_* fields: any number of rows, K a multiple
+ * of 8, segments, paired gate/up, epilogues; no prologue, no gather) computed by a TMA-fed
+ * tcgen05 GEMM with TMEM accumulators.  mb_plan_create fills MB_GV_I_SPLIT_K and
+ * MB_GV_I_TILE_N.                                                                          */
+#define MB_GV_I_SPLIT_K 16   /* CTAs sharing one output tile along the reduction           */
+#define MB_GV_I_TILE_N 17    /* output columns per tile: 128 or 256 (per matrix: half)     */
+/* MB_BODY_ROPE_ROWS: rotary embedding of q and k rows, in place                            */
+#define MB_RP_I_ROWS 0
+#define MB_RP_I_HEADS 1
+#define MB_RP_I_KV_HEADS 2
+#define MB_RP_I_HEAD_DIM 3
+#define MB_RP_I_INVFREQ_BF16 4
+#define MB_RP_F_ROPE_SCALE 0
+#define MB_RP_F_Q_SCALE 1    /* 0 or 1 = none; else q = bf16(q * this) after the rotation  */
+#define MB_RP_S_Q 0          /* [rows, heads * D] bf16                                     */
+#define MB_RP_S_K 1          /* [rows, kv_heads * D] bf16                                  */
+#define MB_RP_S_POS 2        /* int64 [rows]                                               */
+#define MB_RP_S_INVFREQ 3    /* [D / 2]                                                    */
+/* MB_BODY_ATTN_PREFILL: softmax attention with the eager operator's rounding points:
+ * s = bf16(q . k), s = bf16(s * scale), s = bf16(s + mask), p = bf16(softmax_fp32(s)),
+ * out = bf16(sum p v).                                                                     */
+#define MB_AP_I_BATCH 0
+#define MB_AP_I_TOKENS 1
+#define MB_AP_I_HEADS 2
+#define MB_AP_I_KV_HEADS 3
+#define MB_AP_I_HEAD_DIM 4   /* 64, 128 or 256                                             */
+#define MB_AP_I_CAUSAL 5     /* 1: key j visible to query i iff j <= i, no mask tensor      */
+#define MB_AP_I_MASK_BATCH 6 /* leading extent of the mask tensor: 1 or batch              */
+#define MB_AP_F_SCALE 0
+#define MB_AP_S_Q 0          /* [batch * tokens, heads * D] bf16 (after RoPE)              */
+#define MB_AP_S_K 1          /* [batch * tokens, kv_heads * D]                             */
+#define MB_AP_S_V 2
+#define MB_AP_S_OUT 3        /* [batch * tokens, heads * D]                                */
+#define MB_AP_S_MASK 4       /* additive bf16 [mask_batch, 1, tokens, tokens], or absent   */
+
 /* ---- plan descriptor ---------------------------------------------------------------- */
 #define MB_MAX_DYNAMIC 8
 

@@ -66,6 +66,7 @@ struct mb_plan {
     mb::PhaseEntry* d_entries = nullptr;
     mb::Control* d_ctl = nullptr;
     unsigned long long trace = 0;
+    mb::PrefillState* prefill = nullptr;  // MB_MODE_PREFILL plans only
 };
 
 namespace {
@@ -145,6 +146,43 @@ int validate_attention(const mb_plan_desc* d, const mb_phase& P) {
     return MB_OK;
 }
 
+// A prefill plan is a list of kernel launches; it shares the descriptor, the slot table, the
+// status word and the entry points with decode plans.
+int create_prefill_plan(const mb_plan_desc* desc, mb_plan** out) {
+    for (unsigned int i = 0; i < desc->n_phases; ++i) {
+        const int rc = mb::prefill_validate(desc->phases[i], desc->n_slots, desc->n_dynamic);
+        if (rc != MB_OK) return rc;
+    }
+    DeviceGuard guard(desc->device);
+    if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
+    cudaDeviceProp prop;
+    MB_CUDA(cudaGetDeviceProperties(&prop, desc->device));
+    if (prop.major != 10) {
+        g_last_cuda_error = "device is not sm_100 (compute capability " +
+                            std::to_string(prop.major) + "." + std::to_string(prop.minor) + ")";
+        return MB_ERR_UNSUPPORTED;
+    }
+    mb_plan* plan = new (std::nothrow) mb_plan();
+    if (plan == nullptr) return MB_ERR_RESOURCE;
+    plan->device = desc->device;
+    plan->mode = desc->mode;
+    plan->phases.assign(desc->phases, desc->phases + desc->n_phases);
+    plan->slots.assign(desc->n_slots, 0ull);
+    plan->n_dynamic = desc->n_dynamic;
+    plan->sm_count = prop.multiProcessorCount;
+    plan->ctas = prop.multiProcessorCount;
+    cudaError_t err = cudaMalloc(&plan->d_ctl, sizeof(mb::Control));
+    if (err == cudaSuccess) err = cudaMemset(plan->d_ctl, 0, sizeof(mb::Control));
+    if (err == cudaSuccess) err = mb::prefill_create(plan->phases, plan->sm_count, &plan->prefill);
+    if (err != cudaSuccess) {
+        cuda_fail(err, "prefill plan allocation");
+        mb_plan_destroy(plan);
+        return MB_ERR_CUDA;
+    }
+    *out = plan;
+    return MB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -197,6 +235,7 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     if (desc->abi_version != MB_ABI_VERSION) return MB_ERR_VERSION;
     if (desc->n_phases == 0 || desc->phases == nullptr) return MB_ERR_INVALID;
     if (desc->n_dynamic > MB_MAX_DYNAMIC || desc->n_dynamic > desc->n_slots) return MB_ERR_INVALID;
+    if (desc->mode == MB_MODE_PREFILL) return create_prefill_plan(desc, out);
     if (desc->mode != MB_MODE_DECODE) return MB_ERR_UNSUPPORTED;
     if (desc->activation_bytes % 128 != 0) return MB_ERR_INVALID;
 
@@ -294,6 +333,17 @@ int mb_plan_bind(mb_plan* plan, const uint64_t* slot_addresses, size_t n) {
         if (slot_addresses[i] == 0 || (slot_addresses[i] & 15ull) != 0) return MB_ERR_INVALID;
         plan->slots[i] = slot_addresses[i];
     }
+    if (plan->mode == MB_MODE_PREFILL) {
+        DeviceGuard guard(plan->device);
+        if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
+        const int rc = mb::prefill_bind(plan->prefill, plan->phases, plan->slots, plan->d_ctl);
+        if (rc != MB_OK) {
+            g_last_cuda_error = "tensor map encoding failed";
+            return rc;
+        }
+        plan->bound = true;
+        return MB_OK;
+    }
     // Resolve every slot a phase names into its entry, so the kernel reads one record per
     // phase and never a second table.
     std::vector<mb::PhaseEntry> entries(plan->phases.size());
@@ -321,6 +371,17 @@ int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, v
     if (plan == nullptr) return MB_ERR_INVALID;
     if (!plan->bound) return MB_ERR_UNBOUND;
     if (n != plan->n_dynamic || (n > 0 && dynamic_addresses == nullptr)) return MB_ERR_INVALID;
+    if (plan->mode == MB_MODE_PREFILL) {
+        for (size_t i = 0; i < n; ++i)
+            if (dynamic_addresses[i] == 0 || (dynamic_addresses[i] & 7ull) != 0) return MB_ERR_INVALID;
+        DeviceGuard guard(plan->device);
+        if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
+        MB_CUDA(mb::prefill_launch(plan->prefill, plan->phases, plan->slots, plan->n_dynamic,
+                                   reinterpret_cast<const unsigned long long*>(dynamic_addresses),
+                                   plan->d_ctl,
+                                   static_cast<cudaStream_t>(stream)));
+        return MB_OK;
+    }
     mb::KernelParams params;
     std::memset(&params, 0, sizeof(params));
     params.entries = plan->d_entries;
@@ -380,6 +441,7 @@ void mb_plan_destroy(mb_plan* plan) {
         DeviceGuard guard(plan->device);
         if (plan->d_entries) cudaFree(plan->d_entries);
         if (plan->d_ctl) cudaFree(plan->d_ctl);
+        mb::prefill_destroy(plan->prefill);
     }
     delete plan;
 }

@@ -256,45 +256,6 @@ __device__ __forceinline__ const char* activation_row(const PhaseEntry* E, const
     return xbase + static_cast<size_t>(r) * K * 2;
 }
 
-__device__ __forceinline__ uint4 scale_vector(uint4 raw, float scale) {
-    raw.x = pack_bf16(lo_bf16(raw.x) * scale, hi_bf16(raw.x) * scale);
-    raw.y = pack_bf16(lo_bf16(raw.y) * scale, hi_bf16(raw.y) * scale);
-    raw.z = pack_bf16(lo_bf16(raw.z) * scale, hi_bf16(raw.z) * scale);
-    raw.w = pack_bf16(lo_bf16(raw.w) * scale, hi_bf16(raw.w) * scale);
-    return raw;
-}
-
-__device__ __forceinline__ float sum_squares(uint4 v) {
-    float s = 0.f;
-    const unsigned int w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float a = lo_bf16(w[q]), b = hi_bf16(w[q]);
-        s += a * a;
-        s += b * b;
-    }
-    return s;
-}
-
-__device__ __forceinline__ uint4 normalise_vector(uint4 x, uint4 w, float inv, int kind) {
-    unsigned int xv[4] = {x.x, x.y, x.z, x.w};
-    const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        float a = lo_bf16(xv[q]), b = hi_bf16(xv[q]);
-        const float wa = lo_bf16(wv[q]), wb = hi_bf16(wv[q]);
-        if (kind == MB_PRO_RMS_LLAMA) {
-            a = bf16_round(a * inv) * wa;
-            b = bf16_round(b * inv) * wb;
-        } else {
-            a = (a * inv) * (1.0f + wa);
-            b = (b * inv) * (1.0f + wb);
-        }
-        xv[q] = pack_bf16(a, b);
-    }
-    return make_uint4(xv[0], xv[1], xv[2], xv[3]);
-}
-
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)),
                  "l"(src_gmem)

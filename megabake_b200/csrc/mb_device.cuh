@@ -91,6 +91,47 @@ __device__ __forceinline__ unsigned int pack_bf16(float lo, float hi) {
            (static_cast<unsigned int>(float_to_bf16_bits(hi)) << 16);
 }
 
+// Eight bf16 values at a time (one 16-byte vector): embedding scale, sum of squares and the
+// two RMSNorm spellings.
+__device__ __forceinline__ uint4 scale_vector(uint4 raw, float scale) {
+    raw.x = pack_bf16(lo_bf16(raw.x) * scale, hi_bf16(raw.x) * scale);
+    raw.y = pack_bf16(lo_bf16(raw.y) * scale, hi_bf16(raw.y) * scale);
+    raw.z = pack_bf16(lo_bf16(raw.z) * scale, hi_bf16(raw.z) * scale);
+    raw.w = pack_bf16(lo_bf16(raw.w) * scale, hi_bf16(raw.w) * scale);
+    return raw;
+}
+
+__device__ __forceinline__ float sum_squares(uint4 v) {
+    float s = 0.f;
+    const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float a = lo_bf16(w[q]), b = hi_bf16(w[q]);
+        s += a * a;
+        s += b * b;
+    }
+    return s;
+}
+
+__device__ __forceinline__ uint4 normalise_vector(uint4 x, uint4 w, float inv, int kind) {
+    unsigned int xv[4] = {x.x, x.y, x.z, x.w};
+    const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float a = lo_bf16(xv[q]), b = hi_bf16(xv[q]);
+        const float wa = lo_bf16(wv[q]), wb = hi_bf16(wv[q]);
+        if (kind == MB_PRO_RMS_LLAMA) {
+            a = bf16_round(a * inv) * wa;
+            b = bf16_round(b * inv) * wb;
+        } else {
+            a = (a * inv) * (1.0f + wa);
+            b = (b * inv) * (1.0f + wb);
+        }
+        xv[q] = pack_bf16(a, b);
+    }
+    return make_uint4(xv[0], xv[1], xv[2], xv[3]);
+}
+
 // x / (1 + exp(-x)) with the operation order of the decomposed graph.
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
 // 0.5 * x * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))

@@ -2,6 +2,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <vector>
+
+#include "../../include/megabake_b200.h"
+
 namespace mb {
 struct KernelParams;
 
@@ -15,4 +19,17 @@ cudaError_t decode_configure(int smem_bytes);
 cudaError_t decode_occupancy(int smem_bytes, int* blocks_per_sm);
 cudaError_t decode_launch(const KernelParams& params, int ctas, int smem_bytes,
                           cudaStream_t stream);
+
+// Prefill plans (mb_prefill.cu): one kernel launch per phase.
+struct PrefillState;
+struct Control;
+int prefill_validate(const mb_phase& phase, unsigned int n_slots, unsigned int n_dynamic);
+cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillState** out);
+void prefill_destroy(PrefillState* state);
+int prefill_bind(PrefillState* state, const std::vector<mb_phase>& phases,
+                 const std::vector<unsigned long long>& slots, Control* ctl);
+cudaError_t prefill_launch(PrefillState* state, const std::vector<mb_phase>& phases,
+                           const std::vector<unsigned long long>& slots, unsigned int n_dynamic,
+                           const unsigned long long* dynamic_addresses, Control* ctl,
+                           cudaStream_t stream);
 }  // namespace mb

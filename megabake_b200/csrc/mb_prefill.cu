@@ -1,0 +1,1034 @@
+// Prefill path: one kernel launch per phase of an MB_MODE_PREFILL plan, enqueued in order on
+// the caller's stream (and captured as a whole by a CUDA graph when the caller does so).
+//
+//   embed_rows_kernel      gather of embedding rows (+ Gemma's bf16 scalar scale)
+//   rmsnorm_rows_kernel    row-wise RMSNorm, Llama and Gemma spellings
+//   gemm_tc_kernel         C[M, N] = A[M, K] . W[N, K]^T on the 5th-generation tensor cores:
+//                          TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring ->
+//                          tcgen05.mma issued by one thread, fp32 accumulators in tensor memory,
+//                          tcgen05.ld epilogue (bias / residual / gated activation), optional
+//                          split-K with a last-arriver reduction
+//   rope_rows_kernel       rotary embedding of q and k rows in place
+//   attention_prefill_kernel   masked softmax attention with the eager rounding points
+//
+// No load in this file uses cluster multicast.  Every wait is bounded and reports through
+// the plan's status word.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "mb_device.cuh"
+#include "mb_kernels.h"
+
+namespace mb {
+namespace prefill {
+
+// ---------------------------------------------------------------------------------------
+// Row kernels
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) embed_rows_kernel(const unsigned short* table,
+                                                         const long long* ids,
+                                                         unsigned short* out, int rows, int K,
+                                                         int vocab, float scale, Control* ctl,
+                                                         int phase) {
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    long long id = ids[r];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) record_status(ctl, MB_ST_TOKEN_RANGE, phase, r);
+        id = 0;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * K);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * K);
+    for (int v = threadIdx.x; v < K / 8; v += blockDim.x) {
+        uint4 raw = __ldg(src + v);
+        if (scale != 0.f) raw = scale_vector(raw, scale);
+        dst[v] = raw;
+    }
+}
+
+// One warp per row, two passes over the row (the second one hits L1/L2).
+__global__ void __launch_bounds__(128) rmsnorm_rows_kernel(const unsigned short* x,
+                                                           const unsigned short* w,
+                                                           unsigned short* out, int rows, int K,
+                                                           int kind, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= rows) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * K);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * K);
+    const uint4* wv = reinterpret_cast<const uint4*>(w);
+    float ss = 0.f;
+    for (int v = lane; v < K / 8; v += 32) ss += sum_squares(src[v]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
+    for (int v = lane; v < K / 8; v += 32) dst[v] = normalise_vector(src[v], __ldg(wv + v), inv, kind);
+}
+
+// Thread e rotates the element pair (i, i + D/2) of one head row, with the rounding points
+// of the eager graph: cos/sin tables in bf16, every product and the sum rounded to bf16.
+__global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsigned short* k,
+                                                        const long long* pos, const void* inv_freq,
+                                                        int rows, int heads, int kv_heads, int D,
+                                                        int invfreq_bf16, float rope_scale,
+                                                        float q_scale) {
+    const int half = D / 2;
+    const int per_row = (heads + kv_heads) * half;
+    const long long total = static_cast<long long>(rows) * per_row;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(e / per_row);
+        const int rem = static_cast<int>(e - static_cast<long long>(r) * per_row);
+        const int head = rem / half, i = rem - head * half;
+        const float f = invfreq_bf16
+                            ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(inv_freq)[i])
+                            : reinterpret_cast<const float*>(inv_freq)[i];
+        const float angle = static_cast<float>(pos[r]) * f;
+        float sn, cn;
+        sincosf(angle, &sn, &cn);
+        const float c = bf16_round(cn * rope_scale), s = bf16_round(sn * rope_scale);
+        const bool is_q = head < heads;
+        unsigned short* row = is_q ? q + (static_cast<size_t>(r) * heads + head) * D
+                                   : k + (static_cast<size_t>(r) * kv_heads + (head - heads)) * D;
+        const float x1 = bf16_bits_to_float(row[i]), x2 = bf16_bits_to_float(row[i + half]);
+        float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
+        float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+        if (is_q && q_scale != 0.f && q_scale != 1.f) {
+            r1 = bf16_round(r1 * q_scale);
+            r2 = bf16_round(r2 * q_scale);
+        }
+        row[i] = float_to_bf16_bits(r1);
+        row[i + half] = float_to_bf16_bits(r2);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// tcgen05 / TMA wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned int* slot_smem, unsigned int columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(slot_smem)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned int base, unsigned int columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// The mbarrier gets one arrival once every tcgen05.mma this thread issued before has finished.
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]^T, bf16 operands, fp32 accumulate, M = 128.
+__device__ __forceinline__ void umma_bf16(unsigned int tmem_d, unsigned long long desc_a,
+                                          unsigned long long desc_b, unsigned int idesc,
+                                          unsigned int accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+__device__ __forceinline__ unsigned long long umma_desc(unsigned int smem_addr) {
+    unsigned long long d = 0;
+    d |= static_cast<unsigned long long>((smem_addr & 0x3ffffu) >> 4);  // start address
+    d |= 1ull << 16;                                                     // leading byte offset (unused)
+    d |= static_cast<unsigned long long>(1024 >> 4) << 32;               // stride byte offset
+    d |= 1ull << 46;                                                     // descriptor version
+    d |= 2ull << 61;                                                     // SWIZZLE_128B
+    return d;
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_load32(unsigned int taddr, float (&v)[32]) {
+    unsigned int r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---------------------------------------------------------------------------------------
+// The GEMM
+// ---------------------------------------------------------------------------------------
+constexpr int kTileM = 128;
+constexpr int kTileK = 64;  // bf16 elements = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kStageA = kTileM * kTileK * 2;
+
+struct GemmMaps {
+    CUtensorMap a;
+    CUtensorMap w[4];  // segments 0..2, [3] = second matrix of a pair
+};
+
+struct GemmArgs {
+    int M, K, kblocks, split_k, stages, phase;
+    int nseg, pair, epilogue;
+    int n[3];
+    int tile_start[3];  // first n-tile of each segment
+    int tiles_n;        // n-tiles over all segments
+    unsigned short* out[3];
+    const unsigned short* bias[3];
+    const unsigned short* residual;
+    float* workspace;  // split-K partials [tile][split][128][BN] fp32
+    int* counters;     // split-K arrivals per tile, zero between launches
+    Control* ctl;
+};
+
+template <int BN>
+__device__ __forceinline__ void gemm_store_chunk(const GemmArgs& a, int seg, int row, int col0,
+                                                 int width, const float (&v)[32],
+                                                 const float (&u)[32]) {
+    // v: 32 accumulator columns starting at output column col0 of segment seg; u: the paired
+    // matrix's accumulators for the same columns (gated epilogues only)
+    const int n = a.n[seg];
+    unsigned short* out = a.out[seg] + static_cast<size_t>(row) * n;
+    const unsigned short* bias = a.bias[seg];
+    const unsigned short* res =
+        a.epilogue == MB_EPI_RESIDUAL ? a.residual + static_cast<size_t>(row) * n : nullptr;
+    unsigned int packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float y[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int col = col0 + i + j;
+            const bool live = i + j < width;
+            const float b = (bias != nullptr && live) ? bf16_bits_to_float(__ldg(bias + col)) : 0.f;
+            const float t = bf16_round(v[i + j] + b);
+            float result = t;
+            if (a.epilogue == MB_EPI_RESIDUAL)
+                result = (live ? bf16_bits_to_float(res[col]) : 0.f) + t;
+            else if (a.epilogue == MB_EPI_SILU_MUL)
+                result = bf16_round(silu_f32(t)) * bf16_round(u[i + j]);
+            else if (a.epilogue == MB_EPI_GELU_TANH_MUL)
+                result = bf16_round(gelu_tanh_f32(t)) * bf16_round(u[i + j]);
+            y[j] = result;
+        }
+        packed[i / 2] = pack_bf16(y[0], y[1]);
+    }
+    if (width == 32 && (n & 7) == 0) {
+        uint4* dst = reinterpret_cast<uint4*>(out + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    } else {
+        for (int i = 0; i < width; ++i)
+            out[col0 + i] = static_cast<unsigned short>(i & 1 ? packed[i / 2] >> 16 : packed[i / 2] & 0xffffu);
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
+    constexpr int kStageW = BN * kTileK * 2;
+    constexpr int kStage = kStageA + kStageW;
+    constexpr int kHalf = BN / 2;  // columns per matrix of a gated pair
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + a.stages * kStage);
+    unsigned long long* empty = full + 8;
+    unsigned long long* accum = empty + 8;
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(accum + 1);
+    int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    int* last_flag = abort_flag + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, mt = blockIdx.y, z = blockIdx.z;
+    const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
+    const int per_tile = a.pair ? kHalf : BN;  // output columns of one n-tile
+    const int n0 = (tile - a.tile_start[seg]) * per_tile;
+    const int m0 = mt * kTileM;
+    const int kb0 = static_cast<int>(static_cast<long long>(z) * a.kblocks / a.split_k);
+    const int kb1 = static_cast<int>(static_cast<long long>(z + 1) * a.kblocks / a.split_k);
+    const int nkb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned int tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % a.stages;
+                if (it >= a.stages &&
+                    !mbar_wait_bounded(&empty[s], ((it / a.stages) - 1) & 1, abort_flag)) {
+                    record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 1);
+                    *abort_flag = 1;
+                    break;
+                }
+                unsigned char* stage = smem + s * kStage;
+                mbar_arrive_expect_tx(&full[s], kStage);
+                const int kx = (kb0 + it) * kTileK;
+                tma_load_2d(stage, &maps.a, kx, m0, &full[s]);
+                if (a.pair) {
+                    tma_load_2d(stage + kStageA, &maps.w[0], kx, n0, &full[s]);
+                    tma_load_2d(stage + kStageA + kHalf * kTileK * 2, &maps.w[3], kx, n0, &full[s]);
+                } else {
+                    tma_load_2d(stage + kStageA, &maps.w[seg], kx, n0, &full[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major,
+            // N = BN, M = 128
+            const unsigned int idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       (static_cast<unsigned int>(BN >> 3) << 17) |
+                                       (static_cast<unsigned int>(kTileM >> 4) << 24);
+            bool ok = true;
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % a.stages;
+                if (!mbar_wait_bounded(&full[s], (it / a.stages) & 1, abort_flag)) {
+                    record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 2);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const unsigned int base = smem_u32(smem + s * kStage);
+                const unsigned long long da = umma_desc(base);
+                const unsigned long long db = umma_desc(base + kStageA);
+#pragma unroll
+                for (int k = 0; k < kTileK / 16; ++k)  // 32 bytes along K per step: +2 encoded
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+                umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ...
+        const int row_in_tile = quarter * 32 + lane;
+        const int row = m0 + row_in_tile;
+        // `ok` is warp-uniform: the tcgen05.ld below must be executed by whole warps
+        bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum, 0, abort_flag));
+        if (!ok) {
+            if (lane == 0) record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 3);
+            *abort_flag = 1;
+        }
+        tc_fence_after();
+        const unsigned int lane_addr = tmem_base + (static_cast<unsigned int>(quarter * 32) << 16);
+        const int chunks = per_tile / 32;
+        const int tile_id = mt * a.tiles_n + tile;
+        if (ok && a.split_k > 1) {
+            // park this CTA's partial sums; the CTA that arrives last adds them up in split
+            // order (so the result does not depend on arrival order) and runs the epilogue
+            float* mine = a.workspace +
+                          (static_cast<size_t>(tile_id) * a.split_k + z) * (kTileM * BN) +
+                          static_cast<size_t>(row_in_tile) * BN;
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_load32(lane_addr + c * 32, v);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    __stcg(reinterpret_cast<float4*>(mine + c * 32) + q,
+                           make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+            }
+            __threadfence();
+            named_barrier(1, 128);
+            if (warp == 2 && lane == 0) {
+                const int arrived = atomicAdd(a.counters + tile_id, 1);
+                *last_flag = arrived == a.split_k - 1 ? 1 : 0;
+                if (arrived == a.split_k - 1) a.counters[tile_id] = 0;  // re-arm for the next launch
+                __threadfence();
+            }
+            named_barrier(1, 128);
+            ok = *last_flag != 0;
+        }
+        if (ok) {
+            const float* parts = a.workspace + static_cast<size_t>(tile_id) * a.split_k * (kTileM * BN) +
+                                 static_cast<size_t>(row_in_tile) * BN;
+            for (int c = 0; c < chunks; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= a.n[seg]) break;
+                const int width = min(32, a.n[seg] - col0);
+                float v[32], u[32];
+                if (a.split_k > 1) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = u[i] = 0.f;
+                    for (int s = 0; s < a.split_k; ++s) {
+                        const float* p = parts + static_cast<size_t>(s) * (kTileM * BN);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 t = __ldcg(reinterpret_cast<const float4*>(p + c * 32) + q);
+                            v[4 * q] += t.x, v[4 * q + 1] += t.y, v[4 * q + 2] += t.z, v[4 * q + 3] += t.w;
+                        }
+                        if (a.pair) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 t =
+                                    __ldcg(reinterpret_cast<const float4*>(p + kHalf + c * 32) + q);
+                                u[4 * q] += t.x, u[4 * q + 1] += t.y, u[4 * q + 2] += t.z, u[4 * q + 3] += t.w;
+                            }
+                        }
+                    }
+                } else {
+                    tmem_load32(lane_addr + c * 32, v);
+                    if (a.pair)
+                        tmem_load32(lane_addr + kHalf + c * 32, u);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) u[i] = 0.f;
+                    }
+                }
+                if (row < a.M) gemm_store_chunk<BN>(a, seg, row, col0, width, v, u);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // copies this CTA issued may still be landing in its shared memory: give them time
+        const unsigned long long start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Prefill attention.  One CTA (4 warps) per 64 query rows of one head; keys in blocks of 64.
+// Two sweeps over the visible keys so that the probabilities can be rounded to bf16 *after*
+// normalisation, as the eager operator does: sweep 1 finds each row's maximum and
+// denominator, sweep 2 recomputes the scores, forms p = bf16(exp(s - max) / sum) and
+// accumulates p . V.  Scores carry the operator's rounding points:
+// s = bf16(q . k); s = bf16(s * scale); s = bf16(s + mask).
+// ---------------------------------------------------------------------------------------
+struct AttnArgs {
+    const unsigned short* q;
+    const unsigned short* k;
+    const unsigned short* v;
+    unsigned short* out;
+    const unsigned short* mask;  // additive, [mask_batch, 1, T, T], or null
+    int batch, tokens, heads, kv_heads, causal, mask_batch;
+    float scale;
+};
+
+constexpr int kAttnRows = 64;
+constexpr int kAttnKeys = 64;
+constexpr int kAttnThreads = 128;
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned int (&r)[4], const void* smem_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_ptr)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned int (&r)[4], const void* smem_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_ptr)));
+}
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src)
+                 : "memory");
+}
+
+template <int D>
+__device__ __forceinline__ void attn_load_rows(unsigned short* dst, const unsigned short* src,
+                                               size_t row_stride, int row0, int limit) {
+    // 64 rows of D bf16 each into a tile with pitch D + 8; rows past `limit` repeat the last one
+    constexpr int kVectors = D / 8;
+    for (int e = threadIdx.x; e < kAttnRows * kVectors; e += kAttnThreads) {
+        const int r = e / kVectors, c = e - r * kVectors;
+        const int row = min(row0 + r, limit - 1);
+        cp_async_16(dst + r * (D + 8) + c * 8, src + static_cast<size_t>(row) * row_stride + c * 8);
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void attn_scores(float (&sacc)[8][4], const unsigned short* Qs,
+                                            const unsigned short* Ks, int warp, int lane) {
+    constexpr int P = D + 8;
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) sacc[t][q] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned int a[4];
+        ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * P + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            unsigned int b[4];
+            ldmatrix_x4(b, Ks + (np * 16 + ((lane >> 4) & 1) * 8 + (lane & 7)) * P + kk * 16 +
+                               ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(sacc[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+            mma_bf16_16816(sacc[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+        }
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(const AttnArgs a) {
+    constexpr int P = D + 8;
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    unsigned short* Qs = reinterpret_cast<unsigned short*>(attn_smem);
+    unsigned short* Ks = Qs + kAttnRows * P;
+    unsigned short* Vs = Ks + kAttnKeys * P;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tq = lane & 3;
+    const int T = a.tokens;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvh = head / (a.heads / a.kv_heads);
+    const int q0 = qt * kAttnRows;
+    const size_t q_stride = static_cast<size_t>(a.heads) * D;
+    const size_t kv_stride = static_cast<size_t>(a.kv_heads) * D;
+    const unsigned short* qbase = a.q + static_cast<size_t>(b) * T * q_stride + head * D;
+    const unsigned short* kbase = a.k + static_cast<size_t>(b) * T * kv_stride + kvh * D;
+    const unsigned short* vbase = a.v + static_cast<size_t>(b) * T * kv_stride + kvh * D;
+    const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
+    const int nblocks = a.causal ? min(qt + 1, all_blocks) : all_blocks;
+    const int row_lo = q0 + warp * 16 + gid, row_hi = row_lo + 8;
+    const unsigned short* mask_lo = nullptr;
+    const unsigned short* mask_hi = nullptr;
+    if (a.mask != nullptr) {
+        const unsigned short* mb = a.mask + (a.mask_batch > 1 ? static_cast<size_t>(b) * T * T : 0);
+        mask_lo = mb + static_cast<size_t>(min(row_lo, T - 1)) * T;
+        mask_hi = mb + static_cast<size_t>(min(row_hi, T - 1)) * T;
+    }
+
+    attn_load_rows<D>(Qs, qbase, q_stride, q0, T);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    // score of (row, key) with the operator's rounding points; false if the key is not visible
+    auto score = [&](float acc, int row, int key, const unsigned short* mrow, float* s) {
+        float t = bf16_round(acc);
+        t = bf16_round(t * a.scale);
+        if (mrow != nullptr && key < T) t = bf16_round(t + bf16_bits_to_float(__ldg(mrow + key)));
+        *s = t;
+        return key < T && (!a.causal || key <= row);
+    };
+
+    // ---- sweep 1: row maxima and denominators --------------------------------------------
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    for (int jb = 0; jb < nblocks; ++jb) {
+        __syncthreads();  // everybody is done with the previous key block
+        attn_load_rows<D>(Ks, kbase, kv_stride, jb * kAttnKeys, T);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float sacc[8][4];
+        attn_scores<D>(sacc, Qs, Ks, warp, lane);
+        float s_lo[16], s_hi[16];
+        float bm_lo = -INFINITY, bm_hi = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
+                float s;
+                s_lo[2 * t + j] = score(sacc[t][j], row_lo, key, mask_lo, &s) ? s : -INFINITY;
+                s_hi[2 * t + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s) ? s : -INFINITY;
+                bm_lo = fmaxf(bm_lo, s_lo[2 * t + j]);
+                bm_hi = fmaxf(bm_hi, s_hi[2 * t + j]);
+            }
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+            bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, o));
+            bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, o));
+        }
+        const float n_lo = fmaxf(m_lo, bm_lo), n_hi = fmaxf(m_hi, bm_hi);
+        // a row with no visible key yet keeps max = -inf; exp(-inf - -inf) must not be formed
+        l_lo = n_lo == -INFINITY ? 0.f : l_lo * expf(m_lo - n_lo);
+        l_hi = n_hi == -INFINITY ? 0.f : l_hi * expf(m_hi - n_hi);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (s_lo[i] != -INFINITY) l_lo += expf(s_lo[i] - n_lo);
+            if (s_hi[i] != -INFINITY) l_hi += expf(s_hi[i] - n_hi);
+        }
+        m_lo = n_lo;
+        m_hi = n_hi;
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, o);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, o);
+    }
+
+    // ---- sweep 2: probabilities and p . V -------------------------------------------------
+    float oacc[D / 8][4];
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) oacc[t][q] = 0.f;
+    for (int jb = 0; jb < nblocks; ++jb) {
+        __syncthreads();
+        attn_load_rows<D>(Ks, kbase, kv_stride, jb * kAttnKeys, T);
+        attn_load_rows<D>(Vs, vbase, kv_stride, jb * kAttnKeys, T);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float sacc[8][4];
+        attn_scores<D>(sacc, Qs, Ks, warp, lane);
+        unsigned int pfrag[4][4];  // A fragments of P for the four 16-key steps
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            float p[4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
+                float s;
+                p[j] = score(sacc[t][j], row_lo, key, mask_lo, &s) ? __fdiv_rn(expf(s - m_lo), l_lo) : 0.f;
+                p[2 + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s) ? __fdiv_rn(expf(s - m_hi), l_hi) : 0.f;
+            }
+            pfrag[t >> 1][(t & 1) * 2] = pack_bf16(p[0], p[1]);
+            pfrag[t >> 1][(t & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                unsigned int vb[4];
+                ldmatrix_x4_trans(vb, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * P +
+                                          dp * 16 + (lane >> 4) * 8);
+                mma_bf16_16816(oacc[2 * dp], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2], pfrag[kk][3],
+                               vb[0], vb[1]);
+                mma_bf16_16816(oacc[2 * dp + 1], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2],
+                               pfrag[kk][3], vb[2], vb[3]);
+            }
+        }
+    }
+
+    unsigned short* obase = a.out + static_cast<size_t>(b) * T * q_stride + head * D;
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t) {
+        const int d = t * 8 + 2 * tq;
+        if (row_lo < T)
+            *reinterpret_cast<unsigned int*>(obase + static_cast<size_t>(row_lo) * q_stride + d) =
+                pack_bf16(oacc[t][0], oacc[t][1]);
+        if (row_hi < T)
+            *reinterpret_cast<unsigned int*>(obase + static_cast<size_t>(row_hi) * q_stride + d) =
+                pack_bf16(oacc[t][2], oacc[t][3]);
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Host side: validation, tile / split-K geometry, tensor maps, launches.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) ==
+                cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [rows, K] bf16 row-major, boxes of `box_rows` x 64 elements, 128-byte swizzle, zero fill
+// outside the tensor.
+bool make_map(CUtensorMap* map, unsigned long long base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(base), dims,
+              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int gemm_smem_bytes(int bn, int stages) {
+    return stages * (kStageA + bn * kTileK * 2) + 256 + 1024;  // ring + barriers + alignment slack
+}
+
+struct GemmGeometry {
+    int bn, stages, tiles_n, tiles_m, split_k, kblocks;
+    int tile_start[3];
+};
+
+GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
+    GemmGeometry g;
+    const int M = P.i[MB_GV_I_ROWS], K = P.i[MB_GV_I_K];
+    const bool pair = P.i[MB_GV_I_NMAT] == 2;
+    g.tiles_m = (M + kTileM - 1) / kTileM;
+    g.kblocks = (K + kTileK - 1) / kTileK;
+    // wide tiles once there are enough of them to fill the machine; they halve the shared-
+    // memory traffic per flop
+    auto count = [&](int bn) {
+        int tiles = 0;
+        const int per = pair ? bn / 2 : bn;
+        for (int s = 0; s < P.i[MB_GV_I_NSEG]; ++s) tiles += (P.i[MB_GV_I_N0 + s] + per - 1) / per;
+        return tiles;
+    };
+    g.bn = count(256) * g.tiles_m >= sm_count ? 256 : 128;
+    g.stages = g.bn == 256 ? 4 : 6;
+    const int per = pair ? g.bn / 2 : g.bn;
+    int tiles = 0;
+    for (int s = 0; s < 3; ++s) {
+        g.tile_start[s] = s < P.i[MB_GV_I_NSEG] ? tiles : INT_MAX;
+        if (s < P.i[MB_GV_I_NSEG]) tiles += (P.i[MB_GV_I_N0 + s] + per - 1) / per;
+    }
+    g.tiles_n = tiles;
+    // split the reduction when the output tiles alone leave most SMs idle
+    int split = 1;
+    const int ctas = g.tiles_n * g.tiles_m;
+    if (ctas * 2 <= sm_count) {
+        split = sm_count / ctas;
+        if (split > g.kblocks / 4) split = g.kblocks / 4;
+        if (split > 16) split = 16;
+        if (split < 1) split = 1;
+    }
+    g.split_k = split;
+    return g;
+}
+
+}  // namespace
+
+struct PrefillLaunch {
+    int body = MB_BODY_NOP;
+    GemmMaps maps;
+    GemmArgs gemm;
+    GemmGeometry geometry;
+    AttnArgs attn;
+};
+
+}  // namespace prefill
+
+struct PrefillState {
+    std::vector<prefill::PrefillLaunch> launches;
+    float* workspace = nullptr;
+    int* counters = nullptr;
+    size_t workspace_floats = 0;
+    size_t counter_count = 0;
+    int sm_count = 0;
+};
+
+int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dynamic) {
+    auto slot_ok = [&](int s, bool required, bool may_be_dynamic) {
+        if (s < 0) return !required;
+        if (static_cast<unsigned int>(s) >= n_slots) return false;
+        return may_be_dynamic || static_cast<unsigned int>(s) >= n_dynamic;
+    };
+    switch (P.body) {
+        case MB_BODY_NOP:
+            return MB_OK;
+        case MB_BODY_EMBED_ROWS:
+            if (P.i[MB_EM_I_ROWS] < 1 || P.i[MB_EM_I_K] < 8 || P.i[MB_EM_I_K] % 8 ||
+                P.i[MB_EM_I_VOCAB] < 1)
+                return MB_ERR_INVALID;
+            if (!slot_ok(P.slot[MB_EM_S_TABLE], true, false) ||
+                !slot_ok(P.slot[MB_EM_S_IDS], true, true) || !slot_ok(P.slot[MB_EM_S_OUT], true, false))
+                return MB_ERR_INVALID;
+            return MB_OK;
+        case MB_BODY_RMSNORM_ROWS:
+            if (P.i[MB_RN_I_ROWS] < 1 || P.i[MB_RN_I_K] < 8 || P.i[MB_RN_I_K] % 8)
+                return MB_ERR_INVALID;
+            if (P.i[MB_RN_I_KIND] != MB_PRO_RMS_LLAMA && P.i[MB_RN_I_KIND] != MB_PRO_RMS_GEMMA)
+                return MB_ERR_INVALID;
+            for (int s = 0; s < 3; ++s)
+                if (!slot_ok(P.slot[s], true, false)) return MB_ERR_INVALID;
+            return MB_OK;
+        case MB_BODY_GEMM_TC: {
+            const int nseg = P.i[MB_GV_I_NSEG], nmat = P.i[MB_GV_I_NMAT], epi = P.i[MB_GV_I_EPILOGUE];
+            if (P.i[MB_GV_I_ROWS] < 1 || P.i[MB_GV_I_K] < 8 || P.i[MB_GV_I_K] % 8) return MB_ERR_INVALID;
+            if (nseg < 1 || nseg > 3 || (nmat != 1 && nmat != 2)) return MB_ERR_INVALID;
+            if (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE || P.i[MB_GV_I_GATHER] != 0)
+                return MB_ERR_UNSUPPORTED;
+            const bool gated = epi == MB_EPI_SILU_MUL || epi == MB_EPI_GELU_TANH_MUL;
+            if (gated != (nmat == 2) || (nmat == 2 && nseg != 1)) return MB_ERR_INVALID;
+            if (epi < MB_EPI_NONE || epi > MB_EPI_GELU_TANH_MUL) return MB_ERR_INVALID;
+            if (!slot_ok(P.slot[MB_GV_S_X], true, false)) return MB_ERR_INVALID;
+            for (int s = 0; s < nseg; ++s) {
+                if (P.i[MB_GV_I_N0 + s] < 1) return MB_ERR_INVALID;
+                if (!slot_ok(P.slot[MB_GV_S_W0 + s], true, false) ||
+                    !slot_ok(P.slot[MB_GV_S_OUT0 + s], true, false) ||
+                    !slot_ok(P.slot[MB_GV_S_BIAS0 + s], false, false))
+                    return MB_ERR_INVALID;
+            }
+            if (nmat == 2 && !slot_ok(P.slot[MB_GV_S_W_PAIR], true, false)) return MB_ERR_INVALID;
+            if (epi == MB_EPI_RESIDUAL &&
+                (nseg != 1 || !slot_ok(P.slot[MB_GV_S_RESIDUAL], true, false)))
+                return MB_ERR_INVALID;
+            return MB_OK;
+        }
+        case MB_BODY_ROPE_ROWS: {
+            const int D = P.i[MB_RP_I_HEAD_DIM];
+            if (P.i[MB_RP_I_ROWS] < 1 || P.i[MB_RP_I_HEADS] < 1 || P.i[MB_RP_I_KV_HEADS] < 1 ||
+                D < 2 || D % 2)
+                return MB_ERR_INVALID;
+            for (int s = 0; s < 4; ++s)
+                if (!slot_ok(P.slot[s], true, false)) return MB_ERR_INVALID;
+            return MB_OK;
+        }
+        case MB_BODY_ATTN_PREFILL: {
+            const int D = P.i[MB_AP_I_HEAD_DIM];
+            if (D != 64 && D != 128 && D != 256) return MB_ERR_UNSUPPORTED;
+            if (P.i[MB_AP_I_BATCH] < 1 || P.i[MB_AP_I_TOKENS] < 1 || P.i[MB_AP_I_HEADS] < 1 ||
+                P.i[MB_AP_I_KV_HEADS] < 1 || P.i[MB_AP_I_HEADS] % P.i[MB_AP_I_KV_HEADS])
+                return MB_ERR_INVALID;
+            if (P.i[MB_AP_I_BATCH] > 65535 || P.i[MB_AP_I_HEADS] > 65535) return MB_ERR_UNSUPPORTED;
+            for (int s = 0; s < 4; ++s)
+                if (!slot_ok(P.slot[s], true, false)) return MB_ERR_INVALID;
+            if (!slot_ok(P.slot[MB_AP_S_MASK], false, false)) return MB_ERR_INVALID;
+            if (P.slot[MB_AP_S_MASK] >= 0 && P.i[MB_AP_I_MASK_BATCH] != 1 &&
+                P.i[MB_AP_I_MASK_BATCH] != P.i[MB_AP_I_BATCH])
+                return MB_ERR_INVALID;
+            return MB_OK;
+        }
+        default:
+            return MB_ERR_UNSUPPORTED;
+    }
+}
+
+// Creates the per-plan state: geometry of every GEMM (written back into the phase records so
+// that mb_plan users can read it) and the split-K workspace.
+cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillState** out) {
+    using namespace prefill;
+    PrefillState* st = new (std::nothrow) PrefillState();
+    if (st == nullptr) return cudaErrorMemoryAllocation;
+    st->sm_count = sm_count;
+    st->launches.resize(phases.size());
+    size_t floats = 0, counters = 0;
+    for (size_t i = 0; i < phases.size(); ++i) {
+        mb_phase& P = phases[i];
+        st->launches[i].body = P.body;
+        if (P.body != MB_BODY_GEMM_TC) continue;
+        GemmGeometry g = gemm_geometry(P, sm_count);
+        st->launches[i].geometry = g;
+        P.i[MB_GV_I_SPLIT_K] = g.split_k;
+        P.i[MB_GV_I_TILE_N] = g.bn;
+        const size_t tiles = static_cast<size_t>(g.tiles_n) * g.tiles_m;
+        if (g.split_k > 1) {
+            const size_t need = tiles * g.split_k * kTileM * g.bn;
+            if (need > floats) floats = need;
+            if (tiles > counters) counters = tiles;
+        }
+    }
+    cudaError_t err = cudaSuccess;
+    if (floats > 0) {
+        err = cudaMalloc(&st->workspace, floats * sizeof(float));
+        if (err == cudaSuccess) err = cudaMalloc(&st->counters, counters * sizeof(int));
+        if (err == cudaSuccess) err = cudaMemset(st->counters, 0, counters * sizeof(int));
+    }
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   gemm_smem_bytes(128, 6));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   gemm_smem_bytes(256, 4));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_prefill_kernel<128>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (128 + 8) * 2);
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_prefill_kernel<256>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (256 + 8) * 2);
+    if (err != cudaSuccess) {
+        prefill_destroy(st);
+        return err;
+    }
+    st->workspace_floats = floats;
+    st->counter_count = counters;
+    *out = st;
+    return cudaSuccess;
+}
+
+void prefill_destroy(PrefillState* st) {
+    if (st == nullptr) return;
+    if (st->workspace != nullptr) cudaFree(st->workspace);
+    if (st->counters != nullptr) cudaFree(st->counters);
+    delete st;
+}
+
+// Resolves the static addresses of every phase into launch arguments and tensor maps.
+int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
+                 const std::vector<unsigned long long>& slots, Control* ctl) {
+    using namespace prefill;
+    auto addr = [&](int s) -> unsigned long long { return s < 0 ? 0ull : slots[s]; };
+    for (size_t i = 0; i < phases.size(); ++i) {
+        const mb_phase& P = phases[i];
+        PrefillLaunch& L = st->launches[i];
+        if (P.body == MB_BODY_GEMM_TC) {
+            const GemmGeometry& g = L.geometry;
+            GemmArgs& a = L.gemm;
+            std::memset(&a, 0, sizeof(a));
+            a.M = P.i[MB_GV_I_ROWS];
+            a.K = P.i[MB_GV_I_K];
+            a.kblocks = g.kblocks;
+            a.split_k = g.split_k;
+            a.stages = g.stages;
+            a.phase = static_cast<int>(i);
+            a.nseg = P.i[MB_GV_I_NSEG];
+            a.pair = P.i[MB_GV_I_NMAT] == 2 ? 1 : 0;
+            a.epilogue = P.i[MB_GV_I_EPILOGUE];
+            a.tiles_n = g.tiles_n;
+            for (int s = 0; s < 3; ++s) {
+                a.n[s] = s < a.nseg ? P.i[MB_GV_I_N0 + s] : 0;
+                a.tile_start[s] = g.tile_start[s];
+                a.out[s] = reinterpret_cast<unsigned short*>(addr(s < a.nseg ? P.slot[MB_GV_S_OUT0 + s] : -1));
+                a.bias[s] = reinterpret_cast<const unsigned short*>(
+                    addr(s < a.nseg ? P.slot[MB_GV_S_BIAS0 + s] : -1));
+            }
+            a.residual = reinterpret_cast<const unsigned short*>(
+                addr(a.epilogue == MB_EPI_RESIDUAL ? P.slot[MB_GV_S_RESIDUAL] : -1));
+            a.workspace = st->workspace;
+            a.counters = st->counters;
+            a.ctl = ctl;
+            if (!make_map(&L.maps.a, addr(P.slot[MB_GV_S_X]), a.M, a.K, kTileM)) return MB_ERR_CUDA;
+            const int box = a.pair ? g.bn / 2 : g.bn;
+            for (int s = 0; s < a.nseg; ++s)
+                if (!make_map(&L.maps.w[s], addr(P.slot[MB_GV_S_W0 + s]), a.n[s], a.K, box))
+                    return MB_ERR_CUDA;
+            if (a.pair &&
+                !make_map(&L.maps.w[3], addr(P.slot[MB_GV_S_W_PAIR]), a.n[0], a.K, box))
+                return MB_ERR_CUDA;
+        } else if (P.body == MB_BODY_ATTN_PREFILL) {
+            AttnArgs& a = L.attn;
+            a.q = reinterpret_cast<const unsigned short*>(addr(P.slot[MB_AP_S_Q]));
+            a.k = reinterpret_cast<const unsigned short*>(addr(P.slot[MB_AP_S_K]));
+            a.v = reinterpret_cast<const unsigned short*>(addr(P.slot[MB_AP_S_V]));
+            a.out = reinterpret_cast<unsigned short*>(addr(P.slot[MB_AP_S_OUT]));
+            a.mask = reinterpret_cast<const unsigned short*>(addr(P.slot[MB_AP_S_MASK]));
+            a.batch = P.i[MB_AP_I_BATCH];
+            a.tokens = P.i[MB_AP_I_TOKENS];
+            a.heads = P.i[MB_AP_I_HEADS];
+            a.kv_heads = P.i[MB_AP_I_KV_HEADS];
+            a.causal = P.i[MB_AP_I_CAUSAL];
+            a.mask_batch = P.i[MB_AP_I_MASK_BATCH];
+            a.scale = P.f[MB_AP_F_SCALE];
+        }
+    }
+    return MB_OK;
+}
+
+// Enqueues every phase in order.  Dynamic slots (token ids) are resolved here on the host.
+cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases,
+                           const std::vector<unsigned long long>& slots, unsigned int n_dynamic,
+                           const unsigned long long* dyn, Control* ctl, cudaStream_t stream) {
+    using namespace prefill;
+    auto addr = [&](int s) -> unsigned long long {
+        if (s < 0) return 0ull;
+        return static_cast<unsigned int>(s) < n_dynamic ? dyn[s] : slots[s];
+    };
+    for (size_t i = 0; i < phases.size(); ++i) {
+        const mb_phase& P = phases[i];
+        const PrefillLaunch& L = st->launches[i];
+        switch (P.body) {
+            case MB_BODY_EMBED_ROWS:
+                embed_rows_kernel<<<P.i[MB_EM_I_ROWS], 128, 0, stream>>>(
+                    reinterpret_cast<const unsigned short*>(addr(P.slot[MB_EM_S_TABLE])),
+                    reinterpret_cast<const long long*>(addr(P.slot[MB_EM_S_IDS])),
+                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_EM_S_OUT])), P.i[MB_EM_I_ROWS],
+                    P.i[MB_EM_I_K], P.i[MB_EM_I_VOCAB], P.f[MB_EM_F_SCALE], ctl, static_cast<int>(i));
+                break;
+            case MB_BODY_RMSNORM_ROWS:
+                rmsnorm_rows_kernel<<<(P.i[MB_RN_I_ROWS] + 3) / 4, 128, 0, stream>>>(
+                    reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_X])),
+                    reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_W])),
+                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_RN_S_OUT])), P.i[MB_RN_I_ROWS],
+                    P.i[MB_RN_I_K], P.i[MB_RN_I_KIND], P.f[MB_RN_F_EPS]);
+                break;
+            case MB_BODY_GEMM_TC: {
+                const GemmGeometry& g = L.geometry;
+                const dim3 grid(g.tiles_n, g.tiles_m, g.split_k);
+                if (g.bn == 256)
+                    gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem_bytes(256, g.stages), stream>>>(
+                        L.maps, L.gemm);
+                else
+                    gemm_tc_kernel<128><<<grid, kGemmThreads, gemm_smem_bytes(128, g.stages), stream>>>(
+                        L.maps, L.gemm);
+                break;
+            }
+            case MB_BODY_ROPE_ROWS: {
+                const long long work = static_cast<long long>(P.i[MB_RP_I_ROWS]) *
+                                       (P.i[MB_RP_I_HEADS] + P.i[MB_RP_I_KV_HEADS]) *
+                                       (P.i[MB_RP_I_HEAD_DIM] / 2);
+                long long blocks = (work + 255) / 256;
+                if (blocks > 4 * 148 * 8) blocks = 4 * 148 * 8;
+                rope_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_Q])),
+                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_K])),
+                    reinterpret_cast<const long long*>(addr(P.slot[MB_RP_S_POS])),
+                    reinterpret_cast<const void*>(addr(P.slot[MB_RP_S_INVFREQ])), P.i[MB_RP_I_ROWS],
+                    P.i[MB_RP_I_HEADS], P.i[MB_RP_I_KV_HEADS], P.i[MB_RP_I_HEAD_DIM],
+                    P.i[MB_RP_I_INVFREQ_BF16], P.f[MB_RP_F_ROPE_SCALE], P.f[MB_RP_F_Q_SCALE]);
+                break;
+            }
+            case MB_BODY_ATTN_PREFILL: {
+                const int D = P.i[MB_AP_I_HEAD_DIM];
+                const dim3 grid((P.i[MB_AP_I_TOKENS] + kAttnRows - 1) / kAttnRows, P.i[MB_AP_I_HEADS],
+                                P.i[MB_AP_I_BATCH]);
+                const int smem = 3 * 64 * (D + 8) * 2;
+                if (D == 64)
+                    attention_prefill_kernel<64><<<grid, kAttnThreads, smem, stream>>>(L.attn);
+                else if (D == 128)
+                    attention_prefill_kernel<128><<<grid, kAttnThreads, smem, stream>>>(L.attn);
+                else
+                    attention_prefill_kernel<256><<<grid, kAttnThreads, smem, stream>>>(L.attn);
+                break;
+            }
+            default:
+                break;
+        }
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace mb

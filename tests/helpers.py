@@ -40,10 +40,11 @@ class PhaseRunner:
         self.tensors.append(tensor)
         return self.names[name]
 
-    def run(self, phases, activation_bytes: int, ctas: int = 0) -> rt.Plan:
+    def run(self, phases, activation_bytes: int = 0, ctas: int = 0,
+            mode: int = rt.MODE_DECODE) -> rt.Plan:
         plan = rt.Plan(list(phases), n_slots=len(self.tensors), n_dynamic=0,
                        activation_bytes=(activation_bytes + 127) // 128 * 128,
-                       device=self.device.index or 0, ctas=ctas)
+                       device=self.device.index or 0, ctas=ctas, mode=mode)
         plan.bind([t.data_ptr() for t in self.tensors])
         plan.launch([], torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
