@@ -797,7 +797,7 @@ int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dyn
             for (int s = 0; s < nseg; ++s) {
                 if (P.i[MB_GV_I_N0 + s] < 1) return MB_ERR_INVALID;
                 if (!slot_ok(P.slot[MB_GV_S_W0 + s], true, false) ||
-                    !slot_ok(P.slot[MB_GV_S_OUT0 + s], true, false) ||
+                    !slot_ok(P.slot[MB_GV_S_OUT0 + s], true, true) ||
                     !slot_ok(P.slot[MB_GV_S_BIAS0 + s], false, false))
                     return MB_ERR_INVALID;
             }
@@ -813,7 +813,7 @@ int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dyn
                 D < 2 || D % 2)
                 return MB_ERR_INVALID;
             for (int s = 0; s < 4; ++s)
-                if (!slot_ok(P.slot[s], true, false)) return MB_ERR_INVALID;
+                if (!slot_ok(P.slot[s], true, s == MB_RP_S_POS)) return MB_ERR_INVALID;
             return MB_OK;
         }
         case MB_BODY_ATTN_PREFILL: {
@@ -986,12 +986,15 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
             case MB_BODY_GEMM_TC: {
                 const GemmGeometry& g = L.geometry;
                 const dim3 grid(g.tiles_n, g.tiles_m, g.split_k);
+                GemmArgs args = L.gemm;
+                for (int s = 0; s < args.nseg; ++s)  // outputs may be per-launch tensors (logits)
+                    args.out[s] = reinterpret_cast<unsigned short*>(addr(P.slot[MB_GV_S_OUT0 + s]));
                 if (g.bn == 256)
                     gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem_bytes(256, g.stages), stream>>>(
-                        L.maps, L.gemm);
+                        L.maps, args);
                 else
                     gemm_tc_kernel<128><<<grid, kGemmThreads, gemm_smem_bytes(128, g.stages), stream>>>(
-                        L.maps, L.gemm);
+                        L.maps, args);
                 break;
             }
             case MB_BODY_ROPE_ROWS: {

@@ -57,6 +57,14 @@ class BoundDecoder:
             self.plan = rt.Plan(layout.phases, n_slots=len(layout.slots), n_dynamic=3,
                                 activation_bytes=layout.activation_bytes,
                                 device=self.device.index or 0, mode=layout.mode, ctas=ctas)
+            # tensors the plan itself owns: a non-causal mask, and the positions 0..T-1 of
+            # every row when the captured graph held them as constants
+            self._constants = {name: tensor.to(self.device)
+                               for name, tensor in layout.constants.items()}
+            self._positions = None
+            if p.position_ids is None:
+                self._positions = torch.arange(p.tokens, dtype=torch.int64,
+                                               device=self.device).repeat(p.batch)
         self._static_positions = sorted({s.index for s in layout.slots if s.kind == "arg"})
         self._bound_objects: dict[int, torch.Tensor] = {}
         self._bound_pointers: dict[int, int] = {}
@@ -67,7 +75,9 @@ class BoundDecoder:
     # -- binding -------------------------------------------------------------------------
     def _metadata(self, args: Sequence[torch.Tensor]):
         used = {s.index for s in self.layout.slots if s.kind == "arg"}
-        used |= {self.program.input_ids, self.program.position_ids}
+        used |= {self.program.input_ids}
+        if self.program.position_ids is not None:
+            used.add(self.program.position_ids)
         return {i: (tuple(args[i].shape), args[i].dtype, args[i].device) for i in used}
 
     def _zero_workspace(self) -> None:
@@ -109,6 +119,8 @@ class BoundDecoder:
                 table.append(0)
             elif spec.kind == "arg":
                 table.append(self._bound_pointers[spec.index])
+            elif spec.kind == "constant":
+                table.append(self._constants[spec.name].data_ptr())
             else:
                 table.append(base + spec.offset)
         self.plan.bind(table)
@@ -117,9 +129,13 @@ class BoundDecoder:
     def __call__(self, *args: torch.Tensor) -> torch.Tensor:
         p = self.program
         with self._lock:
-            ids, positions = args[p.input_ids], args[p.position_ids]
+            ids = args[p.input_ids]
             self._check_tensor(p.input_ids, ids, align=8)
-            self._check_tensor(p.position_ids, positions, align=8)
+            if p.position_ids is None:
+                positions = self._positions
+            else:
+                positions = args[p.position_ids]
+                self._check_tensor(p.position_ids, positions, align=8)
             self._rebind(args)
             logits = torch.empty((p.batch, p.tokens, p.vocab), dtype=torch.bfloat16,
                                  device=self.device)

@@ -209,6 +209,46 @@ def direct_program(spec: ModelSpec, batch: int, capacity: int) -> DecoderProgram
     )
 
 
+def direct_prefill_arguments(spec: ModelSpec, weights: dict[str, torch.Tensor],
+                             inv_freq: torch.Tensor, input_ids: torch.Tensor) -> list[torch.Tensor]:
+    """Argument list of ``direct_prefill_program``: input_ids, inv_freq, then the weights."""
+    return [input_ids, inv_freq, *[weights[name] for name, _ in parameter_shapes(spec)]]
+
+
+def direct_prefill_program(spec: ModelSpec, batch: int, tokens: int) -> DecoderProgram:
+    """Causal prefill of ``[batch, tokens]`` ids at positions 0..tokens-1 (held by the plan)."""
+    names = [name for name, _ in parameter_shapes(spec)]
+    where = {name: 2 + index for index, name in enumerate(names)}
+    layers = []
+    for index in range(spec.layers):
+        prefix = f"model.layers.{index}."
+        layers.append(LayerBinding(
+            input_norm=where[prefix + "input_layernorm.weight"],
+            q_weight=where[prefix + "self_attn.q_proj.weight"],
+            k_weight=where[prefix + "self_attn.k_proj.weight"],
+            v_weight=where[prefix + "self_attn.v_proj.weight"],
+            o_weight=where[prefix + "self_attn.o_proj.weight"],
+            post_norm=where[prefix + "post_attention_layernorm.weight"],
+            gate_weight=where[prefix + "mlp.gate_proj.weight"],
+            up_weight=where[prefix + "mlp.up_proj.weight"],
+            down_weight=where[prefix + "mlp.down_proj.weight"],
+            key_cache=-1, value_cache=-1, valid_length=-1,
+            q_bias=where.get(prefix + "self_attn.q_proj.bias"),
+            k_bias=where.get(prefix + "self_attn.k_proj.bias"),
+            v_bias=where.get(prefix + "self_attn.v_proj.bias"),
+        ))
+    return DecoderProgram(
+        mode="prefill", batch=batch, tokens=tokens, hidden=spec.hidden, heads=spec.heads,
+        kv_heads=spec.kv_heads, head_dim=spec.head_dim, intermediate=spec.intermediate,
+        vocab=spec.vocab, capacity=0, norm=spec.norm, eps=spec.eps,
+        activation=spec.activation, embed_scale=spec.embed_scale, rope_scale=1.0, q_scale=None,
+        softmax_scale=spec.head_dim**-0.5, inv_freq_dtype="bf16",
+        input_ids=0, position_ids=None, embed_weight=where["model.embed_tokens.weight"],
+        inv_freq=1, final_norm=where["model.norm.weight"],
+        lm_head_weight=where["model.embed_tokens.weight"], layers=tuple(layers), causal=True,
+    )
+
+
 def make_state(spec: ModelSpec, batch: int, capacity: int, device: str | torch.device = "cpu",
                ) -> list[torch.Tensor]:
     state = []

@@ -41,7 +41,7 @@ MAX_GEMV_ROWS = 8
 
 @dataclass(frozen=True)
 class SlotSpec:
-    kind: str  # "dynamic" | "arg" | "workspace"
+    kind: str  # "dynamic" | "arg" | "workspace" | "constant" (tensor in PlanLayout.constants)
     index: int = 0  # argument position, or dynamic ordinal
     offset: int = 0  # byte offset into the workspace
     name: str = ""
@@ -58,6 +58,7 @@ class PlanLayout:
     intervals: int
     notes: list[str] = field(default_factory=list)
     mode: int = rt.MODE_DECODE
+    constants: dict = field(default_factory=dict)  # name -> CPU tensor uploaded at bind
 
 
 @dataclass(frozen=True)
@@ -106,6 +107,10 @@ class _Slots:
         if zero:
             self.zero.append((offset, nbytes))
         self.specs.append(SlotSpec("workspace", offset=offset, name=name))
+        return len(self.specs) - 1
+
+    def constant(self, name: str) -> int:
+        self.specs.append(SlotSpec("constant", name=name))
         return len(self.specs) - 1
 
 
@@ -344,3 +349,138 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
                f"attention: max_chunks={max_chunks} merge_slots={merge_slots} "
                f"exact_keys={exact_keys}"],
     )
+
+
+def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
+                 mask=None) -> PlanLayout:
+    """Prefill packing: one kernel launch per phase, in stream order (no grid barriers).
+
+        [embed rows]                                   (layer 0)
+        [rmsnorm rows] [q|k|v GEMM (+bias)] [rope rows] [attention] [o GEMM + residual]
+        [rmsnorm rows] [gate|up GEMM . act(gate) * up] [down GEMM + residual]      x layers
+        [rmsnorm rows] [lm head GEMM]
+
+    GEMMs run on tcgen05 with TMA-fed operands, so their activations must sit in memory: the
+    norms are phases of their own here (a [rows, hidden] round trip through L2, negligible
+    next to the weights), while bias, residual and the gated activation stay in the GEMM
+    epilogues.  ``mask`` is an additive bf16 ``[1 or B, 1, T, T]`` tensor for a non-causal
+    program (``program.causal`` False); causal programs need none.
+    """
+    del options
+    p = program
+    if p.mode != "prefill":
+        fail("planning", f"plan_prefill got a {p.mode!r} program")
+    if p.head_dim not in (64, 128, 256):
+        fail("resource-admission", f"head_dim {p.head_dim} not in (64, 128, 256)")
+    if p.heads % p.kv_heads:
+        fail("resource-admission", "query heads must be a multiple of kv heads")
+    for name, value in (("hidden", p.hidden), ("intermediate", p.intermediate)):
+        if value % 8:
+            fail("resource-admission", f"{name} size {value} is not a multiple of 8")
+    if p.norm not in ("llama", "gemma") or p.activation not in ("silu", "gelu_tanh"):
+        fail("planning", "unknown norm or activation kind")
+    if not p.causal and mask is None:
+        fail("planning", "a non-causal prefill program needs its mask tensor")
+    B, T, H, D = p.batch, p.tokens, p.hidden, p.head_dim
+    R = B * T
+    q_dim, kv_dim = p.heads * D, p.kv_heads * D
+    slots = _Slots()
+    kind = rt.PRO_RMS_LLAMA if p.norm == "llama" else rt.PRO_RMS_GEMMA
+    act = rt.EPI_SILU_MUL if p.activation == "silu" else rt.EPI_GELU_TANH_MUL
+    hidden = slots.buffer(R * H * 2, "hidden")
+    normed = slots.buffer(R * H * 2, "normed")
+    q_buf = slots.buffer(R * q_dim * 2, "q")
+    k_buf = slots.buffer(R * kv_dim * 2, "k")
+    v_buf = slots.buffer(R * kv_dim * 2, "v")
+    attn = slots.buffer(R * q_dim * 2, "attention")
+    glu = slots.buffer(R * p.intermediate * 2, "gated")
+    constants = {}
+    mask_slot = -1
+    if not p.causal:
+        mask_slot = slots.constant("mask")
+        constants["mask"] = mask.contiguous()
+    phases: list[rt.Phase] = []
+
+    def norm(weight_slot):
+        phase = rt.Phase.blank(rt.BODY_RMSNORM_ROWS, 0)
+        phase.i[rt.RN_I_ROWS], phase.i[rt.RN_I_K], phase.i[rt.RN_I_KIND] = R, H, kind
+        phase.f[rt.RN_F_EPS] = p.eps
+        phase.slot[rt.RN_S_X], phase.slot[rt.RN_S_W], phase.slot[rt.RN_S_OUT] = hidden, weight_slot, normed
+        phases.append(phase)
+
+    def gemm(*, k, x_slot, segments, epilogue=rt.EPI_NONE, pair_slot=-1, residual_slot=-1):
+        phase = rt.Phase.blank(rt.BODY_GEMM_TC, 0)
+        phase.i[rt.GV_I_ROWS] = R
+        phase.i[rt.GV_I_K] = k
+        phase.i[rt.GV_I_NSEG] = len(segments)
+        phase.i[rt.GV_I_NMAT] = 2 if pair_slot >= 0 else 1
+        phase.i[rt.GV_I_EPILOGUE] = epilogue
+        phase.slot[rt.GV_S_X] = x_slot
+        for index, (n, weight, bias, out) in enumerate(segments):
+            phase.i[rt.GV_I_N0 + index] = n
+            phase.slot[rt.GV_S_W0 + index] = weight
+            phase.slot[rt.GV_S_BIAS0 + index] = bias
+            phase.slot[rt.GV_S_OUT0 + index] = out
+        phase.slot[rt.GV_S_W_PAIR] = pair_slot
+        phase.slot[rt.GV_S_RESIDUAL] = residual_slot
+        phases.append(phase)
+
+    embed = rt.Phase.blank(rt.BODY_EMBED_ROWS, 0)
+    embed.i[rt.EM_I_ROWS], embed.i[rt.EM_I_K], embed.i[rt.EM_I_VOCAB] = R, H, p.vocab
+    embed.f[rt.EM_F_SCALE] = float(p.embed_scale or 0.0)
+    embed.slot[rt.EM_S_TABLE] = slots.arg(p.embed_weight, "embed_tokens.weight")
+    embed.slot[rt.EM_S_IDS] = DYN_INPUT_IDS
+    embed.slot[rt.EM_S_OUT] = hidden
+    phases.append(embed)
+    inv_freq = slots.arg(p.inv_freq, "inv_freq")
+    for index, layer in enumerate(p.layers):
+        tag = f"layers.{index}."
+        norm(slots.arg(layer.input_norm, tag + "input_layernorm.weight"))
+        gemm(k=H, x_slot=normed, segments=[
+            (q_dim, slots.arg(layer.q_weight, tag + "q_proj.weight"),
+             slots.arg(layer.q_bias, tag + "q_proj.bias"), q_buf),
+            (kv_dim, slots.arg(layer.k_weight, tag + "k_proj.weight"),
+             slots.arg(layer.k_bias, tag + "k_proj.bias"), k_buf),
+            (kv_dim, slots.arg(layer.v_weight, tag + "v_proj.weight"),
+             slots.arg(layer.v_bias, tag + "v_proj.bias"), v_buf),
+        ])
+        rope = rt.Phase.blank(rt.BODY_ROPE_ROWS, 0)
+        rope.i[rt.RP_I_ROWS], rope.i[rt.RP_I_HEADS], rope.i[rt.RP_I_KV_HEADS] = R, p.heads, p.kv_heads
+        rope.i[rt.RP_I_HEAD_DIM] = D
+        rope.i[rt.RP_I_INVFREQ_BF16] = 1 if p.inv_freq_dtype == "bf16" else 0
+        rope.f[rt.RP_F_ROPE_SCALE] = p.rope_scale
+        rope.f[rt.RP_F_Q_SCALE] = float(p.q_scale or 0.0)
+        rope.slot[rt.RP_S_Q], rope.slot[rt.RP_S_K] = q_buf, k_buf
+        rope.slot[rt.RP_S_POS], rope.slot[rt.RP_S_INVFREQ] = DYN_POSITION_IDS, inv_freq
+        phases.append(rope)
+        attention = rt.Phase.blank(rt.BODY_ATTN_PREFILL, 0)
+        attention.i[rt.AP_I_BATCH], attention.i[rt.AP_I_TOKENS] = B, T
+        attention.i[rt.AP_I_HEADS], attention.i[rt.AP_I_KV_HEADS] = p.heads, p.kv_heads
+        attention.i[rt.AP_I_HEAD_DIM] = D
+        attention.i[rt.AP_I_CAUSAL] = 1 if p.causal else 0
+        attention.i[rt.AP_I_MASK_BATCH] = 1 if mask is None else int(mask.shape[0])
+        attention.f[rt.AP_F_SCALE] = p.softmax_scale
+        attention.slot[rt.AP_S_Q], attention.slot[rt.AP_S_K], attention.slot[rt.AP_S_V] = q_buf, k_buf, v_buf
+        attention.slot[rt.AP_S_OUT], attention.slot[rt.AP_S_MASK] = attn, mask_slot
+        phases.append(attention)
+        gemm(k=q_dim, x_slot=attn, epilogue=rt.EPI_RESIDUAL, residual_slot=hidden, segments=[
+            (H, slots.arg(layer.o_weight, tag + "o_proj.weight"),
+             slots.arg(layer.o_bias, tag + "o_proj.bias"), hidden)])
+        if layer.gate_bias is not None or layer.up_bias is not None:
+            fail("pattern-recognition", "biased gate/up projections are not covered")
+        norm(slots.arg(layer.post_norm, tag + "post_attention_layernorm.weight"))
+        gemm(k=H, x_slot=normed, epilogue=act,
+             pair_slot=slots.arg(layer.up_weight, tag + "up_proj.weight"),
+             segments=[(p.intermediate, slots.arg(layer.gate_weight, tag + "gate_proj.weight"), -1, glu)])
+        gemm(k=p.intermediate, x_slot=glu, epilogue=rt.EPI_RESIDUAL, residual_slot=hidden, segments=[
+            (H, slots.arg(layer.down_weight, tag + "down_proj.weight"),
+             slots.arg(layer.down_bias, tag + "down_proj.bias"), hidden)])
+    norm(slots.arg(p.final_norm, "norm.weight"))
+    gemm(k=H, x_slot=normed, segments=[
+        (p.vocab, slots.arg(p.lm_head_weight, "lm_head.weight"),
+         slots.arg(p.lm_head_bias, "lm_head.bias"), DYN_LOGITS)])
+    return PlanLayout(
+        program=p, phases=phases, slots=slots.specs,
+        workspace_bytes=_align(slots.workspace, 256), zero_ranges=[], activation_bytes=0,
+        intervals=len(phases), notes=[f"{len(phases)} kernel launches per prefill"],
+        mode=rt.MODE_PREFILL, constants=constants)

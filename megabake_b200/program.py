@@ -63,7 +63,7 @@ class DecoderProgram:
     softmax_scale: float
     inv_freq_dtype: str  # "bf16" | "f32"
     input_ids: int
-    position_ids: int
+    position_ids: int | None  # None (prefill only): positions 0..tokens-1, held by the plan
     embed_weight: int
     inv_freq: int
     final_norm: int
