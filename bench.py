@@ -50,9 +50,28 @@ WORKLOADS = {
     "smollm-1.7b-b1-k8192": ("smollm-1.7b", 1, 8192),
     "smollm-1.7b-b8-k8192": ("smollm-1.7b", 8, 8192),
 }
+# prefill workloads: name -> (model preset, batch, prompt tokens)
+PREFILL_WORKLOADS = {
+    "gemma-2b-prefill-t128": ("gemma-2b", 1, 128),
+    "gemma-2b-prefill-t512": ("gemma-2b", 1, 512),
+    "gemma-2b-prefill-t2048": ("gemma-2b", 1, 2048),
+    "smollm-135m-prefill-t128": ("smollm-135m", 1, 128),
+}
 DEFAULT_WORKLOAD = "qwen2-0.5b-b8-k4096"
 METRIC = "decode_us_per_token"
 UNIT = "us/token"
+
+
+def measured_tensor_peak() -> tuple[float, str]:
+    """Dense bf16 TFLOP/s a library GEMM sustains on this pool's B200s (a prefill step is a
+    long run of GEMMs under the power cap, so the sustained figure is the denominator)."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops_sustained"]), "measured sustained"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -202,9 +221,195 @@ def cpu_reference_run(name: str, steps: int, warmup: int, budget_s: float, rank:
     }
 
 
+def prefill_flops(spec, tokens: int) -> tuple[float, float]:
+    """(GEMM flops, attention flops) of one causal prefill of ``tokens`` positions, batch 1:
+    every projection and the LM head at every position; attention as 4 * T^2 * Hq * D * L."""
+    q_dim, kv_dim = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+    per_layer = (q_dim * spec.hidden + 2 * kv_dim * spec.hidden + spec.hidden * q_dim
+                 + 3 * spec.hidden * spec.intermediate)
+    params = spec.layers * per_layer + spec.vocab * spec.hidden
+    return 2.0 * params * tokens, 4.0 * tokens * tokens * q_dim * spec.layers
+
+
+def cpu_prefill_run(name: str, steps: int, budget_s: float) -> dict:
+    """Time the CPU port of the reference prefill forward on this box's host cores."""
+    import torch
+
+    from megabake_b200 import models
+    from oracle import decoder_oracle as oracle
+    from oracle.adapters import oracle_config, oracle_weights
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    preset, batch, tokens = PREFILL_WORKLOADS[name]
+    spec = models.get_spec(preset)
+    weights = models.init_weights(spec, seed=0)
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    ids = torch.randint(0, spec.vocab, (batch, tokens), generator=torch.Generator().manual_seed(7))
+    times = []
+    started = time.perf_counter()
+    with torch.no_grad():
+        for _ in range(max(steps, 1)):
+            t0 = time.perf_counter()
+            oracle.prefill(cfg, ow, ids)
+            times.append(time.perf_counter() - t0)
+            if time.perf_counter() - started > budget_s:
+                break
+    per_step = statistics.median(times)
+    return {
+        "value": batch * tokens / per_step, "unit": "tok/s", "cores": cores, "kind": "port",
+        "sample": f"{len(times)} prefill(s) of {name} (median), CPU port of the reference eager "
+                  f"forward, {cores} threads",
+        "ms_per_step": per_step * 1e3, "steps": len(times),
+    }
+
+
+def run_prefill(args) -> None:
+    import torch
+
+    from megabake_b200 import models
+    from megabake_b200.engine import BoundDecoder
+    from megabake_b200.planner import plan_prefill
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU execution path "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    preset, batch, tokens = PREFILL_WORKLOADS[args.workload]
+    spec = models.get_spec(preset)
+    weights = models.init_weights(spec, seed=rank, device=device)
+    inv_freq = models.inv_freq_buffer(spec, device)
+    layout = plan_prefill(models.direct_prefill_program(spec, batch, tokens))
+    host_ids = torch.randint(0, spec.vocab, (batch, tokens),
+                             generator=torch.Generator().manual_seed(7 + rank)).pin_memory()
+    ids = host_ids.to(device)
+    call_args = models.direct_prefill_arguments(spec, weights, inv_freq, ids)
+    bound = BoundDecoder(layout, call_args)
+    logits = torch.empty(batch, tokens, spec.vocab, dtype=torch.bfloat16, device=device)
+    positions = bound._positions
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        bound.launch_into(ids, positions, logits)
+    bound.check()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        start.record()
+        for _ in range(steps):
+            bound.launch_into(ids, positions, logits)
+        stop.record()
+        barrier()
+    bound.check()
+    device_ms = start.elapsed_time(stop)
+
+    # end to end through the bound callable: pinned host ids -> device, the prefill, greedy pick
+    # of the last position read back to the host, synchronised every step
+    e2e_s = None
+    if not args.skip_e2e:
+        host_pick = torch.zeros(batch, dtype=torch.int64).pin_memory()
+
+        def e2e_step():
+            ids.copy_(host_ids, non_blocking=True)
+            out = bound(*call_args)
+            host_pick.copy_(out[:, -1].argmax(-1), non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(warmup):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        bound.check()
+
+    times = torch.tensor([device_ms, (e2e_s or 0.0) * 1e3], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_ms, e2e_ms = (float(x) for x in times.cpu())
+    if rank == 0:
+        peak, peak_kind = measured_tensor_peak()
+        ms_per_step = device_ms / steps
+        gemm_flops, attn_flops = prefill_flops(spec, tokens)
+        gemm_flops *= batch
+        attn_flops *= batch
+        achieved = gemm_flops / (ms_per_step * 1e-3) / 1e12
+        launches = len(layout.phases)
+        line = {
+            "metric": "prefill_tokens_per_s", "value": batch * tokens * world / (ms_per_step * 1e-3),
+            "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": args.workload, "model": spec.name, "batch_per_gpu": batch,
+                "prompt_tokens": tokens, "replicas": world, "parallelism": f"dp{world} replicas",
+                "weights": "seeded N(0,0.02) random init, tied embeddings",
+                "l2": f"inputs larger than L2: {2 * gemm_flops / (2 * tokens * batch) / 1e6:.0f} MB "
+                      "of weights read per step vs 126 MB L2",
+                "kernel_launches_per_step": launches,
+                "attention_tflop_per_step": attn_flops / 1e12,
+            },
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": f"{peak_kind} cuBLAS bf16 GEMM",
+                "algorithmic_flops_per_step": gemm_flops,
+                "note": "GEMM flops of the whole step (projections + LM head at every position) "
+                        "over the whole step time, attention and row kernels included in the time",
+            },
+            "e2e": None if e2e_s is None else {
+                "value": batch * tokens * world / (e2e_ms * 1e-3 / steps), "unit": "tok/s",
+                "h2d_bytes_per_step": batch * tokens * 8, "d2h_bytes_per_step": batch * 8,
+                "ms_per_step": e2e_ms / steps,
+                "path": "BoundDecoder call of the prefill plan (allocates the logits) + torch argmax "
+                        "of the last position, synchronised every step",
+            },
+            "gpu_launches": steps * launches,
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base = cpu_prefill_run(args.workload, 3, budget_s=25.0)
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if args.workload in PREFILL_WORKLOADS:
+        result = cpu_prefill_run(args.workload, args.steps, budget_s=120.0)
+        preset, batch, tokens = PREFILL_WORKLOADS[args.workload]
+        print(json.dumps({
+            "impl": "reference", "metric": "prefill_tokens_per_s", "value": result["value"],
+            "unit": "tok/s", "n_gpus": args.gpus, "steps": result["steps"], "warmup": 0,
+            "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "model": preset, "batch": batch,
+                       "prompt_tokens": tokens, "device": "host cpu"},
+            "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": result["value"], "unit": "tok/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }), flush=True)
         return
     result = cpu_reference_run(args.workload, args.steps, min(args.warmup, 2), budget_s=120.0)
     preset, batch, keys = WORKLOADS[args.workload]
@@ -398,7 +603,8 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD,
+                        choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true",
@@ -408,6 +614,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in PREFILL_WORKLOADS:
+        run_prefill(args)
     else:
         run_ours(args)
 

@@ -378,7 +378,7 @@ int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, v
         if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
         MB_CUDA(mb::prefill_launch(plan->prefill, plan->phases, plan->slots, plan->n_dynamic,
                                    reinterpret_cast<const unsigned long long*>(dynamic_addresses),
-                                   plan->d_ctl,
+                                   plan->d_ctl, reinterpret_cast<unsigned long long*>(plan->trace),
                                    static_cast<cudaStream_t>(stream)));
         return MB_OK;
     }
@@ -419,7 +419,9 @@ int mb_plan_status(mb_plan* plan, mb_status* out) {
 int mb_plan_set_trace(mb_plan* plan, uint64_t device_address, size_t bytes) {
     if (plan == nullptr) return MB_ERR_INVALID;
     if (device_address != 0) {
-        const size_t need = static_cast<size_t>(plan->ctas) * plan->phases.size() * 8 * sizeof(uint64_t);
+        // decode: 8 stamps per CTA and phase; prefill: 8 stamps per phase (CTA 0 of each GEMM)
+        const size_t per_phase = plan->mode == MB_MODE_PREFILL ? 1 : static_cast<size_t>(plan->ctas);
+        const size_t need = per_phase * plan->phases.size() * 8 * sizeof(uint64_t);
         if (bytes < need || (device_address & 7ull) != 0) return MB_ERR_INVALID;
     }
     plan->trace = device_address;

@@ -31,5 +31,5 @@ int prefill_bind(PrefillState* state, const std::vector<mb_phase>& phases,
 cudaError_t prefill_launch(PrefillState* state, const std::vector<mb_phase>& phases,
                            const std::vector<unsigned long long>& slots, unsigned int n_dynamic,
                            const unsigned long long* dynamic_addresses, Control* ctl,
-                           cudaStream_t stream);
+                           unsigned long long* trace, cudaStream_t stream);
 }  // namespace mb

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <climits>
+#include <cstdlib>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -208,48 +209,72 @@ struct GemmArgs {
     float* workspace;  // split-K partials [tile][split][128][BN] fp32
     int* counters;     // split-K arrivals per tile, zero between launches
     Control* ctl;
+    unsigned long long* trace;  // optional: 8 global-timer stamps of CTA (0, 0, 0), or null
 };
 
-template <int BN>
-__device__ __forceinline__ void gemm_store_chunk(const GemmArgs& a, int seg, int row, int col0,
-                                                 int width, const float (&v)[32],
-                                                 const float (&u)[32]) {
-    // v: 32 accumulator columns starting at output column col0 of segment seg; u: the paired
-    // matrix's accumulators for the same columns (gated epilogues only)
-    const int n = a.n[seg];
-    unsigned short* out = a.out[seg] + static_cast<size_t>(row) * n;
+// Epilogue, step 1: 32 accumulator columns of this thread's row -> bf16 results in the
+// staging tile (shared memory, the drained operand ring).  v: accumulators of output columns
+// col0.. of segment seg; u: the paired matrix's accumulators for the same columns (gated
+// epilogues only).  The residual is added in step 2, where rows are read back coalesced.
+__device__ __forceinline__ void gemm_stage_chunk(const GemmArgs& a, int seg, int col0, int width,
+                                                 const float (&v)[32], const float (&u)[32],
+                                                 unsigned char* stage_row) {
     const unsigned short* bias = a.bias[seg];
-    const unsigned short* res =
-        a.epilogue == MB_EPI_RESIDUAL ? a.residual + static_cast<size_t>(row) * n : nullptr;
-    unsigned int packed[16];
+    // one uniform branch per chunk, not per element: the activation functions are long and
+    // must not be evaluated speculatively for epilogues that do not use them
+    float y[32];
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        float y[2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int col = col0 + i + j;
-            const bool live = i + j < width;
-            const float b = (bias != nullptr && live) ? bf16_bits_to_float(__ldg(bias + col)) : 0.f;
-            const float t = bf16_round(v[i + j] + b);
-            float result = t;
-            if (a.epilogue == MB_EPI_RESIDUAL)
-                result = (live ? bf16_bits_to_float(res[col]) : 0.f) + t;
-            else if (a.epilogue == MB_EPI_SILU_MUL)
-                result = bf16_round(silu_f32(t)) * bf16_round(u[i + j]);
-            else if (a.epilogue == MB_EPI_GELU_TANH_MUL)
-                result = bf16_round(gelu_tanh_f32(t)) * bf16_round(u[i + j]);
-            y[j] = result;
-        }
-        packed[i / 2] = pack_bf16(y[0], y[1]);
+    for (int i = 0; i < 32; ++i) {
+        const float b = (bias != nullptr && i < width) ? bf16_bits_to_float(__ldg(bias + col0 + i)) : 0.f;
+        y[i] = bf16_round(v[i] + b);
     }
-    if (width == 32 && (n & 7) == 0) {
-        uint4* dst = reinterpret_cast<uint4*>(out + col0);
+    if (a.epilogue == MB_EPI_SILU_MUL) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-    } else {
-        for (int i = 0; i < width; ++i)
-            out[col0 + i] = static_cast<unsigned short>(i & 1 ? packed[i / 2] >> 16 : packed[i / 2] & 0xffffu);
+        for (int i = 0; i < 32; ++i) y[i] = bf16_round(silu_f32(y[i])) * bf16_round(u[i]);
+    } else if (a.epilogue == MB_EPI_GELU_TANH_MUL) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = bf16_round(gelu_tanh_f32(y[i])) * bf16_round(u[i]);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(stage_row);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(pack_bf16(y[8 * q], y[8 * q + 1]), pack_bf16(y[8 * q + 2], y[8 * q + 3]),
+                            pack_bf16(y[8 * q + 4], y[8 * q + 5]), pack_bf16(y[8 * q + 6], y[8 * q + 7]));
+}
+
+// Epilogue, step 2: a warp writes the 32 rows it staged, 16 bytes per lane along the row.
+__device__ __forceinline__ void gemm_write_rows(const GemmArgs& a, int seg, int row0, int n0,
+                                                int per_tile, const unsigned char* stage,
+                                                int pitch, int lane) {
+    const int n = a.n[seg];
+    unsigned short* out = a.out[seg];
+    const unsigned short* res = a.epilogue == MB_EPI_RESIDUAL ? a.residual : nullptr;
+    const int vectors = per_tile / 8;
+    for (int idx = lane; idx < 32 * vectors; idx += 32) {
+        const int r = idx / vectors, c = (idx - r * vectors) * 8;
+        const int row = row0 + r, col = n0 + c;
+        if (row >= a.M || col >= n) continue;
+        uint4 t = *reinterpret_cast<const uint4*>(stage + r * pitch + c * 2);
+        const size_t at = static_cast<size_t>(row) * n + col;
+        if ((n & 7) == 0) {
+            if (res != nullptr) {
+                const uint4 h = *reinterpret_cast<const uint4*>(res + at);
+                t.x = pack_bf16(lo_bf16(h.x) + lo_bf16(t.x), hi_bf16(h.x) + hi_bf16(t.x));
+                t.y = pack_bf16(lo_bf16(h.y) + lo_bf16(t.y), hi_bf16(h.y) + hi_bf16(t.y));
+                t.z = pack_bf16(lo_bf16(h.z) + lo_bf16(t.z), hi_bf16(h.z) + hi_bf16(t.z));
+                t.w = pack_bf16(lo_bf16(h.w) + lo_bf16(t.w), hi_bf16(h.w) + hi_bf16(t.w));
+            }
+            *reinterpret_cast<uint4*>(out + at) = t;
+        } else {
+            const unsigned int w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (col + i >= n) break;
+                float y = i & 1 ? hi_bf16(w[i / 2]) : lo_bf16(w[i / 2]);
+                if (res != nullptr) y = bf16_bits_to_float(res[at + i]) + y;
+                out[at + i] = float_to_bf16_bits(y);
+            }
+        }
     }
 }
 
@@ -270,7 +295,14 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     int* last_flag = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, mt = blockIdx.y, z = blockIdx.z;
+    const bool traced = a.trace != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+    auto stamp = [&](int slot) {
+        if (traced) a.trace[slot] = global_timer_ns();
+    };
+    if (threadIdx.x == 0) stamp(0);
+    // m-tiles vary fastest: CTAs that run together share the same weight tile (read from HBM
+    // once) and differ in the activation tile, which stays in L2
+    const int mt = blockIdx.x, tile = blockIdx.y, z = blockIdx.z;
     const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
     const int per_tile = a.pair ? kHalf : BN;  // output columns of one n-tile
     const int n0 = (tile - a.tile_start[seg]) * per_tile;
@@ -294,6 +326,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     __syncthreads();
     tc_fence_after();
     const unsigned int tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) stamp(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -335,6 +368,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
                     break;
                 }
                 tc_fence_after();
+                if (it == 0) stamp(2);
                 const unsigned int base = smem_u32(smem + s * kStage);
                 const unsigned long long da = umma_desc(base);
                 const unsigned long long db = umma_desc(base + kStageA);
@@ -344,12 +378,12 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
                 umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(accum);
+            stamp(3);
         }
         __syncwarp();
     } else {
         const int quarter = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ...
         const int row_in_tile = quarter * 32 + lane;
-        const int row = m0 + row_in_tile;
         // `ok` is warp-uniform: the tcgen05.ld below must be executed by whole warps
         bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum, 0, abort_flag));
         if (!ok) {
@@ -357,22 +391,22 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             *abort_flag = 1;
         }
         tc_fence_after();
+        if (threadIdx.x == 64) stamp(4);
         const unsigned int lane_addr = tmem_base + (static_cast<unsigned int>(quarter * 32) << 16);
         const int chunks = per_tile / 32;
         const int tile_id = mt * a.tiles_n + tile;
         if (ok && a.split_k > 1) {
             // park this CTA's partial sums; the CTA that arrives last adds them up in split
             // order (so the result does not depend on arrival order) and runs the epilogue
+            // layout [tile][split][column][row]: a warp's 32 rows are contiguous, so every
+            // store and every load of the reduction is one 128-byte line per warp
             float* mine = a.workspace +
-                          (static_cast<size_t>(tile_id) * a.split_k + z) * (kTileM * BN) +
-                          static_cast<size_t>(row_in_tile) * BN;
+                          (static_cast<size_t>(tile_id) * a.split_k + z) * (kTileM * BN) + row_in_tile;
             for (int c = 0; c < BN / 32; ++c) {
                 float v[32];
                 tmem_load32(lane_addr + c * 32, v);
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    __stcg(reinterpret_cast<float4*>(mine + c * 32) + q,
-                           make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                for (int i = 0; i < 32; ++i) __stcg(mine + (c * 32 + i) * kTileM, v[i]);
             }
             __threadfence();
             named_barrier(1, 128);
@@ -386,8 +420,12 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
             ok = *last_flag != 0;
         }
         if (ok) {
-            const float* parts = a.workspace + static_cast<size_t>(tile_id) * a.split_k * (kTileM * BN) +
-                                 static_cast<size_t>(row_in_tile) * BN;
+            // every MMA has finished reading the operand ring: its first bytes become the
+            // staging tile, rows padded by 16 bytes against bank conflicts
+            unsigned char* stage_rows = smem;
+            const int pitch = per_tile * 2 + 16;
+            const float* parts = a.workspace +
+                                 static_cast<size_t>(tile_id) * a.split_k * (kTileM * BN) + row_in_tile;
             for (int c = 0; c < chunks; ++c) {
                 const int col0 = n0 + c * 32;
                 if (col0 >= a.n[seg]) break;
@@ -399,21 +437,16 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
                     for (int s = 0; s < a.split_k; ++s) {
                         const float* p = parts + static_cast<size_t>(s) * (kTileM * BN);
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const float4 t = __ldcg(reinterpret_cast<const float4*>(p + c * 32) + q);
-                            v[4 * q] += t.x, v[4 * q + 1] += t.y, v[4 * q + 2] += t.z, v[4 * q + 3] += t.w;
-                        }
+                        for (int i = 0; i < 32; ++i) v[i] += __ldcg(p + (c * 32 + i) * kTileM);
                         if (a.pair) {
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const float4 t =
-                                    __ldcg(reinterpret_cast<const float4*>(p + kHalf + c * 32) + q);
-                                u[4 * q] += t.x, u[4 * q + 1] += t.y, u[4 * q + 2] += t.z, u[4 * q + 3] += t.w;
-                            }
+                            for (int i = 0; i < 32; ++i)
+                                u[i] += __ldcg(p + (kHalf + c * 32 + i) * kTileM);
                         }
                     }
                 } else {
                     tmem_load32(lane_addr + c * 32, v);
+                    if (c == 0 && threadIdx.x == 64) stamp(7);
                     if (a.pair)
                         tmem_load32(lane_addr + kHalf + c * 32, u);
                     else {
@@ -421,10 +454,14 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
                         for (int i = 0; i < 32; ++i) u[i] = 0.f;
                     }
                 }
-                if (row < a.M) gemm_store_chunk<BN>(a, seg, row, col0, width, v, u);
+                gemm_stage_chunk(a, seg, col0, width, v, u, stage_rows + row_in_tile * pitch + c * 64);
             }
+            __syncwarp();
+            gemm_write_rows(a, seg, m0 + quarter * 32, n0, per_tile, stage_rows + quarter * 32 * pitch,
+                            pitch, lane);
         }
     }
+    if (threadIdx.x == 64) stamp(5);
     tc_fence_before();
     __syncthreads();
     if (*abort_flag) {
@@ -434,6 +471,7 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         __syncthreads();
     }
     if (warp == 1) tmem_dealloc(tmem_base, BN);
+    if (threadIdx.x == 32) stamp(6);
 }
 
 
@@ -734,6 +772,10 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         if (split > 16) split = 16;
         if (split < 1) split = 1;
     }
+    if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_SPLIT")) {
+        const int value = std::atoi(forced);
+        if (value >= 1 && value <= 16 && value <= g.kblocks) split = value;
+    }
     g.split_k = split;
     return g;
 }
@@ -959,7 +1001,8 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
 // Enqueues every phase in order.  Dynamic slots (token ids) are resolved here on the host.
 cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases,
                            const std::vector<unsigned long long>& slots, unsigned int n_dynamic,
-                           const unsigned long long* dyn, Control* ctl, cudaStream_t stream) {
+                           const unsigned long long* dyn, Control* ctl,
+                           unsigned long long* trace, cudaStream_t stream) {
     using namespace prefill;
     auto addr = [&](int s) -> unsigned long long {
         if (s < 0) return 0ull;
@@ -985,8 +1028,9 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                 break;
             case MB_BODY_GEMM_TC: {
                 const GemmGeometry& g = L.geometry;
-                const dim3 grid(g.tiles_n, g.tiles_m, g.split_k);
+                const dim3 grid(g.tiles_m, g.tiles_n, g.split_k);
                 GemmArgs args = L.gemm;
+                args.trace = trace == nullptr ? nullptr : trace + 8 * i;
                 for (int s = 0; s < args.nseg; ++s)  // outputs may be per-launch tensors (logits)
                     args.out[s] = reinterpret_cast<unsigned short*>(addr(P.slot[MB_GV_S_OUT0 + s]));
                 if (g.bn == 256)
