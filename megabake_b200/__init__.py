@@ -8,6 +8,7 @@ parts of it this backend keeps):
 ``graphed(function, *args)``        CUDA-graph capture of one compiled call
 ``kv_attention`` / ``attention``    the declared attention operators (``torch.ops.megabake.*``)
 ``DecodeStep``, ``StatefulDecoder`` explicit-state decode wrappers for Hugging Face models
+``PrefillLogits``                   ids -> logits prefill wrapper over ``megabake::attention``
 ``register_transformers_attention`` the ``"megabake"`` attention implementation for HF models
 ``CompilerError``                   every refusal, with a staged diagnostic
 """
@@ -16,7 +17,8 @@ from .diagnostics import CompilerDiagnostic, CompilerError
 from .ops import attention, kv_attention
 
 __all__ = [
-    "CompilerDiagnostic", "CompilerError", "DecodeStep", "StatefulDecoder", "attention",
+    "CompilerDiagnostic", "CompilerError", "DecodeStep", "PrefillLogits", "StatefulDecoder",
+    "attention",
     "graphed", "kv_attention", "make_backend", "register_transformers_attention",
 ]
 
@@ -29,7 +31,8 @@ def __getattr__(name):
     if name in ("graphed", "GraphedCall", "BoundDecoder"):
         from . import engine
         return getattr(engine, name)
-    if name in ("DecodeStep", "StatefulDecoder", "register_transformers_attention"):
+    if name in ("DecodeStep", "PrefillLogits", "StatefulDecoder",
+                "register_transformers_attention"):
         from . import hf
         return getattr(hf, name)
     raise AttributeError(name)

@@ -107,7 +107,7 @@ class _MegakernelCall:
 
     def __call__(self, args: list) -> list:
         from .engine import BoundDecoder
-        from .planner import plan_decode
+        from .planner import plan_decode, plan_prefill
 
         flat = list(args)
         args.clear()
@@ -116,7 +116,11 @@ class _MegakernelCall:
             if program.embed_scale_arg is not None:
                 scale = float(flat[program.embed_scale_arg].float().reshape(-1)[0])
                 program = dataclasses.replace(program, embed_scale=scale)
-            self.decoder = BoundDecoder(plan_decode(program), flat)
+            if program.mode == "prefill":
+                layout = plan_prefill(program, mask=program.mask)
+            else:
+                layout = plan_decode(program)
+            self.decoder = BoundDecoder(layout, flat)
             self.owner.megabake_last_callable = self.decoder
         return [self.decoder(*flat)]
 

@@ -261,3 +261,20 @@ class StatefulDecoder(_ExplicitState):
             hidden = hidden + mixed
             hidden = hidden + layer.mlp(layer.post_attention_layernorm(hidden))
         return self.lm_head(self.model.norm(hidden))
+
+
+class PrefillLogits(torch.nn.Module):
+    """``forward(input_ids[B, T]) -> logits[B, T, V]``: a full causal prefill at positions
+    0..T-1 with every attention module routed to ``megabake::attention``.  This is the callable
+    the reference's prefill benchmark compiles (``benchmarks/full_model.py:178-200``: the model
+    itself, called on the prompt), reduced to its logits so that the compiled graph has one
+    output."""
+
+    def __init__(self, model: torch.nn.Module):
+        super().__init__()
+        register_transformers_attention()
+        model.config._attn_implementation = ATTENTION_IMPLEMENTATION
+        self.model = model
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.model(input_ids=input_ids, use_cache=False).logits

@@ -72,6 +72,8 @@ class DecoderProgram:
     lm_head_bias: int | None = None
     embed_scale_arg: int | None = None  # graph input holding the embedding scale (read at bind)
     causal: bool = True  # prefill mask kind
+    mask: object = field(default=None, compare=False, repr=False)  # additive bf16 mask tensor of a
+    # non-causal prefill, [1 or batch, 1, tokens, tokens]
 
     @property
     def group(self) -> int:

@@ -58,6 +58,13 @@ def _is(node, *targets) -> bool:
     return isinstance(node, torch.fx.Node) and node.op == "call_function" and node.target in targets
 
 
+# Prefill graphs move the head axis in front of the token axis for RoPE and back again for the
+# attention operator ([B, T, H, D] <-> [B, H, T, D]).  While a prefill graph is matched these
+# transposes count as layout-only: the operands are identified by the projection they come
+# from, and the attention call is checked to receive them as [B, T, H, D] again.
+_HEAD_TOKEN_SWAPS_ARE_LAYOUT = False
+
+
 def _keeps_order(node) -> bool:
     """True if a view-like op leaves the element order untouched (it only reshapes, adds or
     moves size-1 axes, or copies)."""
@@ -77,6 +84,8 @@ def _keeps_order(node) -> bool:
             a, b = node.args[1] % len(shape), node.args[2] % len(shape)
             order[a], order[b] = order[b], order[a]
         moved = [d for d in order if shape[d] != 1]
+        if _HEAD_TOKEN_SWAPS_ARE_LAYOUT and len(shape) == 4 and order == [0, 2, 1, 3]:
+            return True
         return moved == sorted(moved)
     return True
 
@@ -304,6 +313,7 @@ class _Matcher:
         allowed = _VIEW_TARGETS | {aten.bmm.default, aten.cat.default, aten.mul.Tensor,
                                    prims.convert_element_type.default, aten._to_copy.default}
         leaves, stack, seen = set(), [body.args[0]], set()
+        counted_positions = False  # positions 0..T-1 built inside the graph (prefill)
         while stack:
             current = stack.pop()
             if isinstance(current, (list, tuple)):
@@ -314,17 +324,22 @@ class _Matcher:
             seen.add(current)
             if current.op == "placeholder":
                 leaves.add(current)
+            elif _is(current, prims.iota.default):
+                if (current.kwargs.get("start", 0) != 0 or current.kwargs.get("step", 1) != 1
+                        or counted_positions):
+                    return None
+                counted_positions = True
+            elif _is(current, aten.add.Tensor) and _scalar(current.args[1]) == 0.0:
+                stack.append(current.args[0])
             elif current.op == "call_function" and current.target in allowed:
                 stack.extend(current.args)
             else:
                 return None
-        if len(leaves) != 2:
-            return None
         inv = [n for n in leaves if _val(n).dtype.is_floating_point]
         pos = [n for n in leaves if not _val(n).dtype.is_floating_point]
-        if len(inv) != 1 or len(pos) != 1:
+        if len(inv) != 1 or len(pos) + int(counted_positions) != 1:
             return None
-        return kind, scale, self.order[inv[0]], self.order[pos[0]]
+        return kind, scale, self.order[inv[0]], (self.order[pos[0]] if pos else None)
 
     def rope(self, node):
         """Rotary embedding of a projection -> (linear, tables dict) or None.  Covers the
@@ -416,6 +431,44 @@ class _Matcher:
         return {"source": operands["source"], "key": operands["key"], "value": operands["value"],
                 "key_cache": indices[0], "value_cache": indices[1], "valid_length": indices[2]}
 
+    def prefill_attention(self, node):
+        """``megabake::attention(q, k, v, mask, scale)`` whose result ``node`` is -> dict."""
+        node = strip(node)
+        if not _is(node, torch.ops.megabake.attention.default):
+            return None
+        query, key, value, mask, scale = node.args[:5]
+        return {"source": query, "key": key, "value": value, "mask": mask, "scale": float(scale),
+                "key_cache": -1, "value_cache": -1, "valid_length": -1, "node": node}
+
+    def constant(self, node, module: torch.fx.GraphModule):
+        """Evaluate a sub-graph that depends on no graph input (the mask of a prefill)."""
+        memo: dict = {}
+
+        def run(current):
+            if isinstance(current, (list, tuple)):
+                return type(current)(run(item) for item in current)
+            if not isinstance(current, torch.fx.Node):
+                return current
+            if current in memo:
+                return memo[current]
+            if current.op == "get_attr":
+                value = getattr(module, current.target)
+            elif current.op == "call_function":
+                value = current.target(*run(current.args),
+                                       **{k: run(v) for k, v in current.kwargs.items()})
+            else:
+                self.refuse("the attention mask depends on a runtime input; call the model "
+                            "without attention_mask (a full causal prefill)", current)
+            memo[current] = value
+            return value
+
+        # recognition runs inside the compiler's tracing modes (fake tensors); the constant has
+        # to be computed for real
+        from torch.utils._python_dispatch import _disable_current_modes
+
+        with _disable_current_modes(), torch.no_grad():
+            return run(node)
+
     # -- embedding ----------------------------------------------------------------------------
     def embedding(self, node):
         """-> (weight index, ids index, scale placeholder index or None) or None."""
@@ -438,6 +491,16 @@ class _Matcher:
 
 def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
     """Match the whole graph; raises ``CompilerError`` if it is not a covered decoder."""
+    global _HEAD_TOKEN_SWAPS_ARE_LAYOUT
+    _HEAD_TOKEN_SWAPS_ARE_LAYOUT = any(
+        _is(node, torch.ops.megabake.attention.default) for node in graph_module.graph.nodes)
+    try:
+        return _recognize(graph_module, mode)
+    finally:
+        _HEAD_TOKEN_SWAPS_ARE_LAYOUT = False
+
+
+def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
     m = _Matcher(graph_module.graph)
     output = next(n for n in graph_module.graph.nodes if n.op == "output")
     results = output.args[0]
@@ -455,6 +518,7 @@ def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderP
     activation, rope_scale, q_scale = None, 1.0, None
     inv_freq = position = None
     layers: list[LayerBinding] = []
+    attention_calls: list[dict] = []
     embed = None
     while True:
         embed = m.embedding(hidden)
@@ -490,12 +554,16 @@ def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderP
         for skip, branch in (pair, pair[::-1]):
             o_proj = m.linear(branch)
             call = m.kv_attention(o_proj.x) if o_proj is not None else None
+            if call is None and o_proj is not None:
+                call = m.prefill_attention(o_proj.x)
             if call is not None:
                 found = (strip(skip), o_proj, call)
                 break
         if found is None:
-            m.refuse("residual branch is not o_proj(megabake::kv_attention(...))", h_mid)
+            m.refuse("residual branch is not o_proj(megabake::kv_attention(...)) or "
+                     "o_proj(megabake::attention(...))", h_mid)
         h_in, o_proj, call = found
+        attention_calls.append(call)
         source = strip(call["source"])
         layer_q_scale = None
         scaled = _binary(source, aten.mul.Tensor)
@@ -531,6 +599,16 @@ def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderP
         hidden = h_in
     if not layers:
         m.refuse("no decoder layer found")
+    stateless = ["mask" in call for call in attention_calls]
+    if any(stateless) != all(stateless):
+        m.refuse("layers mix megabake::attention and megabake::kv_attention")
+    if all(stateless):
+        if mode != "prefill":
+            raise ValueError("mode='decode' graphs must update KV state through "
+                             "megabake::kv_attention (megabake::attention found); use mode='prefill'")
+        layers.reverse()
+        return _prefill_program(m, graph_module, layers, attention_calls[::-1], embed, head, final,
+                                norm_kind, eps, activation, rope_scale, q_scale, inv_freq, position)
     if mode != "decode":
         raise ValueError("mode='prefill' graphs must not update KV state "
                          "(megabake::kv_attention found); use mode='decode'")
@@ -556,3 +634,60 @@ def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderP
         lm_head_bias=head.bias, embed_scale_arg=scale_index,
     )
     return program
+
+
+def _classify_mask(m, mask, batch, tokens, node):
+    """(causal?, tensor to upload or None) of an evaluated additive mask."""
+    if (not isinstance(mask, torch.Tensor) or mask.dim() != 4 or mask.shape[1] != 1
+            or tuple(mask.shape[2:]) != (tokens, tokens) or mask.shape[0] not in (1, batch)):
+        m.refuse("the attention mask is not [1 or batch, 1, tokens, tokens]", node)
+    mask = mask.to(torch.bfloat16)
+    allowed = torch.tril(torch.ones(tokens, tokens, dtype=torch.bool, device=mask.device))
+    floor = torch.finfo(torch.bfloat16).min
+    expected = torch.where(allowed, torch.zeros((), dtype=torch.bfloat16, device=mask.device),
+                           torch.full((), floor, dtype=torch.bfloat16, device=mask.device))
+    causal = bool((mask == expected).all())
+    return causal, (None if causal else mask.contiguous())
+
+
+def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_kind, eps, activation,
+                     rope_scale, q_scale, inv_freq, position) -> DecoderProgram:
+    from torch.utils._python_dispatch import _disable_current_modes
+
+    first = calls[0]
+    batch, tokens, heads, head_dim = _shape(first["source"])
+    kv_shape = _shape(first["key"])
+    if len(kv_shape) != 4 or kv_shape[:2] != (batch, tokens) or kv_shape[3] != head_dim:
+        m.refuse("megabake::attention operands must be [batch, tokens, heads, head_dim]",
+                 first["node"])
+    kv_heads = kv_shape[2]
+    for call in calls:
+        same_mask = call["mask"] is first["mask"] or strip(call["mask"]) is strip(first["mask"])
+        if (_shape(call["source"]) != (batch, tokens, heads, head_dim)
+                or _shape(call["key"]) != kv_shape or _shape(call["value"]) != kv_shape
+                or call["scale"] != first["scale"] or not same_mask):
+            m.refuse("layers disagree on attention shapes, scale or mask", call["node"])
+    embed_weight, ids, scale_index = embed
+    if tuple(_shape(m.placeholders[ids])) != (batch, tokens):
+        m.refuse(f"prefill takes input_ids of shape [{batch}, {tokens}]")
+    # recognition runs inside the compiler's tracing modes (fake tensors): the mask constant
+    # has to be computed and inspected for real
+    if first["mask"] is not None:
+        mask = m.constant(first["mask"], graph_module)
+        with _disable_current_modes():
+            causal, mask_tensor = _classify_mask(m, mask, batch, tokens, first["node"])
+    else:  # no mask at all: every key visible, expressed as an all-zero additive mask
+        with _disable_current_modes():
+            causal, mask_tensor = False, torch.zeros(1, 1, tokens, tokens, dtype=torch.bfloat16)
+    vocab, hidden_size = _shape(m.placeholders[head.weight])
+    return DecoderProgram(
+        mode="prefill", batch=batch, tokens=tokens, hidden=hidden_size, heads=heads,
+        kv_heads=kv_heads, head_dim=head_dim,
+        intermediate=_shape(m.placeholders[layers[0].gate_weight])[0], vocab=vocab, capacity=0,
+        norm=norm_kind, eps=eps, activation=activation, embed_scale=None, rope_scale=rope_scale,
+        q_scale=q_scale, softmax_scale=first["scale"],
+        inv_freq_dtype="bf16" if _val(m.placeholders[inv_freq]).dtype == torch.bfloat16 else "f32",
+        input_ids=ids, position_ids=position, embed_weight=embed_weight, inv_freq=inv_freq,
+        final_norm=final[1], lm_head_weight=head.weight, layers=tuple(layers),
+        lm_head_bias=head.bias, embed_scale_arg=scale_index, causal=causal, mask=mask_tensor,
+    )

@@ -106,6 +106,41 @@ def test_recognition_recovers_the_architecture(name, kind):
         recognize_decoder(graph, "prefill")
 
 
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama3", "tiny-qwen2", "tiny-gemma"])
+def test_prefill_recognition_and_plan(name):
+    from megabake_b200 import PrefillLogits
+    from megabake_b200 import runtime as rt
+    from megabake_b200.planner import plan_prefill
+
+    spec = models.get_spec(name)
+    wrapper = PrefillLogits(models.build_hf_model(spec, seed=1)).eval()
+    backend = make_backend(mode="prefill", compile_kernel=False)
+    torch._dynamo.reset()
+    compiled = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    ids = torch.randint(0, spec.vocab, (2, 10), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        logits = compiled(ids)
+        assert torch.equal(logits, wrapper(ids))       # the FX forward is the eager forward
+    graph = backend.megabake_last_prepared.graph
+    program = recognize_decoder(graph, "prefill")
+    assert (program.mode, program.batch, program.tokens) == ("prefill", 2, 10)
+    assert (program.hidden, program.heads, program.kv_heads, program.head_dim) == (
+        spec.hidden, spec.heads, spec.kv_heads, spec.head_dim)
+    assert program.causal and program.mask is None     # the graph's mask constant is causal
+    assert program.position_ids is None                # positions 0..T-1 are graph constants
+    assert program.softmax_scale == pytest.approx(spec.head_dim ** -0.5)
+    assert len(program.layers) == spec.layers and program.activation == spec.activation
+    with pytest.raises(ValueError, match="mode='decode'"):
+        recognize_decoder(graph, "decode")
+    layout = plan_prefill(program)
+    assert layout.mode == rt.MODE_PREFILL
+    assert len(layout.phases) == 1 + 8 * spec.layers + 2
+    bodies = [phase.body for phase in layout.phases]
+    assert bodies[0] == rt.BODY_EMBED_ROWS and bodies[-1] == rt.BODY_GEMM_TC
+    assert bodies.count(rt.BODY_ATTN_PREFILL) == spec.layers
+    assert bodies.count(rt.BODY_GEMM_TC) == 4 * spec.layers + 1
+
+
 def test_unrecognised_graph_is_refused_not_rerouted():
     class NotADecoder(torch.nn.Module):
         def forward(self, x):

@@ -123,3 +123,38 @@ def test_two_threads_share_one_compiled_callable():
     assert not errors, errors
     assert int(state[2]) == 21  # every call appended exactly one key
     backend.megabake_last_callable.check()
+
+
+@pytest.mark.parametrize("name,batch,tokens", [
+    ("tiny-llama", 2, 40), ("tiny-qwen2", 1, 16), ("tiny-gemma", 2, 70), ("tiny-gemma256", 1, 130),
+])
+def test_compiled_prefill_matches_oracle(name, batch, tokens):
+    """``torch.compile(PrefillLogits(model), backend=make_backend(mode="prefill"))``: capture,
+    recognition (causal mask and positions as graph constants), prefill plan, launches."""
+    from megabake_b200 import PrefillLogits
+
+    spec = models.get_spec(name)
+    weights = models.init_weights(spec, 2)
+    model = models.build_hf_model(spec, 2, device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    wrapper = PrefillLogits(model).eval()
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    backend = make_backend(mode="prefill")
+    torch._dynamo.reset()
+    step = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    ids = torch.randint(0, spec.vocab, (batch, tokens), generator=torch.Generator().manual_seed(9))
+    with torch.no_grad():
+        got = step(ids.cuda())
+        again = step(ids.cuda())
+    torch.cuda.synchronize()
+    ref = oracle.prefill(cfg, ow, ids)
+    assert got.shape == ref.shape and got.dtype == torch.bfloat16
+    assert torch.equal(got, again)
+    assert logits_close(got, ref)[0], max_abs(got, ref)
+    for b in range(batch):
+        assert cosine(got[b], ref[b]) >= LOGIT_COSINE
+        assert greedy_pick_matches(got[b], ref[b])[0]
+    decoder = backend.megabake_last_callable
+    assert isinstance(decoder, BoundDecoder) and decoder.launches == 2
+    decoder.check()
+    assert backend.megabake_last_compiled.mode == "prefill"
