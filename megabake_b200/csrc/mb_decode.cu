@@ -285,17 +285,30 @@ __device__ __noinline__ void activation_issue(const KernelParams& p, const Phase
         gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
     const int vec_per_row = K / 8;  // 16-byte vectors
     bool bad_token = false;
-    for (int r = 0; r < rows; ++r) {
-        const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
-        __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
-        for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-            cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
-    }
-    if (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
-        __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
-        const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
-        for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-            cp_async16(wrow + v * 8, nw + static_cast<size_t>(v) * 16);
+    const bool transformed = P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE || gather;
+    if (rows >= 2 && transformed) {
+        // one warp per row: the warp that copies a row also scales / normalises it, so the
+        // prologue needs no CTA barrier between its passes (activation_finish)
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int r = warp; r < rows; r += kConsumerWarps) {
+            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
+            __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
+            for (int v = lane; v < vec_per_row; v += 32)
+                cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
+        }
+    } else {
+        for (int r = 0; r < rows; ++r) {
+            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
+            __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
+            for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+                cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
+        }
+        if (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
+            __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
+            const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+            for (int v = tid; v < vec_per_row; v += kConsumerThreads)
+                cp_async16(wrow + v * 8, nw + static_cast<size_t>(v) * 16);
+        }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
@@ -316,6 +329,46 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
     const int vec_per_row = K / 8;  // 16-byte vectors
     __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    if (rows >= 2 && (pro != MB_PRO_NONE || gather)) {
+        // warp r owns row r from the copy to the normalised result (see activation_issue)
+        __syncwarp();
+        char* store = store_x ? reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE))
+                              : nullptr;
+        const uint4* nw = pro != MB_PRO_NONE
+                              ? reinterpret_cast<const uint4*>(entry_address(p, E, MB_GV_S_NORM_W))
+                              : nullptr;
+        for (int r = warp; r < rows; r += kConsumerWarps) {
+            __nv_bfloat16* row = xs + static_cast<size_t>(r) * xpitch;
+            // the first weight vector is requested before the row is summed
+            uint4 w_first = make_uint4(0u, 0u, 0u, 0u);
+            if (nw != nullptr && lane < vec_per_row) w_first = __ldg(nw + lane);
+            float ss = 0.f;
+            for (int v = lane; v < vec_per_row; v += 32) {
+                uint4* cell = reinterpret_cast<uint4*>(row + v * 8);
+                uint4 raw = *cell;
+                if (scaled) {
+                    raw = scale_vector(raw, embed_scale);
+                    *cell = raw;
+                }
+                ss += sum_squares(raw);
+                if (store_x)
+                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) = raw;
+            }
+            if (pro != MB_PRO_NONE) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float inv = 1.0f / sqrtf(ss / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
+                for (int v = lane; v < vec_per_row; v += 32) {
+                    uint4* cell = reinterpret_cast<uint4*>(row + v * 8);
+                    const uint4 w = v == lane ? w_first : __ldg(nw + v);
+                    *cell = normalise_vector(*cell, w, inv, pro);
+                }
+            }
+        }
+        named_barrier(kBarConsumers, kConsumerThreads);
+        return;
+    }
 
     if (scaled || store_x || pro != MB_PRO_NONE) {
         // every thread works on the vectors it copied itself, so no barrier is needed yet
