@@ -251,7 +251,10 @@ typedef struct mb_plan_desc {
     uint32_t n_dynamic;       /* slots [0, n_dynamic) are given per launch, <= 8          */
     uint32_t activation_bytes;/* shared memory for activations / attention scratch        */
     uint32_t ctas;            /* 0 = one per SM                                           */
-    uint32_t reserved[4];
+    uint32_t stage_bytes;     /* decode: bytes of one weight-ring stage, a multiple of 1024 up
+                                 to mb_stage_bytes(); 0 = mb_stage_bytes().  Small stages give
+                                 a deeper ring when the reduction length is short            */
+    uint32_t reserved[3];
 } mb_plan_desc;
 
 typedef struct mb_plan_info {

@@ -62,6 +62,7 @@ struct mb_plan {
     int threads = 0;
     int smem_bytes = 0;
     int stages = 0;
+    int stage_bytes = 0;
     int barriers = 0;
     mb::PhaseEntry* d_entries = nullptr;
     mb::Control* d_ctl = nullptr;
@@ -86,6 +87,10 @@ int check_slot(const mb_plan_desc* d, int s, bool required) {
     return static_cast<unsigned int>(s) < d->n_slots ? MB_OK : MB_ERR_INVALID;
 }
 
+int plan_stage_bytes(const mb_plan_desc* d) {
+    return d->stage_bytes == 0 ? mb::decode_stage_bytes() : static_cast<int>(d->stage_bytes);
+}
+
 int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     const int rows = P.i[MB_GV_I_ROWS], K = P.i[MB_GV_I_K], nseg = P.i[MB_GV_I_NSEG];
     const int nmat = P.i[MB_GV_I_NMAT], rt = P.i[MB_GV_I_ROW_TILE], kc = P.i[MB_GV_I_K_CHUNK];
@@ -97,8 +102,7 @@ int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     if (nmat == 2 && nseg != 1) return MB_ERR_INVALID;
     if (rt != mb::decode_row_tile()) return MB_ERR_INVALID;
     if (kc < 32 || kc % 32 != 0 || kc > K) return MB_ERR_INVALID;
-    if (static_cast<long long>(rt) * nmat * (kc * 2 + mb::decode_row_pad()) >
-        mb::decode_stage_bytes())
+    if (static_cast<long long>(rt) * nmat * (kc * 2 + mb::decode_row_pad()) > plan_stage_bytes(d))
         return MB_ERR_RESOURCE;
     // activation rows, plus one staged row of norm weights when the phase normalises
     const long long staged_rows = rows + (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE ? 1 : 0);
@@ -238,6 +242,9 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     if (desc->mode == MB_MODE_PREFILL) return create_prefill_plan(desc, out);
     if (desc->mode != MB_MODE_DECODE) return MB_ERR_UNSUPPORTED;
     if (desc->activation_bytes % 128 != 0) return MB_ERR_INVALID;
+    if (desc->stage_bytes % 1024 != 0 ||
+        desc->stage_bytes > static_cast<unsigned int>(mb::decode_stage_bytes()))
+        return MB_ERR_INVALID;
 
     int barriers = 1;  // the closing barrier
     for (unsigned int i = 0; i < desc->n_phases; ++i) {
@@ -265,7 +272,7 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     if (!prop.cooperativeLaunch) return MB_ERR_UNSUPPORTED;
 
     const int fixed = mb::decode_fixed_smem();
-    const int stage = mb::decode_stage_bytes();
+    const int stage = plan_stage_bytes(desc);
     const int limit = static_cast<int>(prop.sharedMemPerBlockOptin);
     int stages = (limit - fixed - static_cast<int>(desc->activation_bytes)) / stage;
     if (stages > mb::decode_max_stages()) stages = mb::decode_max_stages();
@@ -300,6 +307,7 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     plan->threads = mb::decode_threads();
     plan->smem_bytes = smem;
     plan->stages = stages;
+    plan->stage_bytes = stage;
     plan->barriers = barriers;
 
     cudaError_t err = cudaMalloc(&plan->d_entries, sizeof(mb::PhaseEntry) * desc->n_phases);
@@ -395,6 +403,7 @@ int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, v
     params.n_dynamic = static_cast<int>(plan->n_dynamic);
     params.barriers_per_launch = plan->barriers;
     params.stages = plan->stages;
+    params.stage_bytes = plan->stage_bytes;
     params.activation_bytes = static_cast<int>(plan->activation_bytes);
     DeviceGuard guard(plan->device);
     if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");

@@ -28,12 +28,13 @@ namespace decode {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 constexpr int kRowTile = 8;          // weight rows per stage = one n8 MMA tile
 constexpr int kRowPad = 64;          // bytes added to each staged row: with row lengths that are
                                      // multiples of 128 B this makes 16-byte fragment loads of
                                      // two neighbouring rows hit disjoint banks
-constexpr int kStageBytes = 34816;   // 8 rows x (2048 * 2 + 64) B plus slack: whole 4 KB rows
+constexpr int kStageBytes = 34816;   // largest ring stage: 8 rows x (2048 * 2 + 64) B plus slack,
+                                     // whole 4 KB rows; plans may ask for smaller stages
 constexpr int kCtlBytes = 2048;
 constexpr int kReduceBytes = 16384;  // partial sums of one reduction group of row blocks
 constexpr int kFixedBytes = kCtlBytes + kReduceBytes;
@@ -226,7 +227,7 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                 }
                 __syncwarp();
                 if (mine) {
-                    char* dst = ring + static_cast<size_t>(stage) * kStageBytes +
+                    char* dst = ring + static_cast<size_t>(stage) * p.stage_bytes +
                                 static_cast<size_t>(m * kRowTile + r) * g.pitch;
                     bulk_copy_g2s(dst, src_row + static_cast<size_t>(c) * g.k_chunk * 2, seg_bytes,
                                   &sc->full[stage]);
@@ -586,7 +587,7 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                 }
                 if (group0 == 0 && b == 0 && c == 0) trace_stamp(p, ph, 4, tid);
                 const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
-                const char* wrow = ring + static_cast<size_t>(stage) * kStageBytes +
+                const char* wrow = ring + static_cast<size_t>(stage) * p.stage_bytes +
                                    static_cast<size_t>(gid) * g.pitch + 16 * tq;
                 const __nv_bfloat16* xk = xrow + c * g.k_chunk;
                 const int groups = kc >> 5;  // 32 reduction elements per group
@@ -1264,8 +1265,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         producer_loop(p, sc, ring, tid & 31);
     } else {
         const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(&p.ctl->calls);
-        const unsigned int base =
-            calls * static_cast<unsigned int>(p.barriers_per_launch) * gridDim.x;
+        const unsigned int base = calls * static_cast<unsigned int>(p.barriers_per_launch);
         unsigned int it = 0;
         int barrier_index = 0;
         bool ok = true;
@@ -1324,8 +1324,8 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             if (more) wait_entry(p, &sc->entry[(ph + 1) & 1], tid);  // published by the barrier below
             if (flags & MB_FLAG_BARRIER) {
                 ++barrier_index;
-                ok = grid_barrier(p.ctl, base + barrier_index * gridDim.x, kBarConsumers,
-                                  kConsumerThreads, tid, &sc->abort_flag, &sc->verdict, ph);
+                ok = grid_barrier(p.ctl, base + barrier_index, kBarConsumers, kConsumerThreads, tid,
+                                  &sc->abort_flag, &sc->verdict, ph);
                 if (ok && length_address != 0ull && blockIdx.x == 0 && tid == 0) {
                     int* lenp = reinterpret_cast<int*>(length_address);
                     *lenp = *lenp + 1;
@@ -1341,8 +1341,8 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         if (ok) {
             // Closing barrier: nobody may still read `calls` when CTA 0 advances it.
             ++barrier_index;
-            ok = grid_barrier(p.ctl, base + barrier_index * gridDim.x, kBarConsumers,
-                              kConsumerThreads, tid, &sc->abort_flag, &sc->verdict, p.n_phases);
+            ok = grid_barrier(p.ctl, base + barrier_index, kBarConsumers, kConsumerThreads, tid,
+                              &sc->abort_flag, &sc->verdict, p.n_phases);
             if (ok && blockIdx.x == 0 && tid == 0) p.ctl->calls = calls + 1;
         }
     }
@@ -1441,6 +1441,7 @@ attention_static_kernel(const __grid_constant__ PhaseEntry entry, Control* ctl, 
     p.n_dynamic = 0;
     p.barriers_per_launch = 0;
     p.stages = 0;
+    p.stage_bytes = 0;
     p.activation_bytes = 0;
     const PhaseEntry* E = &sc->entry[0];
     const int D = E->rec.i[MB_AT_I_HEAD_DIM];

@@ -14,11 +14,19 @@ namespace mb {
 // ---------------------------------------------------------------------------------------
 // Control block in global memory, one per plan.
 // ---------------------------------------------------------------------------------------
+constexpr int kBarrierLanes = 8;
 struct Control {
-    unsigned int barrier;   // counting grid barrier, grows by `ctas` per barrier
+    unsigned int reserved;
     unsigned int calls;     // completed launches; the barrier targets derive from it
     int status[4];          // code, phase, detail, (unused)
-    unsigned int pad[2];
+    unsigned int pad[26];
+    // Counting grid barrier, spread over eight counters 128 bytes apart: CTA c arrives on
+    // counter c % 8, so the arrivals (atomics on one address serialise in L2) proceed on eight
+    // addresses at once.  Counter j grows by the number of CTAs mapped to it per barrier.
+    struct Lane {
+        unsigned int count;
+        unsigned int pad[31];
+    } lanes[kBarrierLanes];
 };
 
 // One phase as the kernel reads it: the record plus the device address of every slot it
@@ -41,6 +49,7 @@ struct KernelParams {
     int n_dynamic;
     int barriers_per_launch;
     int stages;            // weight-ring depth
+    int stage_bytes;       // bytes of one ring stage
     int activation_bytes;  // shared bytes reserved for activations / attention scratch
 };
 
@@ -240,47 +249,57 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned int a0, u
 
 // ---------------------------------------------------------------------------------------
 // Counting grid barrier.  Called by `threads` threads of every CTA (named barrier `bar_id`).
-// `target` is the counter value that means "everybody arrived".  Thread 0 decides for the
+// `generation` counts barriers since the plan was created or reset (the same in every CTA).
+// Lanes 0..7 of warp 0 each watch one of the eight counters; together they decide for the
 // whole CTA -- go on, or drain because a wait ran out / a fault was recorded here or in
-// another CTA -- and publishes the decision through `verdict` in shared memory, so that every
+// another CTA -- and publish the decision through `verdict` in shared memory, so that every
 // thread of the CTA takes the same branch afterwards.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int target, int bar_id,
+__device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int generation, int bar_id,
                                              int threads, int tid, volatile int* abort_flag,
                                              volatile int* verdict, int phase) {
     named_barrier(bar_id, threads);
-    if (tid == 0) {
+    if (tid < kBarrierLanes) {
+        constexpr unsigned int kMask = (1u << kBarrierLanes) - 1u;
+        const unsigned int ctas = gridDim.x;
         bool go = *abort_flag == 0;
         if (go) {
-            // release: orders every write this CTA made before the bar.sync above
-            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ctl->barrier)
-                         : "memory");
+            if (tid == 0) {
+                // release: orders every write this CTA made before the bar.sync above
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(
+                                 &ctl->lanes[blockIdx.x % kBarrierLanes].count)
+                             : "memory");
+            }
+            const unsigned int mapped = ctas / kBarrierLanes +
+                                        (static_cast<unsigned int>(tid) < ctas % kBarrierLanes ? 1u : 0u);
+            const unsigned int target = generation * mapped;
             unsigned long long start = 0;
             unsigned int polls = 0;
             for (;;) {
                 unsigned int seen;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
                              : "=r"(seen)
-                             : "l"(&ctl->barrier)
+                             : "l"(&ctl->lanes[tid].count)
                              : "memory");
-                if (static_cast<int>(seen - target) >= 0) break;
-                if ((++polls & 63u) == 0u) {
+                if (__all_sync(kMask, static_cast<int>(seen - target) >= 0)) break;
+                if ((++polls & 63u) == 0u) {  // the eight lanes take this branch together
                     if (start == 0) start = global_timer_ns();
-                    if (peek_status(ctl) != 0 || *abort_flag != 0) {
-                        go = false;
-                        break;
-                    }
-                    if (global_timer_ns() - start > kBarrierTimeoutNs) {
-                        record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase,
-                                      static_cast<int>(blockIdx.x));
+                    const bool faulted = peek_status(ctl) != 0 || *abort_flag != 0;
+                    const bool late = global_timer_ns() - start > kBarrierTimeoutNs;
+                    if (__any_sync(kMask, faulted || late)) {
+                        if (tid == 0 && !faulted)
+                            record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase,
+                                          static_cast<int>(blockIdx.x));
                         go = false;
                         break;
                     }
                 }
             }
         }
-        if (!go) *abort_flag = 1;
-        *verdict = go ? 1 : 0;
+        if (tid == 0) {
+            if (!go) *abort_flag = 1;
+            *verdict = go ? 1 : 0;
+        }
     }
     named_barrier(bar_id, threads);
     return *verdict != 0;

@@ -56,7 +56,8 @@ class BoundDecoder:
             self._zero_workspace()
             self.plan = rt.Plan(layout.phases, n_slots=len(layout.slots), n_dynamic=3,
                                 activation_bytes=layout.activation_bytes,
-                                device=self.device.index or 0, mode=layout.mode, ctas=ctas)
+                                device=self.device.index or 0, mode=layout.mode, ctas=ctas,
+                                stage_bytes=layout.stage_bytes)
             # tensors the plan itself owns: a non-causal mask, and the positions 0..T-1 of
             # every row when the captured graph held them as constants
             self._constants = {name: tensor.to(self.device)

@@ -58,6 +58,7 @@ class PlanLayout:
     intervals: int
     notes: list[str] = field(default_factory=list)
     mode: int = rt.MODE_DECODE
+    stage_bytes: int = 0  # decode: weight-ring stage size handed to mb_plan_create (0 = default)
     constants: dict = field(default_factory=dict)  # name -> CPU tensor uploaded at bind
 
 
@@ -68,12 +69,15 @@ class PlannerOptions:
     max_chunks: int = 32
     merge_slots: int | None = None
     exact_keys: int = EXACT_SOFTMAX_KEYS
+    stage_bytes: int | None = None  # force the ring stage size (tuning sweeps)
 
     @classmethod
     def from_env(cls, **overrides) -> "PlannerOptions":
         values = {}
         if os.environ.get("MEGABAKE_B200_ROW_TILE"):
             values["row_tile"] = int(os.environ["MEGABAKE_B200_ROW_TILE"])
+        if os.environ.get("MEGABAKE_B200_STAGE_BYTES"):
+            values["stage_bytes"] = int(os.environ["MEGABAKE_B200_STAGE_BYTES"])
         values.update(overrides)
         return cls(**values)
 
@@ -175,10 +179,17 @@ def _check_program(p: DecoderProgram) -> None:
 
 
 def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) -> PlanLayout:
+    """Plan one decode step.  The ring stage size is the library's largest unless forced:
+    measured on B200, smaller stages (a deeper ring) never paid -- the consumers' per-stage
+    work, not the bytes in flight, bounds the weight stream."""
     options = options or PlannerOptions.from_env()
+    largest = rt.load_library().mb_stage_bytes(rt.MODE_DECODE)
+    return _plan_decode(program, options, options.stage_bytes or largest)
+
+
+def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: int) -> PlanLayout:
     _check_program(program)
     lib = rt.load_library()
-    stage_bytes = lib.mb_stage_bytes(rt.MODE_DECODE)
     fixed_bytes = lib.mb_fixed_smem_bytes(rt.MODE_DECODE)
     max_smem = lib.mb_max_smem_bytes()
     row_pad = 64
@@ -347,7 +358,8 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
         intervals=intervals,
         notes=[f"{len(phases)} phases in {intervals} barrier intervals",
                f"attention: max_chunks={max_chunks} merge_slots={merge_slots} "
-               f"exact_keys={exact_keys}"],
+               f"exact_keys={exact_keys}", f"ring stage {stage_bytes} B"],
+        stage_bytes=stage_bytes,
     )
 
 

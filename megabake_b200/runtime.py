@@ -96,7 +96,8 @@ class PlanDesc(ctypes.Structure):
         ("n_dynamic", ctypes.c_uint32),
         ("activation_bytes", ctypes.c_uint32),
         ("ctas", ctypes.c_uint32),
-        ("reserved", ctypes.c_uint32 * 4),
+        ("stage_bytes", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint32 * 3),
     ]
 
 
@@ -222,7 +223,8 @@ class Plan:
     serialises calls (``BoundDecoder`` holds a lock)."""
 
     def __init__(self, phases: list[Phase], *, n_slots: int, n_dynamic: int,
-                 activation_bytes: int, device: int, mode: int = MODE_DECODE, ctas: int = 0):
+                 activation_bytes: int, device: int, mode: int = MODE_DECODE, ctas: int = 0,
+                 stage_bytes: int = 0):
         self._lib = load_library()
         self._handle = ctypes.c_void_p()
         self.n_slots = n_slots
@@ -238,6 +240,7 @@ class Plan:
         desc.n_dynamic = n_dynamic
         desc.activation_bytes = activation_bytes
         desc.ctas = ctas
+        desc.stage_bytes = stage_bytes
         code = self._lib.mb_plan_create(ctypes.byref(desc), ctypes.byref(self._handle))
         _check(self._lib, code, "resource-admission" if code in (3, 4) else "planning",
                "mb_plan_create")
