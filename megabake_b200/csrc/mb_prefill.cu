@@ -279,7 +279,7 @@ __device__ __forceinline__ void gemm_write_rows(const GemmArgs& a, int seg, int 
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     constexpr int kStageW = BN * kTileK * 2;
     constexpr int kStage = kStageA + kStageW;
@@ -755,7 +755,12 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         return tiles;
     };
     g.bn = count(256) * g.tiles_m >= sm_count ? 256 : 128;
-    g.stages = g.bn == 256 ? 4 : 6;
+    // two CTAs per SM: while one runs its epilogue the other one keeps the tensor cores busy
+    g.stages = g.bn == 256 ? 2 : 3;
+    if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_STAGES")) {
+        const int value = std::atoi(forced);
+        if (value >= 2 && value <= (g.bn == 256 ? 4 : 6)) g.stages = value;
+    }
     const int per = pair ? g.bn / 2 : g.bn;
     int tiles = 0;
     for (int s = 0; s < 3; ++s) {
