@@ -493,9 +493,7 @@ struct AttnArgs {
     float scale;
 };
 
-constexpr int kAttnRows = 64;
-constexpr int kAttnKeys = 64;
-constexpr int kAttnThreads = 128;
+constexpr int kAttnKeys = 64;  // keys per block
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned int (&r)[4], const void* smem_ptr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -512,12 +510,12 @@ __device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src) {
                  : "memory");
 }
 
-template <int D>
+// `rows` rows of D bf16 each into a tile with pitch D + 8; rows past `limit` repeat the last one
+template <int D, int THREADS>
 __device__ __forceinline__ void attn_load_rows(unsigned short* dst, const unsigned short* src,
-                                               size_t row_stride, int row0, int limit) {
-    // 64 rows of D bf16 each into a tile with pitch D + 8; rows past `limit` repeat the last one
+                                               size_t row_stride, int row0, int rows, int limit) {
     constexpr int kVectors = D / 8;
-    for (int e = threadIdx.x; e < kAttnRows * kVectors; e += kAttnThreads) {
+    for (int e = threadIdx.x; e < rows * kVectors; e += THREADS) {
         const int r = e / kVectors, c = e - r * kVectors;
         const int row = min(row0 + r, limit - 1);
         cp_async_16(dst + r * (D + 8) + c * 8, src + static_cast<size_t>(row) * row_stride + c * 8);
@@ -547,13 +545,17 @@ __device__ __forceinline__ void attn_scores(float (&sacc)[8][4], const unsigned 
     }
 }
 
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(const AttnArgs a) {
+// WARPS warps per CTA, 16 query rows each; K (and V) blocks double-buffered with cp.async so
+// that the next block streams in while the tensor cores work on the current one.
+template <int D, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) attention_prefill_kernel(const AttnArgs a) {
     constexpr int P = D + 8;
+    constexpr int THREADS = WARPS * 32;
+    constexpr int ROWS = WARPS * 16;
     extern __shared__ __align__(16) unsigned char attn_smem[];
     unsigned short* Qs = reinterpret_cast<unsigned short*>(attn_smem);
-    unsigned short* Ks = Qs + kAttnRows * P;
-    unsigned short* Vs = Ks + kAttnKeys * P;
+    unsigned short* Kbuf = Qs + ROWS * P;               // [2][64][P]
+    unsigned short* Vbuf = Kbuf + 2 * kAttnKeys * P;    // [2][64][P]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tq = lane & 3;
@@ -561,15 +563,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(cons
     const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
     const int head = blockIdx.y, b = blockIdx.z;
     const int kvh = head / (a.heads / a.kv_heads);
-    const int q0 = qt * kAttnRows;
+    const int q0 = qt * ROWS;
     const size_t q_stride = static_cast<size_t>(a.heads) * D;
     const size_t kv_stride = static_cast<size_t>(a.kv_heads) * D;
     const unsigned short* qbase = a.q + static_cast<size_t>(b) * T * q_stride + head * D;
     const unsigned short* kbase = a.k + static_cast<size_t>(b) * T * kv_stride + kvh * D;
     const unsigned short* vbase = a.v + static_cast<size_t>(b) * T * kv_stride + kvh * D;
     const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
-    const int nblocks = a.causal ? min(qt + 1, all_blocks) : all_blocks;
+    const int last_row = min(q0 + ROWS, T) - 1;
+    const int nblocks = a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
     const int row_lo = q0 + warp * 16 + gid, row_hi = row_lo + 8;
+    // causal: key blocks that start past this warp's last row contribute nothing to it
+    const int warp_blocks = a.causal ? min((q0 + warp * 16 + 15) / kAttnKeys + 1, nblocks) : nblocks;
     const unsigned short* mask_lo = nullptr;
     const unsigned short* mask_hi = nullptr;
     if (a.mask != nullptr) {
@@ -577,9 +582,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(cons
         mask_lo = mb + static_cast<size_t>(min(row_lo, T - 1)) * T;
         mask_hi = mb + static_cast<size_t>(min(row_hi, T - 1)) * T;
     }
-
-    attn_load_rows<D>(Qs, qbase, q_stride, q0, T);
-    asm volatile("cp.async.commit_group;" ::: "memory");
 
     // score of (row, key) with the operator's rounding points; false if the key is not visible
     auto score = [&](float acc, int row, int key, const unsigned short* mrow, float* s) {
@@ -590,45 +592,57 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(cons
         return key < T && (!a.causal || key <= row);
     };
 
+    attn_load_rows<D, THREADS>(Qs, qbase, q_stride, q0, ROWS, T);
+    attn_load_rows<D, THREADS>(Kbuf, kbase, kv_stride, 0, kAttnKeys, T);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
     // ---- sweep 1: row maxima and denominators --------------------------------------------
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
     for (int jb = 0; jb < nblocks; ++jb) {
-        __syncthreads();  // everybody is done with the previous key block
-        attn_load_rows<D>(Ks, kbase, kv_stride, jb * kAttnKeys, T);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        const unsigned short* Ks = Kbuf + (jb & 1) * kAttnKeys * P;
+        if (jb + 1 < nblocks) {
+            attn_load_rows<D, THREADS>(Kbuf + ((jb + 1) & 1) * kAttnKeys * P, kbase, kv_stride,
+                                       (jb + 1) * kAttnKeys, kAttnKeys, T);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
-        float sacc[8][4];
-        attn_scores<D>(sacc, Qs, Ks, warp, lane);
-        float s_lo[16], s_hi[16];
-        float bm_lo = -INFINITY, bm_hi = -INFINITY;
+        if (jb < warp_blocks) {
+            float sacc[8][4];
+            attn_scores<D>(sacc, Qs, Ks, warp, lane);
+            float s_lo[16], s_hi[16];
+            float bm_lo = -INFINITY, bm_hi = -INFINITY;
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
+            for (int t = 0; t < 8; ++t)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
-                float s;
-                s_lo[2 * t + j] = score(sacc[t][j], row_lo, key, mask_lo, &s) ? s : -INFINITY;
-                s_hi[2 * t + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s) ? s : -INFINITY;
-                bm_lo = fmaxf(bm_lo, s_lo[2 * t + j]);
-                bm_hi = fmaxf(bm_hi, s_hi[2 * t + j]);
+                for (int j = 0; j < 2; ++j) {
+                    const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
+                    float s;
+                    s_lo[2 * t + j] = score(sacc[t][j], row_lo, key, mask_lo, &s) ? s : -INFINITY;
+                    s_hi[2 * t + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s) ? s : -INFINITY;
+                    bm_lo = fmaxf(bm_lo, s_lo[2 * t + j]);
+                    bm_hi = fmaxf(bm_hi, s_hi[2 * t + j]);
+                }
+#pragma unroll
+            for (int o = 1; o <= 2; o <<= 1) {
+                bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, o));
+                bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, o));
             }
+            const float n_lo = fmaxf(m_lo, bm_lo), n_hi = fmaxf(m_hi, bm_hi);
+            // a row with no visible key yet keeps max = -inf; exp(-inf - -inf) must not be formed
+            l_lo = n_lo == -INFINITY ? 0.f : l_lo * expf(m_lo - n_lo);
+            l_hi = n_hi == -INFINITY ? 0.f : l_hi * expf(m_hi - n_hi);
 #pragma unroll
-        for (int o = 1; o <= 2; o <<= 1) {
-            bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, o));
-            bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, o));
+            for (int i = 0; i < 16; ++i) {
+                if (s_lo[i] != -INFINITY) l_lo += expf(s_lo[i] - n_lo);
+                if (s_hi[i] != -INFINITY) l_hi += expf(s_hi[i] - n_hi);
+            }
+            m_lo = n_lo;
+            m_hi = n_hi;
         }
-        const float n_lo = fmaxf(m_lo, bm_lo), n_hi = fmaxf(m_hi, bm_hi);
-        // a row with no visible key yet keeps max = -inf; exp(-inf - -inf) must not be formed
-        l_lo = n_lo == -INFINITY ? 0.f : l_lo * expf(m_lo - n_lo);
-        l_hi = n_hi == -INFINITY ? 0.f : l_hi * expf(m_hi - n_hi);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            if (s_lo[i] != -INFINITY) l_lo += expf(s_lo[i] - n_lo);
-            if (s_hi[i] != -INFINITY) l_hi += expf(s_hi[i] - n_hi);
-        }
-        m_lo = n_lo;
-        m_hi = n_hi;
+        __syncthreads();  // the buffer just used is the target of the load after next
     }
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {
@@ -642,42 +656,57 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(cons
     for (int t = 0; t < D / 8; ++t)
 #pragma unroll
         for (int q = 0; q < 4; ++q) oacc[t][q] = 0.f;
+    attn_load_rows<D, THREADS>(Kbuf, kbase, kv_stride, 0, kAttnKeys, T);
+    attn_load_rows<D, THREADS>(Vbuf, vbase, kv_stride, 0, kAttnKeys, T);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     for (int jb = 0; jb < nblocks; ++jb) {
-        __syncthreads();
-        attn_load_rows<D>(Ks, kbase, kv_stride, jb * kAttnKeys, T);
-        attn_load_rows<D>(Vs, vbase, kv_stride, jb * kAttnKeys, T);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        float sacc[8][4];
-        attn_scores<D>(sacc, Qs, Ks, warp, lane);
-        unsigned int pfrag[4][4];  // A fragments of P for the four 16-key steps
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-            float p[4];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
-                float s;
-                p[j] = score(sacc[t][j], row_lo, key, mask_lo, &s) ? __fdiv_rn(expf(s - m_lo), l_lo) : 0.f;
-                p[2 + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s) ? __fdiv_rn(expf(s - m_hi), l_hi) : 0.f;
-            }
-            pfrag[t >> 1][(t & 1) * 2] = pack_bf16(p[0], p[1]);
-            pfrag[t >> 1][(t & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+        const unsigned short* Ks = Kbuf + (jb & 1) * kAttnKeys * P;
+        const unsigned short* Vs = Vbuf + (jb & 1) * kAttnKeys * P;
+        if (jb + 1 < nblocks) {
+            attn_load_rows<D, THREADS>(Kbuf + ((jb + 1) & 1) * kAttnKeys * P, kbase, kv_stride,
+                                       (jb + 1) * kAttnKeys, kAttnKeys, T);
+            attn_load_rows<D, THREADS>(Vbuf + ((jb + 1) & 1) * kAttnKeys * P, vbase, kv_stride,
+                                       (jb + 1) * kAttnKeys, kAttnKeys, T);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
+        __syncthreads();
+        if (jb < warp_blocks) {
+            float sacc[8][4];
+            attn_scores<D>(sacc, Qs, Ks, warp, lane);
+            unsigned int pfrag[4][4];  // A fragments of P for the four 16-key steps
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+            for (int t = 0; t < 8; ++t) {
+                float p[4];
 #pragma unroll
-            for (int dp = 0; dp < D / 16; ++dp) {
-                unsigned int vb[4];
-                ldmatrix_x4_trans(vb, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * P +
-                                          dp * 16 + (lane >> 4) * 8);
-                mma_bf16_16816(oacc[2 * dp], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2], pfrag[kk][3],
-                               vb[0], vb[1]);
-                mma_bf16_16816(oacc[2 * dp + 1], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2],
-                               pfrag[kk][3], vb[2], vb[3]);
+                for (int j = 0; j < 2; ++j) {
+                    const int key = jb * kAttnKeys + t * 8 + 2 * tq + j;
+                    float s;
+                    p[j] = score(sacc[t][j], row_lo, key, mask_lo, &s)
+                               ? __fdiv_rn(expf(s - m_lo), l_lo) : 0.f;
+                    p[2 + j] = score(sacc[t][2 + j], row_hi, key, mask_hi, &s)
+                                   ? __fdiv_rn(expf(s - m_hi), l_hi) : 0.f;
+                }
+                pfrag[t >> 1][(t & 1) * 2] = pack_bf16(p[0], p[1]);
+                pfrag[t >> 1][(t & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int dp = 0; dp < D / 16; ++dp) {
+                    unsigned int vb[4];
+                    ldmatrix_x4_trans(vb, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * P +
+                                              dp * 16 + (lane >> 4) * 8);
+                    mma_bf16_16816(oacc[2 * dp], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2],
+                                   pfrag[kk][3], vb[0], vb[1]);
+                    mma_bf16_16816(oacc[2 * dp + 1], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2],
+                                   pfrag[kk][3], vb[2], vb[3]);
+                }
             }
         }
+        __syncthreads();
     }
 
     unsigned short* obase = a.out + static_cast<size_t>(b) * T * q_stride + head * D;
@@ -693,6 +722,34 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_prefill_kernel(cons
     }
 }
 
+// Launch geometry: 8 warps (128 query rows) per CTA for long prompts, 4 for short ones so
+// that more CTAs exist.
+inline int attn_warps(int tokens) { return tokens > 256 ? 8 : 4; }
+inline int attn_smem_bytes(int D, int warps) { return (warps * 16 + 4 * kAttnKeys) * (D + 8) * 2; }
+
+template <int D>
+cudaError_t attn_launch(const AttnArgs& a, cudaStream_t stream) {
+    const int warps = attn_warps(a.tokens);
+    const dim3 grid((a.tokens + warps * 16 - 1) / (warps * 16), a.heads, a.batch);
+    const int smem = attn_smem_bytes(D, warps);
+    if (warps == 8)
+        attention_prefill_kernel<D, 8><<<grid, 256, smem, stream>>>(a);
+    else
+        attention_prefill_kernel<D, 4><<<grid, 128, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <int D>
+cudaError_t attn_configure() {
+    cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<D, 8>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           attn_smem_bytes(D, 8));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_prefill_kernel<D, 4>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   attn_smem_bytes(D, 4));
+    return err;
+}
 
 // ---------------------------------------------------------------------------------------
 // Host side: validation, tile / split-K geometry, tensor maps, launches.
@@ -919,12 +976,9 @@ cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillS
     if (err == cudaSuccess)
         err = cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gemm_smem_bytes(256, 4));
-    if (err == cudaSuccess)
-        err = cudaFuncSetAttribute(attention_prefill_kernel<128>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (128 + 8) * 2);
-    if (err == cudaSuccess)
-        err = cudaFuncSetAttribute(attention_prefill_kernel<256>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 64 * (256 + 8) * 2);
+    if (err == cudaSuccess) err = attn_configure<64>();
+    if (err == cudaSuccess) err = attn_configure<128>();
+    if (err == cudaSuccess) err = attn_configure<256>();
     if (err != cudaSuccess) {
         prefill_destroy(st);
         return err;
@@ -1063,15 +1117,10 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
             }
             case MB_BODY_ATTN_PREFILL: {
                 const int D = P.i[MB_AP_I_HEAD_DIM];
-                const dim3 grid((P.i[MB_AP_I_TOKENS] + kAttnRows - 1) / kAttnRows, P.i[MB_AP_I_HEADS],
-                                P.i[MB_AP_I_BATCH]);
-                const int smem = 3 * 64 * (D + 8) * 2;
-                if (D == 64)
-                    attention_prefill_kernel<64><<<grid, kAttnThreads, smem, stream>>>(L.attn);
-                else if (D == 128)
-                    attention_prefill_kernel<128><<<grid, kAttnThreads, smem, stream>>>(L.attn);
-                else
-                    attention_prefill_kernel<256><<<grid, kAttnThreads, smem, stream>>>(L.attn);
+                cudaError_t launched = D == 64    ? attn_launch<64>(L.attn, stream)
+                                       : D == 128 ? attn_launch<128>(L.attn, stream)
+                                                  : attn_launch<256>(L.attn, stream);
+                if (launched != cudaSuccess) return launched;
                 break;
             }
             default:
