@@ -167,6 +167,25 @@ def build_workload(name: str, rank: int, extra_steps: int, device, cache_fill: s
     return spec, batch, keys, capacity, weights, inv_freq, state
 
 
+def max_over_ranks(values, device, distributed: bool) -> list[float]:
+    """Element-wise maximum of per-rank scalars (the timing rule for multi-GPU runs: the job is
+    as slow as its slowest replica).  Works on any initialised process group: NCCL with a CUDA
+    device here, gloo with ``"cpu"`` in the CPU tests."""
+    import torch
+
+    tensor = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if distributed:
+        import torch.distributed as dist
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+    return [float(x) for x in tensor.cpu()]
+
+
+def whole_job_rate(units_per_rank: float, world: int, seconds: float) -> float:
+    """Throughput of the whole job: every rank processed ``units_per_rank`` in ``seconds``
+    (the max over ranks) -- weak scaling, no unit is shared between replicas."""
+    return units_per_rank * world / seconds
+
+
 def algorithmic_bytes(spec, program, batch: int, mean_keys: float) -> float:
     return program.weight_bytes() + batch * mean_keys * program.kv_bytes_per_key()
 
@@ -316,15 +335,30 @@ def run_prefill(args) -> None:
     bound.check()
     device_ms = start.elapsed_time(stop)
 
-    # end to end through the bound callable: pinned host ids -> device, the prefill, greedy pick
-    # of the last position read back to the host, synchronised every step
+    # End to end through the public API: torch.compile(PrefillLogits(model),
+    # backend=make_backend(mode="prefill")) captured once with megabake_b200.graphed.  Per step:
+    # pinned host ids -> device, graph replay (every kernel of the prefill plan), greedy pick of
+    # the last position on the device, device -> host read of it, synchronised every step.
     e2e_s = None
     if not args.skip_e2e:
+        from megabake_b200 import PrefillLogits, graphed, make_backend
+
+        bound.close()
+        del bound, logits
+        model = models.build_hf_model(spec, device=device, weights=weights)
+        del weights, call_args
+        torch.cuda.empty_cache()
+        backend = make_backend(mode="prefill")
+        step_fn = torch.compile(PrefillLogits(model).eval(), backend=backend, fullgraph=True,
+                                dynamic=False)
+        with torch.no_grad():
+            graph_call = graphed(step_fn, ids)
+        compiled = backend.megabake_last_callable
         host_pick = torch.zeros(batch, dtype=torch.int64).pin_memory()
 
         def e2e_step():
             ids.copy_(host_ids, non_blocking=True)
-            out = bound(*call_args)
+            out = graph_call(ids)
             host_pick.copy_(out[:, -1].argmax(-1), non_blocking=True)
             torch.cuda.synchronize()
 
@@ -336,12 +370,9 @@ def run_prefill(args) -> None:
             e2e_step()
         barrier()
         e2e_s = time.perf_counter() - t0
-        bound.check()
+        compiled.check()
 
-    times = torch.tensor([device_ms, (e2e_s or 0.0) * 1e3], dtype=torch.float64, device=device)
-    if distributed:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    device_ms, e2e_ms = (float(x) for x in times.cpu())
+    device_ms, e2e_ms = max_over_ranks([device_ms, (e2e_s or 0.0) * 1e3], device, distributed)
     if rank == 0:
         peak, peak_kind = measured_tensor_peak()
         ms_per_step = device_ms / steps
@@ -351,7 +382,8 @@ def run_prefill(args) -> None:
         achieved = gemm_flops / (ms_per_step * 1e-3) / 1e12
         launches = len(layout.phases)
         line = {
-            "metric": "prefill_tokens_per_s", "value": batch * tokens * world / (ms_per_step * 1e-3),
+            "metric": "prefill_tokens_per_s",
+            "value": whole_job_rate(batch * tokens, world, ms_per_step * 1e-3),
             "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -376,8 +408,9 @@ def run_prefill(args) -> None:
                 "value": batch * tokens * world / (e2e_ms * 1e-3 / steps), "unit": "tok/s",
                 "h2d_bytes_per_step": batch * tokens * 8, "d2h_bytes_per_step": batch * 8,
                 "ms_per_step": e2e_ms / steps,
-                "path": "BoundDecoder call of the prefill plan (allocates the logits) + torch argmax "
-                        "of the last position, synchronised every step",
+                "path": "torch.compile(PrefillLogits, backend=make_backend(mode='prefill')) under "
+                        "megabake_b200.graphed + torch argmax of the last position, synchronised "
+                        "every step",
             },
             "gpu_launches": steps * launches,
             "clocks": sampler.summary(),
@@ -545,11 +578,7 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
             plan_info, sampler, rank, world, distributed, device) -> None:
     import torch
 
-    times = torch.tensor([device_ms, (e2e_s or 0.0) * 1e3], dtype=torch.float64, device=device)
-    if distributed:
-        import torch.distributed as dist
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    device_ms, e2e_ms = (float(x) for x in times.cpu())
+    device_ms, e2e_ms = max_over_ranks([device_ms, (e2e_s or 0.0) * 1e3], device, distributed)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -568,7 +597,7 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
                 "cache_fill": args.cache_fill,
                 "l2": "inputs larger than L2: weights + KV read per step "
                       f"{bytes_per_launch / 1e6:.0f} MB vs 126 MB L2",
-                "tokens_per_s": batch * world / (ms_per_step * 1e-3),
+                "tokens_per_s": whole_job_rate(batch, world, ms_per_step * 1e-3),
                 "phases": len(layout.phases), "barrier_intervals": layout.intervals,
                 "ctas": plan_info["ctas"], "ring_stages": plan_info["ring_stages"],
             },
