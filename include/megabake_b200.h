@@ -237,6 +237,9 @@ typedef struct mb_phase {
 #define MB_AP_S_V 2
 #define MB_AP_S_OUT 3        /* [batch * tokens, heads * D]                                */
 #define MB_AP_S_MASK 4       /* additive bf16 [mask_batch, 1, tokens, tokens], or absent   */
+#define MB_AP_S_VT 5         /* scratch [batch * kv_heads * D, tokens rounded up to 64] bf16:
+                                given, the phase runs on tcgen05 (Q.K^T and P.V as tensor-memory
+                                MMAs, V transposed into this buffer first); absent, on mma.sync */
 
 /* ---- plan descriptor ---------------------------------------------------------------- */
 #define MB_MAX_DYNAMIC 8

@@ -752,6 +752,333 @@ cudaError_t attn_configure() {
 }
 
 // ---------------------------------------------------------------------------------------
+// Prefill attention on the 5th-generation tensor cores.
+//
+// One CTA per 128 query rows of one head.  S = Q . K^T and O += P . V both run as tcgen05.mma
+// with accumulators in tensor memory; the softmax between them runs on eight warps that read
+// S with tcgen05.ld (one thread per row and half a key block, so no shuffles), and write the
+// bf16 probabilities into shared memory in the 128-byte-swizzled K-major layout the second
+// MMA reads them in.  V is consumed transposed ([head_dim, keys], keys contiguous) so that
+// every operand is K-major; a small kernel transposes V once per layer.
+//
+// Same two sweeps and rounding points as attention_prefill_kernel above.
+//   warp 0      TMA producer: Q once, then K (and V^T) blocks into a two-stage ring
+//   warp 1      MMA issuer, owner of the tensor-memory allocation
+//   warps 2-9   softmax; warp w works on TMEM lanes 32 * (w % 4) .. and key columns
+//               32 * ((w - 2) / 4) .. of a block
+// Tensor memory: S double-buffered in columns [0, 64) and [64, 128), O in [128, 128 + D).
+// ---------------------------------------------------------------------------------------
+struct AttnMaps {
+    CUtensorMap q;   // [batch * tokens, heads * D], boxes of 128 rows x 64 columns
+    CUtensorMap k;   // [batch * tokens, kv_heads * D], boxes of 64 rows x 64 columns
+    CUtensorMap vt;  // [batch * kv_heads * D, padded tokens], boxes of D rows x 64 columns
+};
+
+constexpr int kTcRows = 128;
+constexpr int kTcThreads = 320;
+constexpr int kTcSoftmaxThreads = 256;
+
+// V [batch * tokens, kv_heads * D] -> V^T [batch * kv_heads * D, padded], zero beyond `tokens`
+__global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned short* v,
+                                                               unsigned short* vt, int tokens,
+                                                               int padded, int kv_heads, int D) {
+    __shared__ unsigned short tile[64][66];
+    const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+    const int bh = blockIdx.z, b = bh / kv_heads, h = bh - b * kv_heads;
+    const size_t row_stride = static_cast<size_t>(kv_heads) * D;
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int t = e >> 6, d = e & 63;
+        tile[t][d] = t0 + t < tokens
+                         ? v[(static_cast<size_t>(b) * tokens + t0 + t) * row_stride + h * D + d0 + d]
+                         : static_cast<unsigned short>(0);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int d = e >> 6, t = e & 63;
+        if (t0 + t < padded)
+            vt[(static_cast<size_t>(bh) * D + d0 + d) * padded + t0 + t] = tile[t][d];
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1)
+attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Control* ctl,
+                    int phase) {
+    constexpr int kQBytes = kTcRows * D * 2;         // D / 64 boxes of 128 x 64
+    constexpr int kKBytes = kAttnKeys * D * 2;       // D / 64 boxes of 64 x 64
+    constexpr int kVBytes = D * kAttnKeys * 2;       // one box of D x 64
+    constexpr int kPBytes = kTcRows * kAttnKeys * 2; // 128 rows of 128 bytes
+    constexpr unsigned int kTmemCols = D > 128 ? 512 : 256;
+    constexpr unsigned int kColO = 128;
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle; the tile set of
+    // head_dim 256 leaves no room for alignment slack, so the base is checked instead
+    extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+    unsigned char* smem = tc_smem_raw;
+    if ((smem_u32(smem) & 1023u) != 0u) {
+        if (threadIdx.x == 0) record_status(ctl, MB_ST_BAD_PHASE, phase, -1);
+        return;
+    }
+    unsigned char* Qs = smem;
+    unsigned char* Kst = Qs + kQBytes;               // [2][kKBytes]
+    unsigned char* Vst = Kst + 2 * kKBytes;          // [2][kVBytes]
+    unsigned char* Ps = Vst + 2 * kVBytes;           // [2][kPBytes]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(Ps + 2 * kPBytes);
+    unsigned long long* q_full = bars;
+    unsigned long long* kv_full = bars + 1;    // [2]
+    unsigned long long* kv_empty = bars + 3;   // [2]
+    unsigned long long* s_full = bars + 5;     // [2]
+    unsigned long long* s_empty = bars + 7;    // [2]
+    unsigned long long* p_full = bars + 9;     // [2]
+    unsigned long long* p_empty = bars + 11;   // [2]
+    unsigned long long* o_full = bars + 13;
+    unsigned long long* x_full = bars + 14;    // the two halves of every row exchanged their statistics
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 15);
+    int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    float* stats = reinterpret_cast<float*>(bars + 16);  // [2 halves][128 rows][2]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int T = a.tokens;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvh = head / (a.heads / a.kv_heads);
+    const int q0 = qt * kTcRows;
+    const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
+    const int last_row = min(q0 + kTcRows, T) - 1;
+    const int n = a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_empty[s], kTcSoftmaxThreads);
+            mbar_init(&p_full[s], kTcSoftmaxThreads);
+            mbar_init(&p_empty[s], 1);
+        }
+        mbar_init(o_full, 1);
+        mbar_init(x_full, kTcSoftmaxThreads);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned int tmem_base = *tmem_slot;
+
+    auto give_up = [&](int where) {
+        record_status(ctl, MB_ST_PIPE_TIMEOUT, phase, where);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, kQBytes);
+            for (int kb = 0; kb < D / 64; ++kb)
+                tma_load_2d(Qs + kb * (kTcRows * 128), &maps.q, head * D + kb * 64, b * T + q0, q_full);
+            for (int g = 0; g < 2 * n; ++g) {
+                const int st = g & 1, jb = g < n ? g : g - n;
+                if (g >= 2 && !mbar_wait_bounded(&kv_empty[st], ((g >> 1) - 1) & 1, abort_flag)) {
+                    give_up(10);
+                    break;
+                }
+                const bool second = g >= n;
+                mbar_arrive_expect_tx(&kv_full[st], kKBytes + (second ? kVBytes : 0));
+                for (int kb = 0; kb < D / 64; ++kb)
+                    tma_load_2d(Kst + st * kKBytes + kb * (kAttnKeys * 128), &maps.k,
+                                kvh * D + kb * 64, b * T + jb * kAttnKeys, &kv_full[st]);
+                if (second)
+                    tma_load_2d(Vst + st * kVBytes, &maps.vt, jb * kAttnKeys,
+                                (b * a.kv_heads + kvh) * D, &kv_full[st]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned int idesc_s = (1u << 4) | (1u << 7) | (1u << 10) |
+                                         (static_cast<unsigned int>(kAttnKeys >> 3) << 17) |
+                                         (static_cast<unsigned int>(kTcRows >> 4) << 24);
+            const unsigned int idesc_o = (1u << 4) | (1u << 7) | (1u << 10) |
+                                         (static_cast<unsigned int>(D >> 3) << 17) |
+                                         (static_cast<unsigned int>(kTcRows >> 4) << 24);
+            bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
+            if (!ok) give_up(20);
+            // values . probabilities of step g (second sweep), issued one step late so that the
+            // scores of step g + 1 are already under way while the softmax of step g runs
+            auto issue_pv = [&](int g) {
+                const int st = g & 1;
+                if (!mbar_wait_bounded(&p_full[st], ((g - n) >> 1) & 1, abort_flag)) {
+                    give_up(21);
+                    return false;
+                }
+                tc_fence_after();
+                const unsigned long long dp = umma_desc(smem_u32(Ps + st * kPBytes));
+                const unsigned long long dv = umma_desc(smem_u32(Vst + st * kVBytes));
+#pragma unroll
+                for (int k = 0; k < kAttnKeys / 16; ++k)
+                    umma_bf16(tmem_base + kColO, dp + 2 * k, dv + 2 * k, idesc_o,
+                              (g > n || k > 0) ? 1u : 0u);
+                umma_commit(&kv_empty[st]);
+                umma_commit(&p_empty[st]);
+                return true;
+            };
+            for (int g = 0; ok && g < 2 * n; ++g) {
+                const int st = g & 1;
+                if (!mbar_wait_bounded(&kv_full[st], (g >> 1) & 1, abort_flag) ||
+                    (g >= 2 && !mbar_wait_bounded(&s_empty[st], ((g >> 1) - 1) & 1, abort_flag))) {
+                    give_up(22);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int kb = 0; kb < D / 64; ++kb) {
+                    const unsigned long long dq = umma_desc(smem_u32(Qs + kb * (kTcRows * 128)));
+                    const unsigned long long dk =
+                        umma_desc(smem_u32(Kst + st * kKBytes + kb * (kAttnKeys * 128)));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_base + st * kAttnKeys, dq + 2 * k, dk + 2 * k, idesc_s,
+                                  (kb | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[st]);
+                if (g < n) umma_commit(&kv_empty[st]);  // first sweep: the K stage is free again
+                if (g > n) ok = issue_pv(g - 1);
+            }
+            if (ok) ok = issue_pv(2 * n - 1);
+            if (ok) umma_commit(o_full);
+        }
+        __syncwarp();
+    } else {
+        const int sw = warp - 2;                 // 0..7
+        const int quarter = warp & 3;            // TMEM lanes this warp may touch
+        const int half = sw >> 2;                // which 32 key columns of a block
+        const int r = quarter * 32 + lane;       // row of the tile
+        const int row = q0 + r;
+        const unsigned int lane_addr = tmem_base + (static_cast<unsigned int>(quarter * 32) << 16);
+        const unsigned short* mrow = nullptr;
+        if (a.mask != nullptr)
+            mrow = a.mask + (a.mask_batch > 1 ? static_cast<size_t>(b) * T * T : 0) +
+                   static_cast<size_t>(min(row, T - 1)) * T;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int g = 0; g < 2 * n; ++g) {
+            const int st = g & 1, jb = g < n ? g : g - n;
+            ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[st], (g >> 1) & 1, abort_flag));
+            if (!ok) {
+                if (lane == 0) give_up(30);
+                break;
+            }
+            tc_fence_after();
+            float v[32];
+            tmem_load32(lane_addr + st * kAttnKeys + half * 32, v);
+            tc_fence_before();
+            mbar_arrive(&s_empty[st]);
+            const int key0 = jb * kAttnKeys + half * 32;
+            // scores with the operator's rounding points; -inf marks keys that are not visible
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int key = key0 + i;
+                float t = bf16_round(v[i]);
+                t = bf16_round(t * a.scale);
+                if (mrow != nullptr && key < T) t = bf16_round(t + bf16_bits_to_float(__ldg(mrow + key)));
+                v[i] = (key < T && (!a.causal || key <= row)) ? t : -INFINITY;
+            }
+            if (g < n) {
+                float bm = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) bm = fmaxf(bm, v[i]);
+                const float nm = fmaxf(m_run, bm);
+                l_run = nm == -INFINITY ? 0.f : l_run * expf(m_run - nm);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (v[i] != -INFINITY) l_run += expf(v[i] - nm);
+                m_run = nm;
+                if (g == n - 1) {
+                    // the two halves of a row meet: combine their maxima and denominators
+                    stats[(half * kTcRows + r) * 2] = m_run;
+                    stats[(half * kTcRows + r) * 2 + 1] = l_run;
+                    mbar_arrive(x_full);
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(x_full, 0, abort_flag))) {
+                        if (lane == 0) give_up(33);
+                        ok = false;
+                        break;
+                    }
+                    const float om = stats[((half ^ 1) * kTcRows + r) * 2];
+                    const float ol = stats[((half ^ 1) * kTcRows + r) * 2 + 1];
+                    const float fm = fmaxf(m_run, om);
+                    const float mine = m_run == -INFINITY ? 0.f : l_run * expf(m_run - fm);
+                    const float theirs = om == -INFINITY ? 0.f : ol * expf(om - fm);
+                    // the same order of the two terms in both halves, so both get the same sum
+                    l_run = half == 0 ? mine + theirs : theirs + mine;
+                    m_run = fm;
+                }
+            } else {
+                if (g >= n + 2 &&
+                    !__all_sync(0xffffffffu,
+                                mbar_wait_bounded(&p_empty[st], (((g - n) >> 1) - 1) & 1, abort_flag))) {
+                    if (lane == 0) give_up(31);
+                    ok = false;
+                    break;
+                }
+                unsigned int packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = v[2 * i] == -INFINITY ? 0.f : __fdiv_rn(expf(v[2 * i] - m_run), l_run);
+                    const float p1 = v[2 * i + 1] == -INFINITY ? 0.f : __fdiv_rn(expf(v[2 * i + 1] - m_run), l_run);
+                    packed[i] = pack_bf16(p0, p1);
+                }
+                // row r of the P tile: 128 bytes, 16-byte chunk c stored at c ^ (r % 8) (the
+                // 128-byte swizzle the MMA's shared-memory descriptor expects)
+                unsigned char* prow = Ps + st * kPBytes + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int chunk = (half * 4 + c) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                }
+                // generic-proxy writes must be visible to the tensor core's async-proxy reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&p_full[st]);
+            }
+        }
+        ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(o_full, 0, abort_flag));
+        if (!ok && lane == 0 && *abort_flag == 0) give_up(32);
+        tc_fence_after();
+        if (ok) {
+            unsigned short* orow = a.out + (static_cast<size_t>(b) * T + row) * (static_cast<size_t>(a.heads) * D) +
+                                   head * D + half * (D / 2);
+#pragma unroll 1
+            for (int c = 0; c < D / 64; ++c) {
+                float o[32];
+                tmem_load32(lane_addr + kColO + half * (D / 2) + c * 32, o);
+                if (row < T) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        reinterpret_cast<uint4*>(orow + c * 32)[q] =
+                            make_uint4(pack_bf16(o[8 * q], o[8 * q + 1]), pack_bf16(o[8 * q + 2], o[8 * q + 3]),
+                                       pack_bf16(o[8 * q + 4], o[8 * q + 5]), pack_bf16(o[8 * q + 6], o[8 * q + 7]));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+inline int attention_tc_smem_bytes(int D) {
+    return kTcRows * D * 2 + 2 * kAttnKeys * D * 2 + 2 * D * kAttnKeys * 2 + 2 * kTcRows * kAttnKeys * 2 +
+           16 * 8 + 2 * kTcRows * 2 * 4;
+}
+
+// ---------------------------------------------------------------------------------------
 // Host side: validation, tile / split-K geometry, tensor maps, launches.
 // ---------------------------------------------------------------------------------------
 namespace {
@@ -850,6 +1177,9 @@ struct PrefillLaunch {
     GemmArgs gemm;
     GemmGeometry geometry;
     AttnArgs attn;
+    AttnMaps attn_maps;
+    unsigned short* vt = nullptr;  // transposed values of the tensor-core attention, or null
+    int padded_tokens = 0;
 };
 
 }  // namespace prefill
@@ -930,6 +1260,7 @@ int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dyn
             for (int s = 0; s < 4; ++s)
                 if (!slot_ok(P.slot[s], true, false)) return MB_ERR_INVALID;
             if (!slot_ok(P.slot[MB_AP_S_MASK], false, false)) return MB_ERR_INVALID;
+            if (!slot_ok(P.slot[MB_AP_S_VT], false, false)) return MB_ERR_INVALID;
             if (P.slot[MB_AP_S_MASK] >= 0 && P.i[MB_AP_I_MASK_BATCH] != 1 &&
                 P.i[MB_AP_I_MASK_BATCH] != P.i[MB_AP_I_BATCH])
                 return MB_ERR_INVALID;
@@ -976,6 +1307,15 @@ cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillS
     if (err == cudaSuccess)
         err = cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gemm_smem_bytes(256, 4));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   attention_tc_smem_bytes(64));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   attention_tc_smem_bytes(128));
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(attention_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   attention_tc_smem_bytes(256));
     if (err == cudaSuccess) err = attn_configure<64>();
     if (err == cudaSuccess) err = attn_configure<128>();
     if (err == cudaSuccess) err = attn_configure<256>();
@@ -1052,6 +1392,17 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
             a.causal = P.i[MB_AP_I_CAUSAL];
             a.mask_batch = P.i[MB_AP_I_MASK_BATCH];
             a.scale = P.f[MB_AP_F_SCALE];
+            L.vt = reinterpret_cast<unsigned short*>(addr(P.slot[MB_AP_S_VT]));
+            if (L.vt != nullptr) {
+                const int D = P.i[MB_AP_I_HEAD_DIM];
+                const int rows = a.batch * a.tokens;
+                L.padded_tokens = (a.tokens + kAttnKeys - 1) / kAttnKeys * kAttnKeys;
+                if (!make_map(&L.attn_maps.q, addr(P.slot[MB_AP_S_Q]), rows, a.heads * D, kTcRows) ||
+                    !make_map(&L.attn_maps.k, addr(P.slot[MB_AP_S_K]), rows, a.kv_heads * D, kAttnKeys) ||
+                    !make_map(&L.attn_maps.vt, addr(P.slot[MB_AP_S_VT]), a.batch * a.kv_heads * D,
+                              L.padded_tokens, D))
+                    return MB_ERR_CUDA;
+            }
         }
     }
     return MB_OK;
@@ -1117,6 +1468,22 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
             }
             case MB_BODY_ATTN_PREFILL: {
                 const int D = P.i[MB_AP_I_HEAD_DIM];
+                if (L.vt != nullptr) {
+                    const AttnArgs& a = L.attn;
+                    const dim3 tgrid(L.padded_tokens / 64, D / 64, a.batch * a.kv_heads);
+                    transpose_values_kernel<<<tgrid, 256, 0, stream>>>(a.v, L.vt, a.tokens,
+                                                                       L.padded_tokens, a.kv_heads, D);
+                    const dim3 grid((a.tokens + kTcRows - 1) / kTcRows, a.heads, a.batch);
+                    const int smem = attention_tc_smem_bytes(D);
+                    const int ph = static_cast<int>(i);
+                    if (D == 64)
+                        attention_tc_kernel<64><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                    else if (D == 128)
+                        attention_tc_kernel<128><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                    else
+                        attention_tc_kernel<256><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                    break;
+                }
                 cudaError_t launched = D == 64    ? attn_launch<64>(L.attn, stream)
                                        : D == 128 ? attn_launch<128>(L.attn, stream)
                                                   : attn_launch<256>(L.attn, stream);

@@ -406,6 +406,8 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
     v_buf = slots.buffer(R * kv_dim * 2, "v")
     attn = slots.buffer(R * q_dim * 2, "attention")
     glu = slots.buffer(R * p.intermediate * 2, "gated")
+    padded = (T + 63) // 64 * 64
+    v_t = slots.buffer(B * kv_dim * padded * 2, "values_transposed")
     constants = {}
     mask_slot = -1
     if not p.causal:
@@ -474,6 +476,7 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
         attention.f[rt.AP_F_SCALE] = p.softmax_scale
         attention.slot[rt.AP_S_Q], attention.slot[rt.AP_S_K], attention.slot[rt.AP_S_V] = q_buf, k_buf, v_buf
         attention.slot[rt.AP_S_OUT], attention.slot[rt.AP_S_MASK] = attn, mask_slot
+        attention.slot[rt.AP_S_VT] = v_t
         phases.append(attention)
         gemm(k=q_dim, x_slot=attn, epilogue=rt.EPI_RESIDUAL, residual_slot=hidden, segments=[
             (H, slots.arg(layer.o_weight, tag + "o_proj.weight"),

@@ -58,7 +58,7 @@ RP_S_Q, RP_S_K, RP_S_POS, RP_S_INVFREQ = 0, 1, 2, 3
 AP_I_BATCH, AP_I_TOKENS, AP_I_HEADS, AP_I_KV_HEADS, AP_I_HEAD_DIM = 0, 1, 2, 3, 4
 AP_I_CAUSAL, AP_I_MASK_BATCH = 5, 6
 AP_F_SCALE = 0
-AP_S_Q, AP_S_K, AP_S_V, AP_S_OUT, AP_S_MASK = 0, 1, 2, 3, 4
+AP_S_Q, AP_S_K, AP_S_V, AP_S_OUT, AP_S_MASK, AP_S_VT = 0, 1, 2, 3, 4, 5
 
 STATUS_NAMES = {
     0: "ok", 1: "barrier-timeout", 2: "pipeline-timeout", 3: "kv-overflow", 4: "token-range",

@@ -222,10 +222,11 @@ def test_rope_rows(rows, heads, kv_heads, dim):
 
 @pytest.mark.parametrize("batch,tokens,heads,kv_heads,dim", [
     (2, 12, 4, 2, 64), (1, 64, 2, 2, 64), (1, 200, 8, 1, 256), (2, 130, 4, 4, 128),
-    (1, 700, 9, 3, 64),
+    (1, 700, 9, 3, 64), (1, 1100, 2, 1, 256),
 ])
 @pytest.mark.parametrize("explicit_mask", [False, True])
-def test_attention_prefill(batch, tokens, heads, kv_heads, dim, explicit_mask):
+@pytest.mark.parametrize("tensor_core", [True, False])
+def test_attention_prefill(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core):
     q = _bf16(batch, tokens, heads, dim, seed=tokens)
     k = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 1)
     v = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 2)
@@ -247,6 +248,10 @@ def test_attention_prefill(batch, tokens, heads, kv_heads, dim, explicit_mask):
     ph.slot[rt.AP_S_OUT] = runner.slot("o", out)
     if explicit_mask:
         ph.slot[rt.AP_S_MASK] = runner.slot("m", mask.cuda())
+    if tensor_core:   # scratch for the transposed values selects the tcgen05 kernel
+        padded = (tokens + 63) // 64 * 64
+        ph.slot[rt.AP_S_VT] = runner.slot("vt", torch.full(
+            (batch * kv_heads * dim, padded), float("nan"), dtype=torch.bfloat16, device="cuda"))
     _run(runner, [ph])
     assert max_abs(out, ref) <= 2e-2, max_abs(out, ref)
     assert cosine(out, ref) > 0.9999
