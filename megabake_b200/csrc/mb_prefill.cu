@@ -184,6 +184,22 @@ __device__ __forceinline__ void tmem_load32(unsigned int taddr, float (&v)[32]) 
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_load16(unsigned int taddr, float (&v)[16]) {
+    unsigned int r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // ---------------------------------------------------------------------------------------
 // The GEMM
 // ---------------------------------------------------------------------------------------
@@ -758,14 +774,19 @@ cudaError_t attn_configure() {
 // with accumulators in tensor memory; the softmax between them runs on eight warps that read
 // S with tcgen05.ld (one thread per row and half a key block, so no shuffles), and write the
 // bf16 probabilities into shared memory in the 128-byte-swizzled K-major layout the second
-// MMA reads them in.  V is consumed transposed ([head_dim, keys], keys contiguous) so that
+// MMA reads them in.  exp and the division by the row sum use the device's fast forms
+// (ex2.approx, multiplication by the reciprocal): the result is rounded to bf16 right after, so
+// they change a probability only when it sits within 2^-14 of a rounding boundary.  V is consumed transposed ([head_dim, keys], keys contiguous) so that
 // every operand is K-major; a small kernel transposes V once per layer.
 //
 // Same two sweeps and rounding points as attention_prefill_kernel above.
-//   warp 0      TMA producer: Q once, then K (and V^T) blocks into a two-stage ring
+//   warp 0      TMA producers: lane 0 loads Q once and then K blocks, lane 1 the V^T blocks,
+//               each into its own two-stage ring (a K stage is free again as soon as the
+//               scores that read it are done, a V stage after the P . V that read it)
 //   warp 1      MMA issuer, owner of the tensor-memory allocation
-//   warps 2-9   softmax; warp w works on TMEM lanes 32 * (w % 4) .. and key columns
-//               32 * ((w - 2) / 4) .. of a block
+//   warps 2-17  softmax; warp w works on TMEM lanes 32 * (w % 4) .. and key columns
+//               16 * ((w - 2) / 4) .. of a block (sixteen warps: the softmax, not the tensor
+//               cores, is the long pole of a step, and it is latency-bound per warp)
 // Tensor memory: S double-buffered in columns [0, 64) and [64, 128), O in [128, 128 + D).
 // ---------------------------------------------------------------------------------------
 struct AttnMaps {
@@ -775,8 +796,8 @@ struct AttnMaps {
 };
 
 constexpr int kTcRows = 128;
-constexpr int kTcThreads = 320;
-constexpr int kTcSoftmaxThreads = 256;
+constexpr int kTcThreads = 64 + 16 * 32;
+constexpr int kTcSoftmaxWarps = 16;  // one elected lane per warp arrives on the shared barriers
 
 // V [batch * tokens, kv_heads * D] -> V^T [batch * kv_heads * D, padded], zero beyond `tokens`
 __global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned short* v,
@@ -824,17 +845,21 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
     unsigned char* Ps = Vst + 2 * kVBytes;           // [2][kPBytes]
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(Ps + 2 * kPBytes);
     unsigned long long* q_full = bars;
-    unsigned long long* kv_full = bars + 1;    // [2]
-    unsigned long long* kv_empty = bars + 3;   // [2]
+    unsigned long long* k_full = bars + 1;     // [2]
+    unsigned long long* k_empty = bars + 3;    // [2]
     unsigned long long* s_full = bars + 5;     // [2]
     unsigned long long* s_empty = bars + 7;    // [2]
     unsigned long long* p_full = bars + 9;     // [2]
     unsigned long long* p_empty = bars + 11;   // [2]
     unsigned long long* o_full = bars + 13;
-    unsigned long long* x_full = bars + 14;    // the two halves of every row exchanged their statistics
-    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 15);
+    unsigned long long* x_full = bars + 14;    // the column parts of every row exchanged their statistics
+    unsigned long long* v_full = bars + 15;    // [2]
+    unsigned long long* v_empty = bars + 17;   // [2]
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 19);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-    float* stats = reinterpret_cast<float*>(bars + 16);  // [2 halves][128 rows][2]
+    // row statistics of the four column parts meet here once, between the sweeps (the first P
+    // buffer is idle until then)
+    float* stats = reinterpret_cast<float*>(Ps);  // [4 parts][128 rows][2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int T = a.tokens;
@@ -849,15 +874,17 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_empty[s], kTcSoftmaxThreads);
-            mbar_init(&p_full[s], kTcSoftmaxThreads);
+            mbar_init(&s_empty[s], kTcSoftmaxWarps);
+            mbar_init(&p_full[s], kTcSoftmaxWarps);
             mbar_init(&p_empty[s], 1);
         }
         mbar_init(o_full, 1);
-        mbar_init(x_full, kTcSoftmaxThreads);
+        mbar_init(x_full, kTcSoftmaxWarps);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -879,18 +906,25 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 tma_load_2d(Qs + kb * (kTcRows * 128), &maps.q, head * D + kb * 64, b * T + q0, q_full);
             for (int g = 0; g < 2 * n; ++g) {
                 const int st = g & 1, jb = g < n ? g : g - n;
-                if (g >= 2 && !mbar_wait_bounded(&kv_empty[st], ((g >> 1) - 1) & 1, abort_flag)) {
+                if (g >= 2 && !mbar_wait_bounded(&k_empty[st], ((g >> 1) - 1) & 1, abort_flag)) {
                     give_up(10);
                     break;
                 }
-                const bool second = g >= n;
-                mbar_arrive_expect_tx(&kv_full[st], kKBytes + (second ? kVBytes : 0));
+                mbar_arrive_expect_tx(&k_full[st], kKBytes);
                 for (int kb = 0; kb < D / 64; ++kb)
                     tma_load_2d(Kst + st * kKBytes + kb * (kAttnKeys * 128), &maps.k,
-                                kvh * D + kb * 64, b * T + jb * kAttnKeys, &kv_full[st]);
-                if (second)
-                    tma_load_2d(Vst + st * kVBytes, &maps.vt, jb * kAttnKeys,
-                                (b * a.kv_heads + kvh) * D, &kv_full[st]);
+                                kvh * D + kb * 64, b * T + jb * kAttnKeys, &k_full[st]);
+            }
+        } else if (lane == 1) {
+            for (int j = 0; j < n; ++j) {  // second sweep only
+                const int sv = j & 1;
+                if (j >= 2 && !mbar_wait_bounded(&v_empty[sv], ((j >> 1) - 1) & 1, abort_flag)) {
+                    give_up(11);
+                    break;
+                }
+                mbar_arrive_expect_tx(&v_full[sv], kVBytes);
+                tma_load_2d(Vst + sv * kVBytes, &maps.vt, j * kAttnKeys, (b * a.kv_heads + kvh) * D,
+                            &v_full[sv]);
             }
         }
         __syncwarp();
@@ -907,25 +941,26 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             // values . probabilities of step g (second sweep), issued one step late so that the
             // scores of step g + 1 are already under way while the softmax of step g runs
             auto issue_pv = [&](int g) {
-                const int st = g & 1;
-                if (!mbar_wait_bounded(&p_full[st], ((g - n) >> 1) & 1, abort_flag)) {
+                const int st = g & 1, sv = (g - n) & 1;
+                if (!mbar_wait_bounded(&v_full[sv], ((g - n) >> 1) & 1, abort_flag) ||
+                    !mbar_wait_bounded(&p_full[st], ((g - n) >> 1) & 1, abort_flag)) {
                     give_up(21);
                     return false;
                 }
                 tc_fence_after();
                 const unsigned long long dp = umma_desc(smem_u32(Ps + st * kPBytes));
-                const unsigned long long dv = umma_desc(smem_u32(Vst + st * kVBytes));
+                const unsigned long long dv = umma_desc(smem_u32(Vst + sv * kVBytes));
 #pragma unroll
                 for (int k = 0; k < kAttnKeys / 16; ++k)
                     umma_bf16(tmem_base + kColO, dp + 2 * k, dv + 2 * k, idesc_o,
                               (g > n || k > 0) ? 1u : 0u);
-                umma_commit(&kv_empty[st]);
+                umma_commit(&v_empty[sv]);
                 umma_commit(&p_empty[st]);
                 return true;
             };
             for (int g = 0; ok && g < 2 * n; ++g) {
                 const int st = g & 1;
-                if (!mbar_wait_bounded(&kv_full[st], (g >> 1) & 1, abort_flag) ||
+                if (!mbar_wait_bounded(&k_full[st], (g >> 1) & 1, abort_flag) ||
                     (g >= 2 && !mbar_wait_bounded(&s_empty[st], ((g >> 1) - 1) & 1, abort_flag))) {
                     give_up(22);
                     ok = false;
@@ -943,7 +978,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                                   (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[st]);
-                if (g < n) umma_commit(&kv_empty[st]);  // first sweep: the K stage is free again
+                umma_commit(&k_empty[st]);  // the K stage is free as soon as these MMAs have read it
                 if (g > n) ok = issue_pv(g - 1);
             }
             if (ok) ok = issue_pv(2 * n - 1);
@@ -951,9 +986,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
         }
         __syncwarp();
     } else {
-        const int sw = warp - 2;                 // 0..7
         const int quarter = warp & 3;            // TMEM lanes this warp may touch
-        const int half = sw >> 2;                // which 32 key columns of a block
+        const int part = (warp - 2) >> 2;        // which 16 key columns of a block
         const int r = quarter * 32 + lane;       // row of the tile
         const int row = q0 + r;
         const unsigned int lane_addr = tmem_base + (static_cast<unsigned int>(quarter * 32) << 16);
@@ -961,7 +995,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
         if (a.mask != nullptr)
             mrow = a.mask + (a.mask_batch > 1 ? static_cast<size_t>(b) * T * T : 0) +
                    static_cast<size_t>(min(row, T - 1)) * T;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, inv_l = 0.f;
         bool ok = true;
         for (int g = 0; g < 2 * n; ++g) {
             const int st = g & 1, jb = g < n ? g : g - n;
@@ -971,14 +1005,15 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 break;
             }
             tc_fence_after();
-            float v[32];
-            tmem_load32(lane_addr + st * kAttnKeys + half * 32, v);
+            float v[16];
+            tmem_load16(lane_addr + st * kAttnKeys + part * 16, v);
             tc_fence_before();
-            mbar_arrive(&s_empty[st]);
-            const int key0 = jb * kAttnKeys + half * 32;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[st]);  // per-thread arrivals would serialise
+            const int key0 = jb * kAttnKeys + part * 16;
             // scores with the operator's rounding points; -inf marks keys that are not visible
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 16; ++i) {
                 const int key = key0 + i;
                 float t = bf16_round(v[i]);
                 t = bf16_round(t * a.scale);
@@ -988,31 +1023,48 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             if (g < n) {
                 float bm = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) bm = fmaxf(bm, v[i]);
+                for (int i = 0; i < 16; ++i) bm = fmaxf(bm, v[i]);
                 const float nm = fmaxf(m_run, bm);
-                l_run = nm == -INFINITY ? 0.f : l_run * expf(m_run - nm);
+                // exp(-inf - x) is 0 for every finite x: invisible keys need no branch, only a
+                // maximum that is still -inf must not be subtracted
+                const float base = nm == -INFINITY ? 0.f : nm;
+                float sum = l_run * __expf(m_run - base);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (v[i] != -INFINITY) l_run += expf(v[i] - nm);
+                for (int i = 0; i < 16; ++i) sum += __expf(v[i] - base);
+                l_run = sum;
                 m_run = nm;
                 if (g == n - 1) {
-                    // the two halves of a row meet: combine their maxima and denominators
-                    stats[(half * kTcRows + r) * 2] = m_run;
-                    stats[(half * kTcRows + r) * 2 + 1] = l_run;
-                    mbar_arrive(x_full);
+                    // the four parts of a row meet: combine their maxima and denominators, in
+                    // part order, so that all four get the same sum
+                    stats[(part * kTcRows + r) * 2] = m_run;
+                    stats[(part * kTcRows + r) * 2 + 1] = l_run;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(x_full);
                     if (!__all_sync(0xffffffffu, mbar_wait_bounded(x_full, 0, abort_flag))) {
                         if (lane == 0) give_up(33);
                         ok = false;
                         break;
                     }
-                    const float om = stats[((half ^ 1) * kTcRows + r) * 2];
-                    const float ol = stats[((half ^ 1) * kTcRows + r) * 2 + 1];
-                    const float fm = fmaxf(m_run, om);
-                    const float mine = m_run == -INFINITY ? 0.f : l_run * expf(m_run - fm);
-                    const float theirs = om == -INFINITY ? 0.f : ol * expf(om - fm);
-                    // the same order of the two terms in both halves, so both get the same sum
-                    l_run = half == 0 ? mine + theirs : theirs + mine;
-                    m_run = fm;
+                    float fm = -INFINITY;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) fm = fmaxf(fm, stats[(q * kTcRows + r) * 2]);
+                    const float fbase = fm == -INFINITY ? 0.f : fm;
+                    float total = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        total += stats[(q * kTcRows + r) * 2 + 1] *
+                                 __expf(stats[(q * kTcRows + r) * 2] - fbase);
+                    m_run = fbase;
+                    inv_l = total > 0.f ? __frcp_rn(total) : 0.f;
+                    // nobody may overwrite the statistics (they alias the first P tile) before
+                    // every warp has read them
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(x_full);
+                    if (!__all_sync(0xffffffffu, mbar_wait_bounded(x_full, 1, abort_flag))) {
+                        if (lane == 0) give_up(34);
+                        ok = false;
+                        break;
+                    }
                 }
             } else {
                 if (g >= n + 2 &&
@@ -1022,25 +1074,24 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                     ok = false;
                     break;
                 }
-                unsigned int packed[16];
+                unsigned int packed[8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float p0 = v[2 * i] == -INFINITY ? 0.f : __fdiv_rn(expf(v[2 * i] - m_run), l_run);
-                    const float p1 = v[2 * i + 1] == -INFINITY ? 0.f : __fdiv_rn(expf(v[2 * i + 1] - m_run), l_run);
-                    packed[i] = pack_bf16(p0, p1);
-                }
+                for (int i = 0; i < 8; ++i)
+                    packed[i] = pack_bf16(__expf(v[2 * i] - m_run) * inv_l,
+                                          __expf(v[2 * i + 1] - m_run) * inv_l);
                 // row r of the P tile: 128 bytes, 16-byte chunk c stored at c ^ (r % 8) (the
                 // 128-byte swizzle the MMA's shared-memory descriptor expects)
                 unsigned char* prow = Ps + st * kPBytes + r * 128;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int chunk = (half * 4 + c) ^ (r & 7);
+                for (int c = 0; c < 2; ++c) {
+                    const int chunk = (part * 2 + c) ^ (r & 7);
                     *reinterpret_cast<uint4*>(prow + chunk * 16) =
                         make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
                 }
                 // generic-proxy writes must be visible to the tensor core's async-proxy reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&p_full[st]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[st]);
             }
         }
         ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(o_full, 0, abort_flag));
@@ -1048,15 +1099,15 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
         tc_fence_after();
         if (ok) {
             unsigned short* orow = a.out + (static_cast<size_t>(b) * T + row) * (static_cast<size_t>(a.heads) * D) +
-                                   head * D + half * (D / 2);
+                                   head * D + part * (D / 4);
 #pragma unroll 1
             for (int c = 0; c < D / 64; ++c) {
-                float o[32];
-                tmem_load32(lane_addr + kColO + half * (D / 2) + c * 32, o);
+                float o[16];
+                tmem_load16(lane_addr + kColO + part * (D / 4) + c * 16, o);
                 if (row < T) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        reinterpret_cast<uint4*>(orow + c * 32)[q] =
+                    for (int q = 0; q < 2; ++q)
+                        reinterpret_cast<uint4*>(orow + c * 16)[q] =
                             make_uint4(pack_bf16(o[8 * q], o[8 * q + 1]), pack_bf16(o[8 * q + 2], o[8 * q + 3]),
                                        pack_bf16(o[8 * q + 4], o[8 * q + 5]), pack_bf16(o[8 * q + 6], o[8 * q + 7]));
                 }
@@ -1075,7 +1126,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
 
 inline int attention_tc_smem_bytes(int D) {
     return kTcRows * D * 2 + 2 * kAttnKeys * D * 2 + 2 * D * kAttnKeys * 2 + 2 * kTcRows * kAttnKeys * 2 +
-           16 * 8 + 2 * kTcRows * 2 * 4;
+           20 * 8;
 }
 
 // ---------------------------------------------------------------------------------------
