@@ -11,7 +11,8 @@
 //   rope_rows_kernel       rotary embedding of q and k rows in place
 //   attention_prefill_kernel   masked softmax attention with the eager rounding points
 //
-// No load in this file uses cluster multicast.  Every wait is bounded and reports through
+// Every load in this file is a plain (single-CTA) TMA or cp.async load, so the library runs
+// unchanged at any GPU count.  Every wait is bounded and reports through
 // the plan's status word.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -1190,6 +1191,10 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         return tiles;
     };
     g.bn = count(256) * g.tiles_m >= sm_count ? 256 : 128;
+    if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_BN")) {
+        const int value = std::atoi(forced);
+        if (value == 128 || value == 256) g.bn = value;
+    }
     // two CTAs per SM: while one runs its epilogue the other one keeps the tensor cores busy
     g.stages = g.bn == 256 ? 2 : 3;
     if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_STAGES")) {
@@ -1203,12 +1208,14 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         if (s < P.i[MB_GV_I_NSEG]) tiles += (P.i[MB_GV_I_N0 + s] + per - 1) / per;
     }
     g.tiles_n = tiles;
-    // split the reduction when the output tiles alone leave most SMs idle
+    // split the reduction when the output tiles alone leave SMs idle: aim at two CTAs per SM,
+    // keep at least eight k-blocks per CTA (measured: shorter slices lose more to the pipeline
+    // fill and the partial-sum round trip than they gain)
     int split = 1;
     const int ctas = g.tiles_n * g.tiles_m;
-    if (ctas * 2 <= sm_count) {
-        split = sm_count / ctas;
-        if (split > g.kblocks / 4) split = g.kblocks / 4;
+    if (ctas < sm_count) {
+        split = 2 * sm_count / ctas;
+        if (split > g.kblocks / 8) split = g.kblocks / 8;
         if (split > 16) split = 16;
         if (split < 1) split = 1;
     }
