@@ -209,18 +209,24 @@ typedef struct mb_phase {
  * MB_GV_I_TILE_N.                                                                          */
 #define MB_GV_I_SPLIT_K 16   /* CTAs sharing one output tile along the reduction           */
 #define MB_GV_I_TILE_N 17    /* output columns per tile: 128 or 256 (per matrix: half)     */
+#define MB_GV_I_OUT_TOKENS 18   /* > 0: segments 1 and 2 (k, v) write row r at                 */
+#define MB_GV_I_OUT_CAPACITY 19 /* (r / TOKENS) * CAPACITY + r % TOKENS: straight into KV caches */
 /* MB_BODY_ROPE_ROWS: rotary embedding of q and k rows, in place                            */
 #define MB_RP_I_ROWS 0
 #define MB_RP_I_HEADS 1
 #define MB_RP_I_KV_HEADS 2
 #define MB_RP_I_HEAD_DIM 3
 #define MB_RP_I_INVFREQ_BF16 4
+#define MB_RP_I_K_TOKENS 5    /* > 0: k rows live in a cache, row r at (r / TOKENS) * CAPACITY   */
+#define MB_RP_I_K_CAPACITY 6  /*      + r % TOKENS                                                */
+#define MB_RP_I_LEN_VALUE 7   /* written to the int32 at MB_RP_S_LEN, if that slot is given       */
 #define MB_RP_F_ROPE_SCALE 0
 #define MB_RP_F_Q_SCALE 1    /* 0 or 1 = none; else q = bf16(q * this) after the rotation  */
 #define MB_RP_S_Q 0          /* [rows, heads * D] bf16                                     */
 #define MB_RP_S_K 1          /* [rows, kv_heads * D] bf16                                  */
 #define MB_RP_S_POS 2        /* int64 [rows]                                               */
 #define MB_RP_S_INVFREQ 3    /* [D / 2]                                                    */
+#define MB_RP_S_LEN 4        /* optional int32 [1]: the layer's valid length (state handoff) */
 /* MB_BODY_ATTN_PREFILL: softmax attention with the eager operator's rounding points:
  * s = bf16(q . k), s = bf16(s * scale), s = bf16(s + mask), p = bf16(softmax_fp32(s)),
  * out = bf16(sum p v).                                                                     */
@@ -231,6 +237,7 @@ typedef struct mb_phase {
 #define MB_AP_I_HEAD_DIM 4   /* 64, 128 or 256                                             */
 #define MB_AP_I_CAUSAL 5     /* 1: key j visible to query i iff j <= i, no mask tensor      */
 #define MB_AP_I_MASK_BATCH 6 /* leading extent of the mask tensor: 1 or batch              */
+#define MB_AP_I_KV_CAPACITY 7 /* rows per batch of the K and V tensors (a KV cache); 0 = tokens */
 #define MB_AP_F_SCALE 0
 #define MB_AP_S_Q 0          /* [batch * tokens, heads * D] bf16 (after RoPE)              */
 #define MB_AP_S_K 1          /* [batch * tokens, kv_heads * D]                             */

@@ -9,6 +9,7 @@ parts of it this backend keeps):
 ``kv_attention`` / ``attention``    the declared attention operators (``torch.ops.megabake.*``)
 ``DecodeStep``, ``StatefulDecoder`` explicit-state decode wrappers for Hugging Face models
 ``PrefillLogits``                   ids -> logits prefill wrapper over ``megabake::attention``
+``StatefulPrefill``                 prefill that also fills the explicit decode state
 ``register_transformers_attention`` the ``"megabake"`` attention implementation for HF models
 ``CompilerError``                   every refusal, with a staged diagnostic
 """
@@ -18,7 +19,7 @@ from .ops import attention, kv_attention
 
 __all__ = [
     "CompilerDiagnostic", "CompilerError", "DecodeStep", "PrefillLogits", "StatefulDecoder",
-    "attention",
+    "StatefulPrefill", "attention",
     "graphed", "kv_attention", "make_backend", "register_transformers_attention",
 ]
 
@@ -31,7 +32,7 @@ def __getattr__(name):
     if name in ("graphed", "GraphedCall", "BoundDecoder"):
         from . import engine
         return getattr(engine, name)
-    if name in ("DecodeStep", "PrefillLogits", "StatefulDecoder",
+    if name in ("DecodeStep", "PrefillLogits", "StatefulDecoder", "StatefulPrefill",
                 "register_transformers_attention"):
         from . import hf
         return getattr(hf, name)

@@ -73,21 +73,22 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(const unsigned short*
     for (int v = lane; v < K / 8; v += 32) dst[v] = normalise_vector(src[v], __ldg(wv + v), inv, kind);
 }
 
-// Thread e rotates the element pair (i, i + D/2) of one head row, with the rounding points
-// of the eager graph: cos/sin tables in bf16, every product and the sum rounded to bf16.
+// One thread per (row, i): the cos / sin pair of that position and frequency is computed once
+// and applied to element pair (i, i + D/2) of every q and k head of the row, with the rounding
+// points of the eager graph: tables in bf16, every product and the sum rounded to bf16.
 __global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsigned short* k,
                                                         const long long* pos, const void* inv_freq,
                                                         int rows, int heads, int kv_heads, int D,
                                                         int invfreq_bf16, float rope_scale,
-                                                        float q_scale) {
+                                                        float q_scale, int k_tokens, int k_capacity,
+                                                        int* length, int length_value) {
     const int half = D / 2;
-    const int per_row = (heads + kv_heads) * half;
-    const long long total = static_cast<long long>(rows) * per_row;
+    const long long total = static_cast<long long>(rows) * half;
+    if (length != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *length = length_value;
     for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
          e += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int r = static_cast<int>(e / per_row);
-        const int rem = static_cast<int>(e - static_cast<long long>(r) * per_row);
-        const int head = rem / half, i = rem - head * half;
+        const int r = static_cast<int>(e / half);
+        const int i = static_cast<int>(e - static_cast<long long>(r) * half);
         const float f = invfreq_bf16
                             ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(inv_freq)[i])
                             : reinterpret_cast<const float*>(inv_freq)[i];
@@ -95,18 +96,23 @@ __global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsig
         float sn, cn;
         sincosf(angle, &sn, &cn);
         const float c = bf16_round(cn * rope_scale), s = bf16_round(sn * rope_scale);
-        const bool is_q = head < heads;
-        unsigned short* row = is_q ? q + (static_cast<size_t>(r) * heads + head) * D
-                                   : k + (static_cast<size_t>(r) * kv_heads + (head - heads)) * D;
-        const float x1 = bf16_bits_to_float(row[i]), x2 = bf16_bits_to_float(row[i + half]);
-        float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
-        float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
-        if (is_q && q_scale != 0.f && q_scale != 1.f) {
-            r1 = bf16_round(r1 * q_scale);
-            r2 = bf16_round(r2 * q_scale);
+        for (int head = 0; head < heads + kv_heads; ++head) {
+            const bool is_q = head < heads;
+            // k rows may live in a KV cache: batch b's rows start at b * capacity
+            const size_t k_row = k_tokens > 0 ? static_cast<size_t>(r / k_tokens) * k_capacity + r % k_tokens
+                                              : static_cast<size_t>(r);
+            unsigned short* row = is_q ? q + (static_cast<size_t>(r) * heads + head) * D
+                                       : k + (k_row * kv_heads + (head - heads)) * D;
+            const float x1 = bf16_bits_to_float(row[i]), x2 = bf16_bits_to_float(row[i + half]);
+            float r1 = bf16_round(bf16_round(x1 * c) + bf16_round(-x2 * s));
+            float r2 = bf16_round(bf16_round(x2 * c) + bf16_round(x1 * s));
+            if (is_q && q_scale != 0.f && q_scale != 1.f) {
+                r1 = bf16_round(r1 * q_scale);
+                r2 = bf16_round(r2 * q_scale);
+            }
+            row[i] = float_to_bf16_bits(r1);
+            row[i + half] = float_to_bf16_bits(r2);
         }
-        row[i] = float_to_bf16_bits(r1);
-        row[i + half] = float_to_bf16_bits(r2);
     }
 }
 
@@ -217,6 +223,7 @@ struct GemmMaps {
 struct GemmArgs {
     int M, K, kblocks, split_k, stages, phase;
     int nseg, pair, epilogue;
+    int out_tokens, out_capacity;  // > 0: segments 1, 2 write row r at (r / tokens) * capacity + r % tokens
     int n[3];
     int tile_start[3];  // first n-tile of each segment
     int tiles_n;        // n-tiles over all segments
@@ -272,7 +279,10 @@ __device__ __forceinline__ void gemm_write_rows(const GemmArgs& a, int seg, int 
         const int row = row0 + r, col = n0 + c;
         if (row >= a.M || col >= n) continue;
         uint4 t = *reinterpret_cast<const uint4*>(stage + r * pitch + c * 2);
-        const size_t at = static_cast<size_t>(row) * n + col;
+        const size_t out_row = (seg >= 1 && a.out_tokens > 0)
+                                   ? static_cast<size_t>(row / a.out_tokens) * a.out_capacity + row % a.out_tokens
+                                   : static_cast<size_t>(row);
+        const size_t at = out_row * n + col;
         if ((n & 7) == 0) {
             if (res != nullptr) {
                 const uint4 h = *reinterpret_cast<const uint4*>(res + at);
@@ -507,6 +517,7 @@ struct AttnArgs {
     unsigned short* out;
     const unsigned short* mask;  // additive, [mask_batch, 1, T, T], or null
     int batch, tokens, heads, kv_heads, causal, mask_batch;
+    int kv_rows;  // rows per batch of the K and V tensors (tokens, or a cache's capacity)
     float scale;
 };
 
@@ -584,8 +595,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_prefill_kernel(const 
     const size_t q_stride = static_cast<size_t>(a.heads) * D;
     const size_t kv_stride = static_cast<size_t>(a.kv_heads) * D;
     const unsigned short* qbase = a.q + static_cast<size_t>(b) * T * q_stride + head * D;
-    const unsigned short* kbase = a.k + static_cast<size_t>(b) * T * kv_stride + kvh * D;
-    const unsigned short* vbase = a.v + static_cast<size_t>(b) * T * kv_stride + kvh * D;
+    const unsigned short* kbase = a.k + static_cast<size_t>(b) * a.kv_rows * kv_stride + kvh * D;
+    const unsigned short* vbase = a.v + static_cast<size_t>(b) * a.kv_rows * kv_stride + kvh * D;
     const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
     const int last_row = min(q0 + ROWS, T) - 1;
     const int nblocks = a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
@@ -803,7 +814,8 @@ constexpr int kTcSoftmaxWarps = 16;  // one elected lane per warp arrives on the
 // V [batch * tokens, kv_heads * D] -> V^T [batch * kv_heads * D, padded], zero beyond `tokens`
 __global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned short* v,
                                                                unsigned short* vt, int tokens,
-                                                               int padded, int kv_heads, int D) {
+                                                               int padded, int kv_heads, int D,
+                                                               int kv_rows) {
     __shared__ unsigned short tile[64][66];
     const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
     const int bh = blockIdx.z, b = bh / kv_heads, h = bh - b * kv_heads;
@@ -811,7 +823,7 @@ __global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned sh
     for (int e = threadIdx.x; e < 64 * 64; e += 256) {
         const int t = e >> 6, d = e & 63;
         tile[t][d] = t0 + t < tokens
-                         ? v[(static_cast<size_t>(b) * tokens + t0 + t) * row_stride + h * D + d0 + d]
+                         ? v[(static_cast<size_t>(b) * kv_rows + t0 + t) * row_stride + h * D + d0 + d]
                          : static_cast<unsigned short>(0);
     }
     __syncthreads();
@@ -914,7 +926,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 mbar_arrive_expect_tx(&k_full[st], kKBytes);
                 for (int kb = 0; kb < D / 64; ++kb)
                     tma_load_2d(Kst + st * kKBytes + kb * (kAttnKeys * 128), &maps.k,
-                                kvh * D + kb * 64, b * T + jb * kAttnKeys, &k_full[st]);
+                                kvh * D + kb * 64, b * a.kv_rows + jb * kAttnKeys, &k_full[st]);
             }
         } else if (lane == 1) {
             for (int j = 0; j < n; ++j) {  // second sweep only
@@ -1285,6 +1297,9 @@ int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dyn
             const bool gated = epi == MB_EPI_SILU_MUL || epi == MB_EPI_GELU_TANH_MUL;
             if (gated != (nmat == 2) || (nmat == 2 && nseg != 1)) return MB_ERR_INVALID;
             if (epi < MB_EPI_NONE || epi > MB_EPI_GELU_TANH_MUL) return MB_ERR_INVALID;
+            if (P.i[MB_GV_I_OUT_TOKENS] < 0 ||
+                (P.i[MB_GV_I_OUT_TOKENS] > 0 && P.i[MB_GV_I_OUT_CAPACITY] < P.i[MB_GV_I_OUT_TOKENS]))
+                return MB_ERR_INVALID;
             if (!slot_ok(P.slot[MB_GV_S_X], true, false)) return MB_ERR_INVALID;
             for (int s = 0; s < nseg; ++s) {
                 if (P.i[MB_GV_I_N0 + s] < 1) return MB_ERR_INVALID;
@@ -1306,6 +1321,9 @@ int prefill_validate(const mb_phase& P, unsigned int n_slots, unsigned int n_dyn
                 return MB_ERR_INVALID;
             for (int s = 0; s < 4; ++s)
                 if (!slot_ok(P.slot[s], true, s == MB_RP_S_POS)) return MB_ERR_INVALID;
+            if (!slot_ok(P.slot[MB_RP_S_LEN], false, false)) return MB_ERR_INVALID;
+            if (P.i[MB_RP_I_K_TOKENS] > 0 && P.i[MB_RP_I_K_CAPACITY] < P.i[MB_RP_I_K_TOKENS])
+                return MB_ERR_INVALID;
             return MB_OK;
         }
         case MB_BODY_ATTN_PREFILL: {
@@ -1415,6 +1433,8 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
             a.nseg = P.i[MB_GV_I_NSEG];
             a.pair = P.i[MB_GV_I_NMAT] == 2 ? 1 : 0;
             a.epilogue = P.i[MB_GV_I_EPILOGUE];
+            a.out_tokens = P.i[MB_GV_I_OUT_TOKENS];
+            a.out_capacity = P.i[MB_GV_I_OUT_CAPACITY];
             a.tiles_n = g.tiles_n;
             for (int s = 0; s < 3; ++s) {
                 a.n[s] = s < a.nseg ? P.i[MB_GV_I_N0 + s] : 0;
@@ -1449,6 +1469,7 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
             a.kv_heads = P.i[MB_AP_I_KV_HEADS];
             a.causal = P.i[MB_AP_I_CAUSAL];
             a.mask_batch = P.i[MB_AP_I_MASK_BATCH];
+            a.kv_rows = P.i[MB_AP_I_KV_CAPACITY] > 0 ? P.i[MB_AP_I_KV_CAPACITY] : a.tokens;
             a.scale = P.f[MB_AP_F_SCALE];
             L.vt = reinterpret_cast<unsigned short*>(addr(P.slot[MB_AP_S_VT]));
             if (L.vt != nullptr) {
@@ -1456,7 +1477,8 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
                 const int rows = a.batch * a.tokens;
                 L.padded_tokens = (a.tokens + kAttnKeys - 1) / kAttnKeys * kAttnKeys;
                 if (!make_map(&L.attn_maps.q, addr(P.slot[MB_AP_S_Q]), rows, a.heads * D, kTcRows) ||
-                    !make_map(&L.attn_maps.k, addr(P.slot[MB_AP_S_K]), rows, a.kv_heads * D, kAttnKeys) ||
+                    !make_map(&L.attn_maps.k, addr(P.slot[MB_AP_S_K]), a.batch * a.kv_rows, a.kv_heads * D,
+                              kAttnKeys) ||
                     !make_map(&L.attn_maps.vt, addr(P.slot[MB_AP_S_VT]), a.batch * a.kv_heads * D,
                               L.padded_tokens, D))
                     return MB_ERR_CUDA;
@@ -1511,7 +1533,6 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
             }
             case MB_BODY_ROPE_ROWS: {
                 const long long work = static_cast<long long>(P.i[MB_RP_I_ROWS]) *
-                                       (P.i[MB_RP_I_HEADS] + P.i[MB_RP_I_KV_HEADS]) *
                                        (P.i[MB_RP_I_HEAD_DIM] / 2);
                 long long blocks = (work + 255) / 256;
                 if (blocks > 4 * 148 * 8) blocks = 4 * 148 * 8;
@@ -1521,7 +1542,9 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                     reinterpret_cast<const long long*>(addr(P.slot[MB_RP_S_POS])),
                     reinterpret_cast<const void*>(addr(P.slot[MB_RP_S_INVFREQ])), P.i[MB_RP_I_ROWS],
                     P.i[MB_RP_I_HEADS], P.i[MB_RP_I_KV_HEADS], P.i[MB_RP_I_HEAD_DIM],
-                    P.i[MB_RP_I_INVFREQ_BF16], P.f[MB_RP_F_ROPE_SCALE], P.f[MB_RP_F_Q_SCALE]);
+                    P.i[MB_RP_I_INVFREQ_BF16], P.f[MB_RP_F_ROPE_SCALE], P.f[MB_RP_F_Q_SCALE],
+                    P.i[MB_RP_I_K_TOKENS], P.i[MB_RP_I_K_CAPACITY],
+                    reinterpret_cast<int*>(addr(P.slot[MB_RP_S_LEN])), P.i[MB_RP_I_LEN_VALUE]);
                 break;
             }
             case MB_BODY_ATTN_PREFILL: {
@@ -1530,7 +1553,8 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                     const AttnArgs& a = L.attn;
                     const dim3 tgrid(L.padded_tokens / 64, D / 64, a.batch * a.kv_heads);
                     transpose_values_kernel<<<tgrid, 256, 0, stream>>>(a.v, L.vt, a.tokens,
-                                                                       L.padded_tokens, a.kv_heads, D);
+                                                                       L.padded_tokens, a.kv_heads, D,
+                                                                       a.kv_rows);
                     const dim3 grid((a.tokens + kTcRows - 1) / kTcRows, a.heads, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
                     const int ph = static_cast<int>(i);

@@ -29,6 +29,7 @@ from typing import Any
 import torch
 from transformers.cache_utils import Cache, CacheLayerMixin
 
+from . import ops as _ops  # noqa: F401  (registers torch.ops.megabake.*)
 from .ops import attention as _attention_op
 
 ATTENTION_IMPLEMENTATION = "megabake"
@@ -278,3 +279,31 @@ class PrefillLogits(torch.nn.Module):
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
         return self.model(input_ids=input_ids, use_cache=False).logits
+
+
+class StatefulPrefill(StatefulDecoder):
+    """``forward(input_ids[B, T], *state) -> logits[B, T, V]``: a full causal prefill at
+    positions 0..T-1 that also fills the explicit decode state (rows 0..T-1 of every layer's
+    caches, valid lengths = T) through ``megabake::prefill_kv_attention``.  Same state tensors and
+    order as ``StatefulDecoder`` / ``DecodeStep``: compile this with ``mode="prefill"``, the decode
+    wrapper with ``mode="decode"``, and generation is prefill once, then one decode call per
+    token."""
+
+    def _attend(self, module, normalized, rotary, key_cache, value_cache, valid_length):
+        batch, tokens, _ = normalized.shape
+        dim = self.head_dim
+        query = module.q_proj(normalized).view(batch, tokens, -1, dim)
+        key = module.k_proj(normalized).view(batch, tokens, -1, dim)
+        value = module.v_proj(normalized).view(batch, tokens, -1, dim)
+        rotate = sys.modules[type(module).__module__].apply_rotary_pos_emb
+        query, key = rotate(query, key, rotary[0], rotary[1], unsqueeze_dim=2)
+        mixed = torch.ops.megabake.prefill_kv_attention(
+            query, key, value, key_cache, value_cache, valid_length, float(module.scaling)
+        )
+        mixed = mixed.view(batch, -1, tokens, dim).transpose(1, 2)
+        return module.o_proj(mixed.reshape(batch, tokens, -1))
+
+    def forward(self, input_ids: torch.Tensor, *state: torch.Tensor):
+        batch, tokens = input_ids.shape
+        positions = torch.arange(tokens, device=input_ids.device)[None].expand(batch, -1)
+        return super().forward(input_ids, positions, *state)

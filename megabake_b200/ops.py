@@ -25,7 +25,8 @@ from __future__ import annotations
 
 import torch
 
-__all__ = ["kv_attention", "attention", "KV_ATTENTION_OP", "ATTENTION_OP"]
+__all__ = ["kv_attention", "attention", "prefill_kv_attention", "KV_ATTENTION_OP", "ATTENTION_OP",
+           "PREFILL_KV_ATTENTION_OP"]
 
 
 def _repeat_kv(tensor: torch.Tensor, groups: int) -> torch.Tensor:
@@ -105,5 +106,53 @@ def _(query, key, value, mask, scale):
     return query.new_empty((batch * heads, length, dim))
 
 
+@torch.library.custom_op(
+    "megabake::prefill_kv_attention",
+    mutates_args=("key_cache", "value_cache", "valid_length"),
+)
+def prefill_kv_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    valid_length: torch.Tensor,
+    scale: float,
+) -> torch.Tensor:
+    """Causal prefill attention that also hands the prompt's keys and values to the decode
+    state: ``key``/``value`` (``[batch, tokens, kv_heads, dim]``) are written to rows
+    ``0 .. tokens - 1`` of the caches (``[batch, capacity, kv_heads, dim]``) and
+    ``valid_length`` (int32 ``[1]``) is set to ``tokens``, so that ``megabake::kv_attention``
+    can continue from there.  The attention itself is ``megabake::attention`` with the causal
+    mask (same rounding points).  The reference has no such operator: its prefill cannot seed
+    its decode state (``examples/single_gpu_generate.py:3-4``)."""
+    batch, tokens, heads, dim = query.shape
+    capacity = key_cache.shape[1]
+    if tokens > capacity:
+        raise RuntimeError(f"prompt of {tokens} tokens exceeds the KV capacity {capacity}")
+    key_cache[:, :tokens].copy_(key)
+    value_cache[:, :tokens].copy_(value)
+    valid_length.fill_(tokens)
+    allowed = torch.tril(torch.ones(tokens, tokens, dtype=torch.bool, device=query.device))
+    mask = torch.where(allowed, torch.zeros((), dtype=query.dtype, device=query.device),
+                       torch.full((), torch.finfo(query.dtype).min, dtype=query.dtype,
+                                  device=query.device))[None, None]
+    q = query.transpose(1, 2)
+    groups = heads // key.shape[2]
+    k = _repeat_kv(key.transpose(1, 2), groups)
+    v = _repeat_kv(value.transpose(1, 2), groups)
+    scores = torch.matmul(q, k.transpose(2, 3)) * scale + mask
+    weights = torch.softmax(scores, dim=-1, dtype=torch.float32).to(q.dtype)
+    mixed = torch.matmul(weights, v)
+    return mixed.reshape(-1, mixed.shape[2], mixed.shape[3])
+
+
+@prefill_kv_attention.register_fake
+def _(query, key, value, key_cache, value_cache, valid_length, scale):
+    batch, length, heads, dim = query.shape
+    return query.new_empty((batch * heads, length, dim))
+
+
 KV_ATTENTION_OP = torch.ops.megabake.kv_attention.default
+PREFILL_KV_ATTENTION_OP = torch.ops.megabake.prefill_kv_attention.default
 ATTENTION_OP = torch.ops.megabake.attention.default

@@ -408,6 +408,11 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
     glu = slots.buffer(R * p.intermediate * 2, "gated")
     padded = (T + 63) // 64 * 64
     v_t = slots.buffer(B * kv_dim * padded * 2, "values_transposed")
+    # state handoff: keys and values go straight into the caller's KV caches (rows 0..T-1 of
+    # every batch row) and the valid lengths are set to T
+    handoff = all(layer.key_cache >= 0 for layer in p.layers)
+    if handoff and p.capacity < T:
+        fail("state-capacity", f"prompt of {T} tokens exceeds the KV capacity {p.capacity}")
     constants = {}
     mask_slot = -1
     if not p.causal:
@@ -450,21 +455,29 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
     for index, layer in enumerate(p.layers):
         tag = f"layers.{index}."
         norm(slots.arg(layer.input_norm, tag + "input_layernorm.weight"))
+        k_out = slots.arg(layer.key_cache, tag + "key_cache") if handoff else k_buf
+        v_out = slots.arg(layer.value_cache, tag + "value_cache") if handoff else v_buf
         gemm(k=H, x_slot=normed, segments=[
             (q_dim, slots.arg(layer.q_weight, tag + "q_proj.weight"),
              slots.arg(layer.q_bias, tag + "q_proj.bias"), q_buf),
             (kv_dim, slots.arg(layer.k_weight, tag + "k_proj.weight"),
-             slots.arg(layer.k_bias, tag + "k_proj.bias"), k_buf),
+             slots.arg(layer.k_bias, tag + "k_proj.bias"), k_out),
             (kv_dim, slots.arg(layer.v_weight, tag + "v_proj.weight"),
-             slots.arg(layer.v_bias, tag + "v_proj.bias"), v_buf),
+             slots.arg(layer.v_bias, tag + "v_proj.bias"), v_out),
         ])
+        if handoff:
+            phases[-1].i[rt.GV_I_OUT_TOKENS], phases[-1].i[rt.GV_I_OUT_CAPACITY] = T, p.capacity
         rope = rt.Phase.blank(rt.BODY_ROPE_ROWS, 0)
         rope.i[rt.RP_I_ROWS], rope.i[rt.RP_I_HEADS], rope.i[rt.RP_I_KV_HEADS] = R, p.heads, p.kv_heads
         rope.i[rt.RP_I_HEAD_DIM] = D
         rope.i[rt.RP_I_INVFREQ_BF16] = 1 if p.inv_freq_dtype == "bf16" else 0
         rope.f[rt.RP_F_ROPE_SCALE] = p.rope_scale
         rope.f[rt.RP_F_Q_SCALE] = float(p.q_scale or 0.0)
-        rope.slot[rt.RP_S_Q], rope.slot[rt.RP_S_K] = q_buf, k_buf
+        rope.slot[rt.RP_S_Q], rope.slot[rt.RP_S_K] = q_buf, k_out
+        if handoff:
+            rope.i[rt.RP_I_K_TOKENS], rope.i[rt.RP_I_K_CAPACITY] = T, p.capacity
+            rope.i[rt.RP_I_LEN_VALUE] = T
+            rope.slot[rt.RP_S_LEN] = slots.arg(layer.valid_length, tag + "valid_length")
         rope.slot[rt.RP_S_POS], rope.slot[rt.RP_S_INVFREQ] = DYN_POSITION_IDS, inv_freq
         phases.append(rope)
         attention = rt.Phase.blank(rt.BODY_ATTN_PREFILL, 0)
@@ -474,7 +487,8 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
         attention.i[rt.AP_I_CAUSAL] = 1 if p.causal else 0
         attention.i[rt.AP_I_MASK_BATCH] = 1 if mask is None else int(mask.shape[0])
         attention.f[rt.AP_F_SCALE] = p.softmax_scale
-        attention.slot[rt.AP_S_Q], attention.slot[rt.AP_S_K], attention.slot[rt.AP_S_V] = q_buf, k_buf, v_buf
+        attention.slot[rt.AP_S_Q], attention.slot[rt.AP_S_K], attention.slot[rt.AP_S_V] = q_buf, k_out, v_out
+        attention.i[rt.AP_I_KV_CAPACITY] = p.capacity if handoff else 0
         attention.slot[rt.AP_S_OUT], attention.slot[rt.AP_S_MASK] = attn, mask_slot
         attention.slot[rt.AP_S_VT] = v_t
         phases.append(attention)

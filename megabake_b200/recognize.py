@@ -440,6 +440,32 @@ class _Matcher:
         return {"source": query, "key": key, "value": value, "mask": mask, "scale": float(scale),
                 "key_cache": -1, "value_cache": -1, "valid_length": -1, "node": node}
 
+    def prefill_state_attention(self, node):
+        """``megabake::prefill_kv_attention`` (causal prefill that also fills the decode state)
+        whose result ``node`` is -> dict or None."""
+        node = strip(node)
+        call = node.args[0] if _is(node, operator.getitem) and node.args[1] == 0 else None
+        target = torch.ops.megabake.prefill_kv_attention.default
+        if _is(node, target):
+            names = ("query", "key", "value", "key_cache", "value_cache", "valid_length", "scale")
+            operands = dict(zip(names, node.args))
+            state = [operands[n] for n in names[3:6]]
+        elif (isinstance(call, torch.fx.Node) and call.op == "call_function"
+              and "functionaliz" in type(call.target).__name__.lower() and call.args
+              and call.args[0] is target):
+            operands = call.kwargs
+            bases = operands["_all_bases"]
+            state = [bases[operands[f"_{n}_base_index"]]
+                     for n in ("key_cache", "value_cache", "valid_length")]
+        else:
+            return None
+        indices = [_placeholder_index(n, self.order) for n in state]
+        if any(i is None for i in indices):
+            self.refuse("KV state tensors must be graph inputs", node)
+        return {"source": operands["query"], "key": operands["key"], "value": operands["value"],
+                "mask": None, "causal": True, "scale": float(operands["scale"]), "node": node,
+                "key_cache": indices[0], "value_cache": indices[1], "valid_length": indices[2]}
+
     def constant(self, node, module: torch.fx.GraphModule):
         """Evaluate a sub-graph that depends on no graph input (the mask of a prefill)."""
         memo: dict = {}
@@ -492,8 +518,12 @@ class _Matcher:
 def recognize_decoder(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
     """Match the whole graph; raises ``CompilerError`` if it is not a covered decoder."""
     global _HEAD_TOKEN_SWAPS_ARE_LAYOUT
+    prefill_ops = (torch.ops.megabake.attention.default,
+                   torch.ops.megabake.prefill_kv_attention.default)
     _HEAD_TOKEN_SWAPS_ARE_LAYOUT = any(
-        _is(node, torch.ops.megabake.attention.default) for node in graph_module.graph.nodes)
+        _is(node, *prefill_ops) or (node.op == "call_function" and node.args
+                                    and node.args[0] in prefill_ops)
+        for node in graph_module.graph.nodes)
     try:
         return _recognize(graph_module, mode)
     finally:
@@ -555,7 +585,7 @@ def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
             o_proj = m.linear(branch)
             call = m.kv_attention(o_proj.x) if o_proj is not None else None
             if call is None and o_proj is not None:
-                call = m.prefill_attention(o_proj.x)
+                call = m.prefill_attention(o_proj.x) or m.prefill_state_attention(o_proj.x)
             if call is not None:
                 found = (strip(skip), o_proj, call)
                 break
@@ -662,7 +692,10 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
                  first["node"])
     kv_heads = kv_shape[2]
     for call in calls:
-        same_mask = call["mask"] is first["mask"] or strip(call["mask"]) is strip(first["mask"])
+        same_mask = call["mask"] is first["mask"] or (
+            call["mask"] is not None and first["mask"] is not None
+            and strip(call["mask"]) is strip(first["mask"]))
+        same_mask = same_mask and bool(call.get("causal")) == bool(first.get("causal"))
         if (_shape(call["source"]) != (batch, tokens, heads, head_dim)
                 or _shape(call["key"]) != kv_shape or _shape(call["value"]) != kv_shape
                 or call["scale"] != first["scale"] or not same_mask):
@@ -672,7 +705,16 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
         m.refuse(f"prefill takes input_ids of shape [{batch}, {tokens}]")
     # recognition runs inside the compiler's tracing modes (fake tensors): the mask constant
     # has to be computed and inspected for real
-    if first["mask"] is not None:
+    capacity = 0
+    if first.get("causal"):  # the stateful prefill operator is causal by definition
+        causal, mask_tensor = True, None
+        cache = _val(m.placeholders[first["key_cache"]])
+        if tuple(cache.shape[0:1]) != (batch,) or tuple(cache.shape[2:]) != (kv_heads, head_dim):
+            m.refuse("KV caches must be [batch, capacity, kv_heads, head_dim]", first["node"])
+        capacity = int(cache.shape[1])
+        if capacity < tokens:
+            m.refuse(f"prompt of {tokens} tokens exceeds the KV capacity {capacity}", first["node"])
+    elif first["mask"] is not None:
         mask = m.constant(first["mask"], graph_module)
         with _disable_current_modes():
             causal, mask_tensor = _classify_mask(m, mask, batch, tokens, first["node"])
@@ -683,8 +725,8 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
     return DecoderProgram(
         mode="prefill", batch=batch, tokens=tokens, hidden=hidden_size, heads=heads,
         kv_heads=kv_heads, head_dim=head_dim,
-        intermediate=_shape(m.placeholders[layers[0].gate_weight])[0], vocab=vocab, capacity=0,
-        norm=norm_kind, eps=eps, activation=activation, embed_scale=None, rope_scale=rope_scale,
+        intermediate=_shape(m.placeholders[layers[0].gate_weight])[0], vocab=vocab,
+        capacity=capacity, norm=norm_kind, eps=eps, activation=activation, embed_scale=None, rope_scale=rope_scale,
         q_scale=q_scale, softmax_scale=first["scale"],
         inv_freq_dtype="bf16" if _val(m.placeholders[inv_freq]).dtype == torch.bfloat16 else "f32",
         input_ids=ids, position_ids=position, embed_weight=embed_weight, inv_freq=inv_freq,

@@ -45,7 +45,7 @@ AT_F_SCALE, AT_F_ROPE_SCALE, AT_F_Q_SCALE = 0, 1, 2
  AT_S_PARTIAL, AT_S_COUNTER) = range(11)
 
 # prefill bodies
-GV_I_SPLIT_K, GV_I_TILE_N = 16, 17
+GV_I_SPLIT_K, GV_I_TILE_N, GV_I_OUT_TOKENS, GV_I_OUT_CAPACITY = 16, 17, 18, 19
 EM_I_ROWS, EM_I_K, EM_I_VOCAB = 0, 1, 2
 EM_F_SCALE = 0
 EM_S_TABLE, EM_S_IDS, EM_S_OUT = 0, 1, 2
@@ -53,10 +53,11 @@ RN_I_ROWS, RN_I_K, RN_I_KIND = 0, 1, 2
 RN_F_EPS = 0
 RN_S_X, RN_S_W, RN_S_OUT = 0, 1, 2
 RP_I_ROWS, RP_I_HEADS, RP_I_KV_HEADS, RP_I_HEAD_DIM, RP_I_INVFREQ_BF16 = 0, 1, 2, 3, 4
+RP_I_K_TOKENS, RP_I_K_CAPACITY, RP_I_LEN_VALUE = 5, 6, 7
 RP_F_ROPE_SCALE, RP_F_Q_SCALE = 0, 1
-RP_S_Q, RP_S_K, RP_S_POS, RP_S_INVFREQ = 0, 1, 2, 3
+RP_S_Q, RP_S_K, RP_S_POS, RP_S_INVFREQ, RP_S_LEN = 0, 1, 2, 3, 4
 AP_I_BATCH, AP_I_TOKENS, AP_I_HEADS, AP_I_KV_HEADS, AP_I_HEAD_DIM = 0, 1, 2, 3, 4
-AP_I_CAUSAL, AP_I_MASK_BATCH = 5, 6
+AP_I_CAUSAL, AP_I_MASK_BATCH, AP_I_KV_CAPACITY = 5, 6, 7
 AP_F_SCALE = 0
 AP_S_Q, AP_S_K, AP_S_V, AP_S_OUT, AP_S_MASK, AP_S_VT = 0, 1, 2, 3, 4, 5
 
