@@ -10,6 +10,7 @@ parts of it this backend keeps):
 ``DecodeStep``, ``StatefulDecoder`` explicit-state decode wrappers for Hugging Face models
 ``PrefillLogits``                   ids -> logits prefill wrapper over ``megabake::attention``
 ``StatefulPrefill``                 prefill that also fills the explicit decode state
+``GreedyGenerator``                 compiled prefill + decode loop over one KV state
 ``register_transformers_attention`` the ``"megabake"`` attention implementation for HF models
 ``CompilerError``                   every refusal, with a staged diagnostic
 """
@@ -18,8 +19,8 @@ from .diagnostics import CompilerDiagnostic, CompilerError
 from .ops import attention, kv_attention
 
 __all__ = [
-    "CompilerDiagnostic", "CompilerError", "DecodeStep", "PrefillLogits", "StatefulDecoder",
-    "StatefulPrefill", "attention",
+    "CompilerDiagnostic", "CompilerError", "DecodeStep", "GreedyGenerator", "PrefillLogits",
+    "StatefulDecoder", "StatefulPrefill", "attention",
     "graphed", "kv_attention", "make_backend", "register_transformers_attention",
 ]
 
@@ -36,4 +37,7 @@ def __getattr__(name):
                 "register_transformers_attention"):
         from . import hf
         return getattr(hf, name)
+    if name == "GreedyGenerator":
+        from .generate import GreedyGenerator
+        return GreedyGenerator
     raise AttributeError(name)

@@ -141,6 +141,44 @@ def test_prefill_recognition_and_plan(name):
     assert bodies.count(rt.BODY_GEMM_TC) == 4 * spec.layers + 1
 
 
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen2", "tiny-gemma"])
+def test_stateful_prefill_fills_the_decode_state(name):
+    """The handoff operator on CPU: eager and FX forwards equal the oracle's prefill bit for
+    bit, the caches hold the oracle's keys and values, and the graph is recognised and planned
+    with the caches as GEMM outputs."""
+    from megabake_b200 import StatefulPrefill
+    from megabake_b200 import runtime as rt
+    from megabake_b200.planner import plan_prefill
+    from oracle import decoder_oracle as oracle
+    from oracle.adapters import oracle_config, oracle_weights
+
+    spec = models.get_spec(name)
+    weights = models.init_weights(spec, 3)
+    wrapper = StatefulPrefill(models.build_hf_model(spec, 3, weights=weights), 24).eval()
+    ids = torch.randint(0, spec.vocab, (2, 7), generator=torch.Generator().manual_seed(1))
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    reference, kv = oracle.prefill(cfg, ow, ids, return_kv=True)
+    backend = make_backend(mode="prefill", compile_kernel=False)
+    torch._dynamo.reset()
+    compiled = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    for forward in (wrapper, compiled):
+        state = wrapper.make_state(2)
+        with torch.no_grad():
+            logits = forward(ids, *state)
+        assert torch.equal(logits, reference)
+        for index in range(spec.layers):
+            assert torch.equal(state[3 * index][:, :7], kv[index][0])
+            assert torch.equal(state[3 * index + 1][:, :7], kv[index][1])
+            assert int(state[3 * index + 2]) == 7 and not state[3 * index][:, 7:].any()
+    program = recognize_decoder(backend.megabake_last_prepared.graph, "prefill")
+    assert program.mode == "prefill" and program.causal and program.capacity == 24
+    assert all(layer.key_cache >= 0 and layer.valid_length >= 0 for layer in program.layers)
+    layout = plan_prefill(program)
+    qkv = [ph for ph in layout.phases if ph.body == rt.BODY_GEMM_TC and ph.i[rt.GV_I_NSEG] == 3]
+    assert len(qkv) == spec.layers
+    assert all(ph.i[rt.GV_I_OUT_TOKENS] == 7 and ph.i[rt.GV_I_OUT_CAPACITY] == 24 for ph in qkv)
+
+
 def test_unrecognised_graph_is_refused_not_rerouted():
     class NotADecoder(torch.nn.Module):
         def forward(self, x):

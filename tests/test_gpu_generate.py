@@ -73,3 +73,27 @@ def test_prefill_hands_the_state_to_decode(name, batch, prompt):
             token = ref[:, -1].float().argmax(-1, keepdim=True)
     decode_backend.megabake_last_callable.check()
     assert int(state[2].item()) == prompt + steps
+
+
+def test_greedy_generator_picks_what_the_oracle_would():
+    from megabake_b200 import GreedyGenerator
+
+    spec = models.get_spec("tiny-llama")
+    weights = models.init_weights(spec, 1)
+    model = models.build_hf_model(spec, 1, device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    batch, prompt, new = 2, 12, 6
+    ids = torch.randint(0, spec.vocab, (batch, prompt), generator=torch.Generator().manual_seed(1))
+    torch._dynamo.reset()
+    produced = GreedyGenerator(model, batch, prompt, capacity=prompt + new + 2)(ids, new).cpu()
+    assert produced.shape == (batch, new)
+    # replay the produced ids through the oracle: every one must be an acceptable greedy pick of
+    # the oracle's logits at its position
+    everything = torch.cat([ids, produced], dim=1)
+    reference = oracle.prefill(cfg, ow, everything[:, :-1])
+    for step in range(new):
+        at = prompt - 1 + step
+        chosen = torch.full((batch, spec.vocab), -1.0)
+        chosen[torch.arange(batch), produced[:, step]] = 1.0      # "logits" whose argmax is the pick
+        assert greedy_pick_matches(chosen, reference[:, at])[0], step
