@@ -186,6 +186,10 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                                              entry_address(p, E, MB_GV_S_W_PAIR))
                                        : nullptr;
         const size_t row_bytes = static_cast<size_t>(g.K) * 2;
+        // ring position: one division per phase, then counted up (a division per stage costs
+        // more than the rest of the stage's bookkeeping)
+        int stage = static_cast<int>(it % static_cast<unsigned int>(p.stages));
+        unsigned int wraps = it / static_cast<unsigned int>(p.stages);
         for (int blk = 0; blk < g.n_blocks; ++blk) {
             const int block0 = g.r0 + blk * kRowTile;
             const int nrows = min(kRowTile, g.r1 - block0);
@@ -210,8 +214,7 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                 src_row = base + static_cast<size_t>(local) * row_bytes;
             }
             for (int c = 0; c < g.n_chunks; ++c) {
-                const int stage = it % p.stages;
-                const unsigned int parity = ((it / p.stages) & 1u) ^ 1u;
+                const unsigned int parity = (wraps & 1u) ^ 1u;
                 if (!mbar_wait_bounded(&sc->empty[stage], parity, &sc->abort_flag)) {
                     if (lane == 0 && !sc->abort_flag) {
                         record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
@@ -233,6 +236,10 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
                                   &sc->full[stage]);
                 }
                 ++it;
+                if (++stage == p.stages) {
+                    stage = 0;
+                    ++wraps;
+                }
             }
         }
     }
@@ -535,6 +542,9 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
 
     bool dead = false;
     bool staged = false;  // activation rows not yet waited for / normalised
+    // ring position: one division per phase, then counted up
+    int stage = static_cast<int>(it % static_cast<unsigned int>(p.stages));
+    unsigned int wraps = it / static_cast<unsigned int>(p.stages);
     for (int group0 = 0; group0 < g.n_blocks; group0 += NB) {
         const int nb = min(NB, g.n_blocks - group0);
         // The block this warp finalises, this lane's two output cells in it (token gid, rows
@@ -569,15 +579,19 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                     for (int q = 0; q < 4; ++q) acc[m][u][q] = 0.f;
 
             for (int c = 0; c < g.n_chunks; ++c) {
-                const int stage = it % p.stages;
-                const unsigned int parity = (it / p.stages) & 1u;
+                const int this_stage = stage;
+                const unsigned int parity = wraps & 1u;
                 ++it;
+                if (++stage == p.stages) {
+                    stage = 0;
+                    ++wraps;
+                }
                 if (group0 == 0 && b == 0 && c == 0) trace_stamp(p, ph, 6, tid);
                 // A wait that runs out must not make this warp leave: the others would hang
                 // at the next CTA barrier.  It records the fault, and every warp then falls
                 // through the remaining loops without waiting or computing.
-                if (dead || sc->abort_flag ||
-                    !mbar_wait_bounded(&sc->full[stage], parity, &sc->abort_flag)) {
+                // (the bounded wait itself watches the CTA's abort flag while it spins)
+                if (dead || !mbar_wait_bounded(&sc->full[this_stage], parity, &sc->abort_flag)) {
                     if (!dead && !sc->abort_flag) {
                         record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
                         sc->abort_flag = 1;
@@ -587,7 +601,7 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                 }
                 if (group0 == 0 && b == 0 && c == 0) trace_stamp(p, ph, 4, tid);
                 const int kc = min(g.k_chunk, g.K - c * g.k_chunk);
-                const char* wrow = ring + static_cast<size_t>(stage) * p.stage_bytes +
+                const char* wrow = ring + static_cast<size_t>(this_stage) * p.stage_bytes +
                                    static_cast<size_t>(gid) * g.pitch + 16 * tq;
                 const __nv_bfloat16* xk = xrow + c * g.k_chunk;
                 const int groups = kc >> 5;  // 32 reduction elements per group
@@ -612,7 +626,7 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sc->empty[stage]);
+                if (lane == 0) mbar_arrive(&sc->empty[this_stage]);
             }
             float* cell = red + (static_cast<size_t>(b * kConsumerWarps + warp) * 32 + lane) * PV;
 #pragma unroll
