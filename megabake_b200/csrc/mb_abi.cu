@@ -79,7 +79,9 @@ long long attention_scratch_bytes(int head_dim, int group, int merge_slots) {
     const long long cs = 4LL * head_dim;
     const long long stats = 4LL * (2 * 8 * 8 + 8 * 64 + 16);
     const long long states = 4LL * (head_dim + 2) * group * (merge_slots + 2);
-    return qs + new_rows + cs + stats + states;
+    // per-warp K/V tile slots of the split-key loop (64-wide heads): 8 warps x 2 slots x 16 keys
+    const long long staging = head_dim == 64 ? 8LL * 2 * 16 * ((head_dim * 2 + 64) + (head_dim * 2 + 16)) : 0;
+    return qs + new_rows + cs + stats + states + staging;
 }
 
 int check_slot(const mb_plan_desc* d, int s, bool required) {

@@ -269,6 +269,13 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem)
                  "l"(src_gmem)
                  : "memory");
 }
+// 16 bytes, or 16 zero bytes when `valid` is false (the source is not read then).
+__device__ __forceinline__ void cp_async16_or_zero(void* dst_smem, const void* src_gmem,
+                                                   bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(valid ? 16 : 0)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
@@ -762,6 +769,14 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     float* fold = wstat + 2 * kConsumerWarps * 8;  // [8][64] chunk weights + denominators
     float* merge = fold + kFoldFloats;
     float* running = merge + static_cast<size_t>(merge_slots) * group * SW;
+    // Split mode with 64-wide heads: every warp streams its 16-key K and V tiles through two
+    // private shared-memory slots with cp.async, one tile ahead of the one it works on, so that
+    // the two dependent global round trips per block leave the critical path.
+    constexpr bool kStaged = D == 64 && !EXACT;
+    constexpr int kKPitch = D * 2 + 64, kVPitch = D * 2 + 16;  // bank-conflict-free fragment reads
+    constexpr int kTileBytes = 16 * (kKPitch + kVPitch);
+    char* staging = reinterpret_cast<char*>(running + 2 * static_cast<size_t>(group) * SW) +
+                    static_cast<size_t>(warp) * 2 * kTileBytes;
     const size_t key_stride = static_cast<size_t>(Hkv) * D;  // elements between keys
 
     for (int item = cta; item < items; item += ctas) {
@@ -807,6 +822,43 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 for (int x = 0; x < DB; ++x)
                     vt[x][q] = ok ? *reinterpret_cast<const uint4*>(vp + 64 * x)
                                   : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        // staged variant: this warp's tile `blk` into slot `slot` (rows past the valid length
+        // become zeros: their probabilities are zero, but 0 * stale bits may be NaN)
+        auto issue_tile = [&](int blk, int slot) {
+            char* kdst = staging + slot * kTileBytes;
+            char* vdst = kdst + 16 * kKPitch;
+            constexpr int kChunks = D / 8;  // 16-byte pieces per row
+#pragma unroll
+            for (int t = 0; t < 16 * kChunks / 32; ++t) {
+                const int c = lane + 32 * t, row = c / kChunks, piece = c - row * kChunks;
+                const int key = (blk << 4) + row;
+                const bool ok = key < L;
+                const size_t at = static_cast<size_t>(ok ? key : 0) * key_stride + piece * 8;
+                cp_async16_or_zero(kdst + row * kKPitch + piece * 16, kc0 + at, ok);
+                cp_async16_or_zero(vdst + row * kVPitch + piece * 16, vc0 + at, ok);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        auto staged_keys = [&](int slot, uint4 (&kt)[2][DC]) {
+            const char* kbase = staging + slot * kTileBytes;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int i = 0; i < DC; ++i)
+                    kt[j][i] = *reinterpret_cast<const uint4*>(kbase + (8 * j + gid) * kKPitch +
+                                                               (32 * i + 8 * tq) * 2);
+        };
+        auto staged_values = [&](int slot, uint4 (&vt)[DB][4]) {
+            const char* vbase = staging + slot * kTileBytes + 16 * kKPitch;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int row = 2 * tq + (q & 1) + ((q >> 1) << 3);
+#pragma unroll
+                for (int x = 0; x < DB; ++x)
+                    vt[x][q] = *reinterpret_cast<const uint4*>(vbase + row * kVPitch +
+                                                               (64 * x + 8 * gid) * 2);
             }
         };
         auto patch_new_row = [&](int blk, uint4 (&kt)[2][DC], uint4 (&vt)[DB][4]) {
@@ -873,7 +925,17 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             if (kEarlyKeys) load_keys(first, kt);
             if (kEarlyValues) load_values(first, vt);
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (kStaged) {
+            // the first tile flies during the barrier and the rotation below; an empty group
+            // keeps the group count the same for warps without a tile
+            if (first < blk1)
+                issue_tile(first, 0);
+            else
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // the prologue rows only
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         named_barrier(kBarConsumers, kConsumerThreads);
         // rotate in place: thread e owns the element pair (i, i + D/2) of row e / (D/2); rows
         // 0..group-1 are query heads, row `group` is the new key
@@ -1015,11 +1077,26 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             // online softmax, one 16-key block per iteration, the next block requested ahead
             uint4 kt_next[2][DC];
             uint4 vt_next[DB][4];
+            int slot = 0;
             for (int blk = first; blk < blk1; blk += kConsumerWarps) {
                 const int kb = blk << 4;
                 const int following = blk + kConsumerWarps;
-                if (!kEarlyKeys) load_keys(blk, kt);
-                if (!kEarlyValues) load_values(blk, vt);
+                if (kStaged) {
+                    if (following < blk1) {
+                        issue_tile(following, slot ^ 1);
+                        asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    } else {
+                        asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    }
+                    __syncwarp();  // every lane's pieces of the current tile have landed
+                    staged_keys(slot, kt);
+                    staged_values(slot, vt);
+                    __syncwarp();  // the slot may be refilled from the next iteration on
+                    slot ^= 1;
+                } else {
+                    if (!kEarlyKeys) load_keys(blk, kt);
+                    if (!kEarlyValues) load_values(blk, vt);
+                }
                 if (following < blk1) {
                     if (kEarlyKeys) load_keys(following, kt_next);
                     if (kEarlyValues) load_values(following, vt_next);
@@ -1501,7 +1578,8 @@ std::mutex g_static_mutex;
 long long static_attention_smem(int head_dim, int group, int merge_slots) {
     return mb::decode::kCtlBytes + 8LL * (head_dim + 32) * 2 + 2LL * head_dim * 2 + 4LL * head_dim +
            4LL * (2 * 8 * 8 + mb::decode::kFoldFloats) +
-           4LL * (head_dim + 2) * group * (merge_slots + 2);
+           4LL * (head_dim + 2) * group * (merge_slots + 2) +
+           (head_dim == 64 ? 8LL * 2 * 16 * ((head_dim * 2 + 64) + (head_dim * 2 + 16)) : 0);
 }
 }  // namespace
 
@@ -1533,7 +1611,7 @@ extern "C" int mb_attention_decode_static(const mb_attention_args* a, void* stre
             cudaDeviceProp prop;
             if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return MB_ERR_CUDA;
             if (prop.major != 10) return MB_ERR_UNSUPPORTED;
-            dev.max_smem = 100 * 1024;
+            dev.max_smem = 160 * 1024;
             if (cudaFuncSetAttribute(attention_static_kernel,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      dev.max_smem) != cudaSuccess)
@@ -1548,7 +1626,9 @@ extern "C" int mb_attention_decode_static(const mb_attention_args* a, void* stre
     const int pairs = a->batch * a->kv_heads;
     int merge_slots = 8;
     while (merge_slots > 1 &&
-           static_attention_smem(a->head_dim, group, merge_slots) - kCtlBytes > 48 * 1024)
+           static_attention_smem(a->head_dim, group, merge_slots) - kCtlBytes -
+                   (a->head_dim == 64 ? 8 * 2 * 16 * ((64 * 2 + 64) + (64 * 2 + 16)) : 0) >
+               48 * 1024)
         merge_slots /= 2;
     if (static_attention_smem(a->head_dim, group, merge_slots) > dev.max_smem) return MB_ERR_RESOURCE;
     // What fits the fixed array: arrival counters for every (row, kv head) and at least one

@@ -145,11 +145,33 @@ def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, 
     return ROW_TILE, min(k_chunk, k)
 
 
-def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int) -> int:
-    """Shared-memory scratch of the decode attention body (mirrors the native layout)."""
+def attention_state_bytes(head_dim: int, group: int, merge_slots: int) -> int:
+    """Query rows, new K/V rows, tables, statistics and head states of the decode attention
+    body (mirrors the native layout)."""
     stats = 4 * (2 * 8 * 8 + 8 * 64 + 16)
     return (16 * (head_dim + 32) + 4 * head_dim + 4 * head_dim + stats
             + 4 * (head_dim + 2) * group * (merge_slots + 2))
+
+
+def attention_staging_bytes(head_dim: int) -> int:
+    """Per-warp K/V tile slots of the split-key loop (64-wide heads only): 8 warps x 2 slots x
+    16 keys x (a K row padded by 64 B + a V row padded by 16 B)."""
+    if head_dim != 64:
+        return 0
+    return CONSUMER_WARPS * 2 * 16 * ((head_dim * 2 + 64) + (head_dim * 2 + 16))
+
+
+def attention_merge_slots(head_dim: int, group: int, wanted: int = CONSUMER_WARPS) -> int:
+    """Per-warp states merged at once: as many as keep the state area within 48 KB."""
+    slots = wanted
+    while slots > 1 and attention_state_bytes(head_dim, group, slots) > 48 * 1024:
+        slots //= 2
+    return slots
+
+
+def attention_scratch_bytes(head_dim: int, group: int, merge_slots: int) -> int:
+    """Shared-memory scratch of the decode attention body."""
+    return attention_state_bytes(head_dim, group, merge_slots) + attention_staging_bytes(head_dim)
 
 
 def exact_softmax_keys(capacity: int, limit: int = EXACT_SOFTMAX_KEYS) -> int:
@@ -213,8 +235,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
 
     merge_slots = options.merge_slots or CONSUMER_WARPS
     exact_keys = exact_softmax_keys(p.capacity, options.exact_keys)
-    while merge_slots > 1 and attention_scratch_bytes(D, p.group, merge_slots) > 48 * 1024:
-        merge_slots //= 2
+    merge_slots = attention_merge_slots(D, p.group, merge_slots)
     activation = attention_scratch_bytes(D, p.group, merge_slots)
 
     phases: list[rt.Phase] = []

@@ -199,9 +199,7 @@ def test_attention_decode(batch, heads, kv_heads, dim, cached, exact):
     ph.i[rt.AT_I_INVFREQ_BF16] = 1
     ph.i[rt.AT_I_MAX_CHUNKS] = max_chunks
     exact_keys = pl.exact_softmax_keys(capacity) if exact else 0
-    merge_slots = 8
-    while merge_slots > 1 and pl.attention_scratch_bytes(dim, group, merge_slots) > 48 * 1024:
-        merge_slots //= 2
+    merge_slots = pl.attention_merge_slots(dim, group)
     ph.i[rt.AT_I_MERGE_SLOTS] = merge_slots
     ph.i[rt.AT_I_EXACT_KEYS] = exact_keys
     ph.f[rt.AT_F_SCALE] = dim ** -0.5

@@ -54,9 +54,7 @@ def _plan_step(tensors, batch, heads, kv_heads, dim, capacity):
     counters = torch.zeros(max(4, batch * kv_heads), dtype=torch.int32, device="cuda")
     runner = PhaseRunner()
     ph = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BARRIER | rt.FLAG_BUMP_LENGTH)
-    merge_slots = 8
-    while merge_slots > 1 and pl.attention_scratch_bytes(dim, group, merge_slots) > 48 * 1024:
-        merge_slots //= 2
+    merge_slots = pl.attention_merge_slots(dim, group)
     for index, value in ((rt.AT_I_BATCH, batch), (rt.AT_I_HEADS, heads),
                          (rt.AT_I_KV_HEADS, kv_heads), (rt.AT_I_HEAD_DIM, dim),
                          (rt.AT_I_CAPACITY, capacity), (rt.AT_I_INVFREQ_BF16, 1),
