@@ -328,6 +328,31 @@ typedef struct mb_attention_args {
 
 int mb_attention_decode_static(const mb_attention_args* args, void* stream);
 
+/* ---- greedy pick on the device ------------------------------------------------------------
+ * Replaces the host-side pick of the reference's generation loop
+ * (`int(logits[0, -1].argmax().item())`, examples/single_gpu_generate.py:76) and provides what
+ * its roadmap lists as missing (multi-step decode loop with on-device argmax,
+ * docs/roadmap.md:180,223): for every batch row, the index of the largest logit (lowest index
+ * on ties, NaN above every number -- torch.argmax's rules) is written into `input_ids`, the
+ * tensor the next decode launch reads; `position_ids` (optional) is advanced by one; the id is
+ * appended to `out_tokens[row][cursor[row]]` and `cursor[row]` incremented (optional; the
+ * cursor keeps counting when the log is full, ids past `out_capacity` are dropped).
+ * One launch, no allocation, no host synchronisation: a decode launch followed by this call
+ * can be enqueued back to back any number of times, or captured in a CUDA graph.           */
+typedef struct mb_greedy_args {
+    int32_t rows;             /* batch rows                                               */
+    int32_t vocab;            /* logits per row                                           */
+    int32_t out_capacity;     /* ids per row that out_tokens can hold                     */
+    int32_t reserved;
+    uint64_t logits;          /* [rows, vocab] bf16, contiguous                           */
+    uint64_t input_ids;       /* int64 [rows], overwritten with the picks                 */
+    uint64_t position_ids;    /* int64 [rows], incremented; 0 = leave alone               */
+    uint64_t out_tokens;      /* int64 [rows, out_capacity] log of picks; 0 = none        */
+    uint64_t cursor;          /* int32 [rows] next free column of out_tokens (with it)    */
+} mb_greedy_args;
+
+int mb_greedy_advance(const mb_greedy_args* args, void* stream);
+
 const char* mb_strerror(int code);
 const char* mb_status_string(int status_code);
 const char* mb_last_cuda_error(void);

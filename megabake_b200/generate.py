@@ -1,5 +1,6 @@
 """Greedy generation on one GPU: one compiled prefill that seeds the explicit KV state, then one
-compiled decode call per token.
+compiled decode call per token -- picked on the host (``__call__``) or, with no host work per
+token at all, picked on the device inside a replayed CUDA graph (``on_device``).
 
 The counterpart of the reference's ``examples/single_gpu_generate.py`` -- which has to feed the
 prompt through its decode step token by token because its prefill cannot seed the decode state
@@ -11,6 +12,8 @@ from __future__ import annotations
 
 import torch
 
+from . import runtime as rt
+from .engine import graphed
 from .frontend import make_backend
 from .hf import StatefulDecoder, StatefulPrefill
 
@@ -54,3 +57,57 @@ class GreedyGenerator:
             if backend.megabake_last_callable is not None:
                 backend.megabake_last_callable.check()
         return torch.cat(produced, dim=1)
+
+    # -- the multi-step loop with the pick on the device ------------------------------------
+    def _build_loop(self, steps_per_graph: int):
+        """Capture ``steps_per_graph`` x (decode launch, greedy pick) in one CUDA graph.  The
+        pick writes the next id into the very tensor the next decode launch reads and advances
+        the positions, so a replay needs nothing from the host (the reference lists this loop
+        as future work, ``docs/roadmap.md:180``)."""
+        if 2 * steps_per_graph + 1 > self.capacity:
+            raise ValueError("the KV capacity is too small to warm this many steps up")
+        self._token = torch.zeros(self.batch, 1, dtype=torch.int64, device=self.device)
+        self._position = torch.zeros(self.batch, 1, dtype=torch.int64, device=self.device)
+        self._picked = torch.zeros(self.batch, self.capacity, dtype=torch.int64, device=self.device)
+        self._cursor = torch.zeros(self.batch, dtype=torch.int32, device=self.device)
+        for index in range(2, len(self.state), 3):
+            self.state[index].zero_()  # the warm-up runs of the capture start from an empty cache
+
+        def loop(token, position, *state):
+            for _ in range(steps_per_graph):
+                logits = self._decode(token, position, *state)
+                rt.greedy_advance(logits, token, position, self._picked, self._cursor)
+            return self._picked
+
+        self._loop = graphed(loop, self._token, self._position, *self.state)
+        self._loop_steps = steps_per_graph
+
+    @torch.no_grad()
+    def on_device(self, input_ids: torch.Tensor, new_tokens: int,
+                  steps_per_graph: int = 1) -> torch.Tensor:
+        """Same result as ``__call__``, but every token after the prompt is picked by
+        ``mb_greedy_advance`` on the device and the decode steps run as replays of one CUDA
+        graph holding ``steps_per_graph`` steps; the host reads the ids once, at the end.
+        ``new_tokens - 1`` must be a multiple of ``steps_per_graph``."""
+        if tuple(input_ids.shape) != (self.batch, self.prompt_tokens):
+            raise ValueError("this generator was compiled for another prompt shape")
+        if self.prompt_tokens + new_tokens > self.capacity:
+            raise ValueError("the KV capacity cannot hold the prompt plus the new tokens")
+        if steps_per_graph < 1 or (new_tokens - 1) % steps_per_graph:
+            raise ValueError("new_tokens - 1 must be a multiple of steps_per_graph")
+        if getattr(self, "_loop_steps", None) != steps_per_graph:
+            self._build_loop(steps_per_graph)
+        logits = self._prefill(input_ids.to(self.device), *self.state)
+        self._cursor.zero_()
+        self._position.fill_(self.prompt_tokens)
+        # the first pick comes from the prompt's last position; positions stay where they are
+        rt.greedy_advance(logits[:, -1].contiguous(), self._token, None, self._picked,
+                          self._cursor)
+        for _ in range((new_tokens - 1) // steps_per_graph):
+            self._loop(self._token, self._position, *self.state)
+        for backend in (self.prefill_backend, self.decode_backend):
+            if backend.megabake_last_callable is not None:
+                backend.megabake_last_callable.check()
+        if int(self._cursor.max()) != new_tokens or int(self._cursor.min()) != new_tokens:
+            raise RuntimeError("the device-side loop produced an unexpected number of tokens")
+        return self._picked[:, :new_tokens].clone()

@@ -129,6 +129,18 @@ class AttentionArgs(ctypes.Structure):
     ]
 
 
+class GreedyArgs(ctypes.Structure):
+    """``mb_greedy_args`` of the on-device greedy pick."""
+
+    _fields_ = [
+        ("rows", ctypes.c_int32), ("vocab", ctypes.c_int32), ("out_capacity", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("logits", ctypes.c_uint64), ("input_ids", ctypes.c_uint64),
+        ("position_ids", ctypes.c_uint64), ("out_tokens", ctypes.c_uint64),
+        ("cursor", ctypes.c_uint64),
+    ]
+
+
 class Status(ctypes.Structure):
     _fields_ = [
         ("code", ctypes.c_int32),
@@ -145,7 +157,7 @@ EXPORTS = (
     "mb_plan_create", "mb_plan_query", "mb_plan_bind", "mb_plan_launch", "mb_plan_status",
     "mb_plan_reset", "mb_plan_set_trace", "mb_plan_destroy", "mb_strerror", "mb_status_string", "mb_last_cuda_error",
     "mb_abi_version", "mb_fixed_smem_bytes", "mb_stage_bytes", "mb_max_smem_bytes",
-    "mb_attention_decode_static",
+    "mb_attention_decode_static", "mb_greedy_advance",
 )
 
 _library = None
@@ -200,6 +212,8 @@ def load_library(path: Path | None = None) -> ctypes.CDLL:
         lib.mb_last_cuda_error.restype = ctypes.c_char_p
         lib.mb_attention_decode_static.argtypes = [ctypes.POINTER(AttentionArgs), ctypes.c_void_p]
         lib.mb_attention_decode_static.restype = ctypes.c_int
+        lib.mb_greedy_advance.argtypes = [ctypes.POINTER(GreedyArgs), ctypes.c_void_p]
+        lib.mb_greedy_advance.restype = ctypes.c_int
         if lib.mb_abi_version() != MB_ABI_VERSION:
             raise _native_error(
                 f"{target} speaks ABI {lib.mb_abi_version()}, the host expects {MB_ABI_VERSION}"
@@ -217,6 +231,50 @@ def _check(lib: ctypes.CDLL, code: int, stage: str, what: str) -> None:
     if code == 2 and detail:
         message += f" [{detail}]"
     raise CompilerError(CompilerDiagnostic(stage, message))
+
+
+def greedy_advance(logits, input_ids, position_ids=None, out_tokens=None, cursor=None,
+                   stream: int | None = None) -> None:
+    """Enqueue ``mb_greedy_advance``: per row of ``logits`` (``[rows, 1, vocab]`` or
+    ``[rows, vocab]`` bf16) write the greedy pick into ``input_ids`` (int64 ``[rows, 1]``),
+    add one to ``position_ids`` and append the pick to ``out_tokens[row, cursor[row]]``.
+    Non-blocking, on ``stream`` (default: torch's current stream); the tensors are the
+    caller's and must stay alive until the stream has run the kernel."""
+    import torch
+
+    lib = load_library()
+    rows, vocab = logits.shape[0], logits.shape[-1]
+    if logits.dtype != torch.bfloat16 or not logits.is_contiguous() or logits.numel() != rows * vocab:
+        raise CompilerError(CompilerDiagnostic(
+            "input-binding", "greedy_advance needs contiguous bf16 logits of one position per row"))
+    for name, tensor, dtype in (("input_ids", input_ids, torch.int64),
+                                ("position_ids", position_ids, torch.int64),
+                                ("out_tokens", out_tokens, torch.int64),
+                                ("cursor", cursor, torch.int32)):
+        if tensor is None:
+            continue
+        if tensor.dtype != dtype or not tensor.is_contiguous() or tensor.device != logits.device:
+            raise CompilerError(CompilerDiagnostic(
+                "input-binding", f"greedy_advance: {name} must be a contiguous {dtype} tensor on "
+                                 f"{logits.device}"))
+        if name != "out_tokens" and tensor.numel() != rows:
+            raise CompilerError(CompilerDiagnostic(
+                "input-binding", f"greedy_advance: {name} must hold one element per row"))
+    if (out_tokens is None) != (cursor is None):
+        raise CompilerError(CompilerDiagnostic(
+            "input-binding", "greedy_advance: out_tokens and cursor come together"))
+    args = GreedyArgs()
+    args.rows, args.vocab = rows, vocab
+    args.out_capacity = 0 if out_tokens is None else out_tokens.shape[-1]
+    args.logits, args.input_ids = logits.data_ptr(), input_ids.data_ptr()
+    args.position_ids = 0 if position_ids is None else position_ids.data_ptr()
+    args.out_tokens = 0 if out_tokens is None else out_tokens.data_ptr()
+    args.cursor = 0 if cursor is None else cursor.data_ptr()
+    if stream is None:
+        stream = torch.cuda.current_stream(logits.device).cuda_stream
+    with torch.cuda.device(logits.device):
+        _check(lib, lib.mb_greedy_advance(ctypes.byref(args), ctypes.c_void_p(stream)),
+               "runtime", "mb_greedy_advance")
 
 
 class Plan:

@@ -97,3 +97,66 @@ def test_greedy_generator_picks_what_the_oracle_would():
         chosen = torch.full((batch, spec.vocab), -1.0)
         chosen[torch.arange(batch), produced[:, step]] = 1.0      # "logits" whose argmax is the pick
         assert greedy_pick_matches(chosen, reference[:, at])[0], step
+
+
+@pytest.mark.parametrize("rows,vocab", [(1, 49152), (3, 1001), (8, 151936), (2, 7)])
+def test_greedy_advance_is_argmax_with_first_index_ties(rows, vocab):
+    """``mb_greedy_advance`` through the C ABI: pick = first index of the row maximum, written
+    into the ids the next launch reads; positions advance; picks are logged at the cursor."""
+    from megabake_b200 import runtime as rt
+
+    generator = torch.Generator().manual_seed(rows * 1000 + vocab)
+    # few distinct values, so every row has many exact ties for the maximum
+    logits = torch.randint(-6, 7, (rows, 1, vocab), generator=generator).float().mul(0.125)
+    logits = logits.to(torch.bfloat16)
+    if vocab % 8:  # rows that do not start on a 16-byte boundary take the scalar head and tail
+        assert (vocab * 2) % 16 != 0
+    expected = torch.stack([(row == row.max()).nonzero()[0, 0] for row in logits[:, 0].float()])
+    ids = torch.full((rows, 1), -1, dtype=torch.int64, device="cuda")
+    positions = torch.arange(rows, dtype=torch.int64, device="cuda").reshape(rows, 1) + 40
+    log = torch.full((rows, 2), -1, dtype=torch.int64, device="cuda")
+    cursor = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    device_logits = logits.cuda()
+    for call in range(3):  # the third pick no longer fits the log: dropped, cursor still counts
+        rt.greedy_advance(device_logits, ids, positions, log, cursor)
+    torch.cuda.synchronize()
+    assert ids.cpu().flatten().tolist() == expected.tolist()
+    assert positions.cpu().flatten().tolist() == [40 + r + 3 for r in range(rows)]
+    assert log.cpu().tolist() == [[int(e), int(e)] for e in expected]
+    assert cursor.cpu().tolist() == [3] * rows
+    # a NaN beats every number, the first one wins (torch.argmax's rule)
+    device_logits[0, 0, vocab // 2] = float("nan")
+    device_logits[0, 0, vocab - 1] = float("nan")
+    rt.greedy_advance(device_logits, ids)
+    torch.cuda.synchronize()
+    assert int(ids[0, 0]) == vocab // 2
+
+
+@pytest.mark.parametrize("steps_per_graph", [1, 5])
+def test_device_side_loop_reproduces_the_host_loop(steps_per_graph):
+    """The multi-step loop with on-device picks (decode launch + ``mb_greedy_advance`` replayed
+    as one CUDA graph) must produce the ids the host-picked loop produces, and those must be
+    acceptable greedy picks of the oracle's logits."""
+    from megabake_b200 import GreedyGenerator
+
+    spec = models.get_spec("tiny-qwen2")
+    weights = models.init_weights(spec, 2)
+    model = models.build_hf_model(spec, 2, device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    batch, prompt, new = 2, 10, 11
+    ids = torch.randint(0, spec.vocab, (batch, prompt), generator=torch.Generator().manual_seed(5))
+    torch._dynamo.reset()
+    generator = GreedyGenerator(model, batch, prompt, capacity=prompt + new + 14)
+    on_host = generator(ids, new).cpu()
+    on_device = generator.on_device(ids, new, steps_per_graph=steps_per_graph).cpu()
+    assert on_device.shape == (batch, new) and on_device.dtype == torch.int64
+    assert torch.equal(on_device, on_host)
+    again = generator.on_device(ids, new, steps_per_graph=steps_per_graph).cpu()  # graph reuse
+    assert torch.equal(again, on_host)
+    everything = torch.cat([ids, on_device], dim=1)
+    reference = oracle.prefill(cfg, ow, everything[:, :-1])
+    for step in range(new):
+        chosen = torch.full((batch, spec.vocab), -1.0)
+        chosen[torch.arange(batch), on_device[:, step]] = 1.0
+        assert greedy_pick_matches(chosen, reference[:, prompt - 1 + step])[0], step
