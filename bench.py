@@ -14,6 +14,9 @@ number of keys (filled by a seeded prefill of uniform-random token ids).  Prints
                  with HOST buffers: per step a pinned host->device copy of token and position ids,
                  the graph replay (one megakernel launch), a device argmax of the logits and a
                  device->host read of the picked ids, synchronised every step
+* ``device_loop`` the same compiled step with the next token picked on the device
+                 (``mb_greedy_advance``) and 8 steps per CUDA graph replay: no host work per token,
+                 the picked ids are read once at the end (host wall clock)
 * ``roofline``   HBM roofline of the megakernel: algorithmic bytes per launch (weights once +
                  the valid KV rows) / mean launch time, against the measured copy bandwidth
 * ``cpu_baseline`` / ``--impl reference``  the CPU port of the reference forward (``oracle/``),
@@ -60,6 +63,7 @@ PREFILL_WORKLOADS = {
 DEFAULT_WORKLOAD = "qwen2-0.5b-b8-k4096"
 METRIC = "decode_us_per_token"
 UNIT = "us/token"
+LOOP_STEPS = 8  # decode steps per CUDA graph in the device-side greedy loop
 
 
 def measured_tensor_peak() -> tuple[float, str]:
@@ -482,7 +486,7 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=device)
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    total_calls = 2 * (steps + warmup) + 16
+    total_calls = 3 * (steps + warmup) + 96  # three timed loops plus graph warm-ups
     spec, batch, keys, capacity, weights, inv_freq, state = build_workload(
         args.workload, rank, total_calls, device, args.cache_fill)
     program = models.direct_program(spec, batch, capacity)
@@ -570,15 +574,51 @@ def run_ours(args) -> None:
     e2e_s = time.perf_counter() - t0
     compiled_decoder.check()
 
+    # ---- multi-step loop with the pick on the device ------------------------------------------
+    # The same compiled step, but the next token is picked by mb_greedy_advance on the device and
+    # LOOP_STEPS x (decode launch, pick) are captured in one CUDA graph: the host only replays
+    # graphs and reads all picked ids once at the end.
+    from megabake_b200 import runtime as rt
+
+    per_graph = LOOP_STEPS
+    replays = max(1, steps // per_graph)
+    picked = torch.zeros(batch, (replays + 4) * per_graph, dtype=torch.int64, device=device)
+    cursor = torch.zeros(batch, dtype=torch.int32, device=device)
+    dev_pos.fill_(keys + call)
+
+    def device_loop(token, position, *kv_state):
+        for _ in range(per_graph):
+            out = step_fn(token, position, *kv_state)
+            rt.greedy_advance(out, token, position, picked, cursor)
+        return picked
+
+    with torch.no_grad():
+        loop_call = graphed(device_loop, dev_ids, dev_pos, *state)
+    cursor.zero_()
+    loop_call(dev_ids, dev_pos, *state)  # one untimed replay
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(replays):
+        loop_call(dev_ids, dev_pos, *state)
+    host_picks = picked.cpu()  # the one device -> host read (synchronises)
+    barrier()
+    loop_s = time.perf_counter() - t0
+    compiled_decoder.check()
+    assert int(cursor.min()) == (replays + 1) * per_graph and int(host_picks.max()) < spec.vocab
+    loop = {"seconds": loop_s, "steps": replays * per_graph, "per_graph": per_graph,
+            "d2h_bytes": host_picks.numel() * 8}
+
     return _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s,
-                   mean_keys, plan_info, sampler, rank, world, distributed, device)
+                   mean_keys, plan_info, sampler, rank, world, distributed, device, loop)
 
 
 def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s, mean_keys,
-            plan_info, sampler, rank, world, distributed, device) -> None:
+            plan_info, sampler, rank, world, distributed, device, loop=None) -> None:
     import torch
 
-    device_ms, e2e_ms = max_over_ranks([device_ms, (e2e_s or 0.0) * 1e3], device, distributed)
+    device_ms, e2e_ms, loop_ms = max_over_ranks(
+        [device_ms, (e2e_s or 0.0) * 1e3, (loop["seconds"] if loop else 0.0) * 1e3], device,
+        distributed)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -617,6 +657,16 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
             "gpu_launches": steps,
             "clocks": sampler.summary(),
         }
+        if loop is not None:
+            line["device_loop"] = {
+                "value": loop_ms * 1e3 / loop["steps"] / (batch * world), "unit": UNIT,
+                "ms_per_step": loop_ms / loop["steps"], "steps": loop["steps"],
+                "steps_per_graph": loop["per_graph"], "launches_per_step": 2,
+                "h2d_bytes_per_step": 0, "d2h_bytes_total": loop["d2h_bytes"],
+                "path": "the same compiled step + mb_greedy_advance (pick on the device), "
+                        f"{loop['per_graph']} steps per CUDA graph replay, host wall clock, picked "
+                        "ids read once at the end",
+            }
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_reference_run(args.workload, 8, 1, budget_s=25.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}

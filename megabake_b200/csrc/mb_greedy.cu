@@ -7,10 +7,11 @@
 // logit: the kernel below writes the chosen id straight into the `input_ids` tensor the next
 // decode launch reads, advances `position_ids`, and logs the id.
 //
-// One CTA per batch row.  Each thread scans a strided share of the row's logits with 16-byte
-// loads (inputs come from L2: the LM head wrote them a moment ago), keeping (value, first index
-// of that value); shuffles and one shared-memory step reduce the CTA.  Ties go to the lowest
-// index and a NaN beats every number, which is what torch.argmax does.
+// One CTA of 1,024 threads per batch row.  Each thread scans a strided share of the row's logits
+// with 16-byte loads, four in flight (inputs come from L2: the LM head wrote them a moment ago,
+// and the scan is bound by that latency), keeping (value, first index of that value);
+// shuffles and one shared-memory step reduce the CTA.  Ties go to the lowest index and a NaN
+// beats every number, which is what torch.argmax does.
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -20,7 +21,8 @@
 namespace mb {
 namespace greedy {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 1024;
+constexpr int kUnroll = 4;  // 16-byte loads in flight per thread: the scan is L2-latency bound
 
 struct Pick {
     float value;
@@ -51,15 +53,26 @@ greedy_pick_kernel(const unsigned short* __restrict__ logits, int vocab, long lo
     if (head > vocab) head = vocab;
     const int vectors = (vocab - head) / 8;
     const uint4* body = reinterpret_cast<const uint4*>(x + head);
-    for (int v = tid; v < vectors; v += kThreads) {
-        const uint4 raw = __ldg(body + v);
-        const unsigned int w[4] = {raw.x, raw.y, raw.z, raw.w};
-        const int base = head + 8 * v;
+    for (int v0 = tid; v0 < vectors; v0 += kThreads * kUnroll) {
+        uint4 raw[kUnroll];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float lo = bf16_bits(w[q] & 0xffffu), hi = bf16_bits(w[q] >> 16);
-            if (beats(lo, base + 2 * q, mine.value, mine.index)) mine = {lo, base + 2 * q};
-            if (beats(hi, base + 2 * q + 1, mine.value, mine.index)) mine = {hi, base + 2 * q + 1};
+        for (int u = 0; u < kUnroll; ++u) {
+            const int v = v0 + u * kThreads;
+            raw[u] = v < vectors ? __ldg(body + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int v = v0 + u * kThreads;
+            if (v >= vectors) break;
+            const unsigned int w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            const int base = head + 8 * v;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float lo = bf16_bits(w[q] & 0xffffu), hi = bf16_bits(w[q] >> 16);
+                if (beats(lo, base + 2 * q, mine.value, mine.index)) mine = {lo, base + 2 * q};
+                if (beats(hi, base + 2 * q + 1, mine.value, mine.index))
+                    mine = {hi, base + 2 * q + 1};
+            }
         }
     }
     for (int i = tid; i < head; i += kThreads) {
