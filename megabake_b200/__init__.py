@@ -11,6 +11,7 @@ parts of it this backend keeps):
 ``PrefillLogits``                   ids -> logits prefill wrapper over ``megabake::attention``
 ``StatefulPrefill``                 prefill that also fills the explicit decode state
 ``GreedyGenerator``                 compiled prefill + decode loop over one KV state
+``bucketed`` / ``PaddingDependence`` prompts of any length through a few fixed-shape compiles
 ``register_transformers_attention`` the ``"megabake"`` attention implementation for HF models
 ``CompilerError``                   every refusal, with a staged diagnostic
 """
@@ -19,8 +20,8 @@ from .diagnostics import CompilerDiagnostic, CompilerError
 from .ops import attention, kv_attention
 
 __all__ = [
-    "CompilerDiagnostic", "CompilerError", "DecodeStep", "GreedyGenerator", "PrefillLogits",
-    "StatefulDecoder", "StatefulPrefill", "attention",
+    "CompilerDiagnostic", "CompilerError", "DecodeStep", "GreedyGenerator", "PaddingDependence",
+    "PrefillLogits", "StatefulDecoder", "StatefulPrefill", "attention", "bucketed",
     "graphed", "kv_attention", "make_backend", "register_transformers_attention",
 ]
 
@@ -37,6 +38,9 @@ def __getattr__(name):
                 "register_transformers_attention"):
         from . import hf
         return getattr(hf, name)
+    if name in ("bucketed", "PaddingDependence"):
+        from . import buckets
+        return getattr(buckets, name)
     if name == "GreedyGenerator":
         from .generate import GreedyGenerator
         return GreedyGenerator

@@ -158,3 +158,37 @@ def test_compiled_prefill_matches_oracle(name, batch, tokens):
     assert isinstance(decoder, BoundDecoder) and decoder.launches == 2
     decoder.check()
     assert backend.megabake_last_compiled.mode == "prefill"
+
+
+def test_bucketed_prefill_serves_odd_prompt_lengths():
+    """``bucketed(PrefillLogits(model), backend=make_backend(mode="prefill"))``: prompts of 9
+    and 21 tokens run through the 16- and 32-token plans; logits at the real positions match the
+    oracle's prefill of the unpadded prompt."""
+    from megabake_b200 import PrefillLogits, bucketed
+
+    spec = models.get_spec("tiny-qwen2")
+    weights = models.init_weights(spec, 6)
+    model = models.build_hf_model(spec, 6, device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    cfg, ow = oracle_config(spec), oracle_weights(weights, models.inv_freq_buffer(spec))
+    backend = make_backend(mode="prefill")
+    torch._dynamo.reset()
+    call = bucketed(PrefillLogits(model).eval(), backend=backend,
+                    sequence_args={"input_ids": 1}, buckets=(16, 32))
+    generator = torch.Generator().manual_seed(4)
+    planned = []
+    for length in (9, 21, 16):
+        ids = torch.randint(0, spec.vocab, (2, length), generator=generator)
+        got = call(ids.cuda())
+        torch.cuda.synchronize()
+        ref = oracle.prefill(cfg, ow, ids)
+        assert got.shape == ref.shape
+        assert logits_close(got, ref)[0], (length, max_abs(got, ref))
+        for b in range(2):
+            assert cosine(got[b], ref[b]) >= LOGIT_COSINE
+            assert greedy_pick_matches(got[b, -1:], ref[b, -1:])[0]
+        decoder = backend.megabake_last_callable
+        assert isinstance(decoder, BoundDecoder)
+        decoder.check()
+        planned.append(decoder.program.tokens)  # the plan of the most recent capture
+    assert planned == [16, 32, 32] and call.verified == {16, 32}  # the third call reused bucket 16
