@@ -53,6 +53,7 @@ __device__ __forceinline__ void trace_stamp(const KernelParams& p, int ph, int e
 struct SharedCtl {
     unsigned long long full[kMaxStages];
     unsigned long long empty[kMaxStages];
+    unsigned long long act_full;     // the activation rows of the current GEMV phase have landed
     volatile int abort_flag;
     volatile unsigned int issued;    // stages the producer armed
     int bcast[4];                    // small broadcasts (attention chunking, arrival order)
@@ -281,56 +282,50 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 // One global round trip: every activation row (and the norm weight vector, staged as one
-// extra row) is copied global -> shared with 16-byte asynchronous copies that are all in
-// flight together; scaling, sums of squares and the normalisation then run out of shared
-// memory.  Kept out of line and free of unrolled row loops: the phase loop must stay small
-// enough for the instruction cache.
+// extra row) is copied global -> shared by ONE bulk copy per row, issued by a single warp and
+// counted on an mbarrier; scaling, sums of squares and the normalisation then run out of shared
+// memory.  (16-byte cp.async copies by all threads moved the same bytes, but issuing a few
+// hundred of them stalled the issuing warps for about a microsecond on the load/store unit's
+// miss tracking; the bulk-copy engine takes the rows in one instruction.)
 // Part 1 (activation_issue) only starts the copies; part 2 (activation_finish) waits for them
 // and normalises.  The GEMV body runs its own address arithmetic and epilogue-operand loads
 // between the two, under the latency of the copies.
+// `round` counts the GEMV phases this CTA has run: the parity of the activation barrier.
 __device__ __noinline__ void activation_issue(const KernelParams& p, const PhaseEntry* E, int ph,
-                                              __nv_bfloat16* xs, int tid) {
+                                              SharedCtl* sc, __nv_bfloat16* xs, int tid) {
+    if (tid >= 32) return;
     const mb_phase& P = E->rec;
     const int rows = P.i[MB_GV_I_ROWS];
     const int K = P.i[MB_GV_I_K];
     const int xpitch = K + 32;
     const bool gather = P.i[MB_GV_I_GATHER] != 0;
+    const bool normed = P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE;
     const char* xbase = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X));
     const long long* ids =
         gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
-    const int vec_per_row = K / 8;  // 16-byte vectors
+    const unsigned int row_bytes = static_cast<unsigned int>(K) * 2u;
+    const int lane = tid;
     bool bad_token = false;
-    const bool transformed = P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE || gather;
-    if (rows >= 2 && transformed) {
-        // one warp per row: the warp that copies a row also scales / normalises it, so the
-        // prologue needs no CTA barrier between its passes (activation_finish)
-        const int warp = tid >> 5, lane = tid & 31;
-        for (int r = warp; r < rows; r += kConsumerWarps) {
-            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
-            __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
-            for (int v = lane; v < vec_per_row; v += 32)
-                cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
-        }
-    } else {
-        for (int r = 0; r < rows; ++r) {
-            const char* src = activation_row(E, xbase, ids, r, K, &bad_token);
-            __nv_bfloat16* dst = xs + static_cast<size_t>(r) * xpitch;
-            for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-                cp_async16(dst + v * 8, src + static_cast<size_t>(v) * 16);
-        }
-        if (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
-            __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
-            const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
-            for (int v = tid; v < vec_per_row; v += kConsumerThreads)
-                cp_async16(wrow + v * 8, nw + static_cast<size_t>(v) * 16);
-        }
+    const char* src = nullptr;
+    if (lane < rows) src = activation_row(E, xbase, ids, lane, K, &bad_token);
+    if (lane == rows && normed)  // the norm weights travel as row number `rows`
+        src = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
+    if (sc->abort_flag) return;  // a faulted CTA arms nothing (activation_finish will not wait)
+    if (lane == 0) {
+        // the rows' shared memory was last touched by ordinary loads and stores
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_expect_tx(&sc->act_full, row_bytes * static_cast<unsigned int>(rows + (normed ? 1 : 0)));
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    if (bad_token && tid == 0) record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
+    __syncwarp();
+    if (src != nullptr)
+        bulk_copy_g2s(xs + static_cast<size_t>(lane) * xpitch, src, row_bytes, &sc->act_full);
+    if (__any_sync(0xffffffffu, bad_token) && lane == 0)
+        record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
 }
 
-__device__ __noinline__ void activation_finish(const KernelParams& p, const PhaseEntry* E,
-                                               SharedCtl* sc, __nv_bfloat16* xs, int tid) {
+__device__ __noinline__ void activation_finish(const KernelParams& p, const PhaseEntry* E, int ph,
+                                               SharedCtl* sc, __nv_bfloat16* xs, unsigned int round,
+                                               int tid) {
     const mb_phase& P = E->rec;
     const int rows = P.i[MB_GV_I_ROWS];
     const int K = P.i[MB_GV_I_K];
@@ -342,22 +337,22 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
     const bool store_x = gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0;
     const int warp = tid >> 5, lane = tid & 31;
     const int vec_per_row = K / 8;  // 16-byte vectors
-    __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
+    if (!mbar_wait_bounded(&sc->act_full, round & 1u, &sc->abort_flag)) {
+        if (!sc->abort_flag) {
+            record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, blockIdx.x);
+            sc->abort_flag = 1;
+        }
+        // fall through: the rows are garbage, the CTA drains at the next barrier
+    }
 
     if (rows >= 2 && (pro != MB_PRO_NONE || gather)) {
-        // warp r owns row r from the copy to the normalised result (see activation_issue)
-        __syncwarp();
+        // one warp per row: sum of squares and normalisation of a row need no CTA barrier
+        // between them
         char* store = store_x ? reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE))
-                              : nullptr;
-        const uint4* nw = pro != MB_PRO_NONE
-                              ? reinterpret_cast<const uint4*>(entry_address(p, E, MB_GV_S_NORM_W))
                               : nullptr;
         for (int r = warp; r < rows; r += kConsumerWarps) {
             __nv_bfloat16* row = xs + static_cast<size_t>(r) * xpitch;
-            // the first weight vector is requested before the row is summed
-            uint4 w_first = make_uint4(0u, 0u, 0u, 0u);
-            if (nw != nullptr && lane < vec_per_row) w_first = __ldg(nw + lane);
             float ss = 0.f;
             for (int v = lane; v < vec_per_row; v += 32) {
                 uint4* cell = reinterpret_cast<uint4*>(row + v * 8);
@@ -376,8 +371,8 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
                 const float inv = 1.0f / sqrtf(ss / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
                 for (int v = lane; v < vec_per_row; v += 32) {
                     uint4* cell = reinterpret_cast<uint4*>(row + v * 8);
-                    const uint4 w = v == lane ? w_first : __ldg(nw + v);
-                    *cell = normalise_vector(*cell, w, inv, pro);
+                    *cell = normalise_vector(*cell, *reinterpret_cast<const uint4*>(wrow + v * 8),
+                                             inv, pro);
                 }
             }
         }
@@ -386,7 +381,7 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
     }
 
     if (scaled || store_x || pro != MB_PRO_NONE) {
-        // every thread works on the vectors it copied itself, so no barrier is needed yet
+        // every thread works on its own vectors in both passes
         char* store = store_x ? reinterpret_cast<char*>(entry_address(p, E, MB_GV_S_XSTORE))
                               : nullptr;
         for (int r = 0; r < rows; ++r) {
@@ -521,7 +516,8 @@ __device__ __forceinline__ void store_output(const EpilogueCtx& e, const OutputC
 template <int NMAT>
 __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntry* E, int ph,
                                              SharedCtl* sc, const __nv_bfloat16* xs, float* red,
-                                             const char* ring, unsigned int& it, int tid) {
+                                             const char* ring, unsigned int& it,
+                                             unsigned int act_round, int tid) {
     constexpr int NB = NMAT == 1 ? 8 : 4;  // row blocks per reduction group
     constexpr int PV = 2 * NMAT;           // partial values per lane and block
     const int cta = blockIdx.x, ctas = gridDim.x;
@@ -572,7 +568,7 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
         }
 
         if (!staged) {
-            activation_finish(p, E, sc, const_cast<__nv_bfloat16*>(xs), tid);
+            activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
             staged = true;
         }
         for (int b = 0; b < nb; ++b) {
@@ -660,7 +656,8 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
         }
         if (group0 + NB < g.n_blocks) named_barrier(kBarConsumers, kConsumerThreads);
     }
-    if (!staged) activation_finish(p, E, sc, const_cast<__nv_bfloat16*>(xs), tid);  // no rows here
+    if (!staged)  // no rows here
+        activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
     return !dead && !sc->abort_flag;
 }
 
@@ -1341,6 +1338,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             mbar_init(&sc->full[s], 1);
             mbar_init(&sc->empty[s], kConsumerWarps);
         }
+        mbar_init(&sc->act_full, 1);
         sc->abort_flag = peek_status(p.ctl) != 0 ? 1 : 0;  // a faulted plan runs nothing
         sc->issued = 0;
         mbar_init_fence();
@@ -1358,6 +1356,7 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(&p.ctl->calls);
         const unsigned int base = calls * static_cast<unsigned int>(p.barriers_per_launch);
         unsigned int it = 0;
+        unsigned int act_round = 0;  // GEMV phases run so far: parity of the activation barrier
         int barrier_index = 0;
         bool ok = true;
         // Optional per-phase trace: thread 0 of every CTA stamps the global timer at phase
@@ -1380,12 +1379,13 @@ decode_kernel(const __grid_constant__ KernelParams p) {
                     break;
                 case MB_BODY_GEMV: {
                     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(act);
-                    activation_issue(p, E, ph, xs, tid);
+                    activation_issue(p, E, ph, sc, xs, tid);
                     stamp(ph, 1);
                     if (E->rec.i[MB_GV_I_NMAT] == 2)
-                        gemv_consume<2>(p, E, ph, sc, xs, red, ring, it, tid);
+                        gemv_consume<2>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
                     else
-                        gemv_consume<1>(p, E, ph, sc, xs, red, ring, it, tid);
+                        gemv_consume<1>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
+                    ++act_round;
                     break;
                 }
                 case MB_BODY_ATTN_DECODE: {

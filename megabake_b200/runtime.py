@@ -9,6 +9,7 @@ library or one of its symbols is missing: there is no other execution path.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -150,7 +151,10 @@ class Status(ctypes.Structure):
     ]
 
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "_lib" / "libmegabake_b200.so"
+# The in-tree build, unless MEGABAKE_B200_LIBRARY names another build of the same ABI (a debug
+# build, or two builds compared in one session).
+LIBRARY_PATH = Path(os.environ.get("MEGABAKE_B200_LIBRARY") or
+                    Path(__file__).resolve().parent / "_lib" / "libmegabake_b200.so")
 
 # Every symbol include/megabake_b200.h declares; the loader checks all of them.
 EXPORTS = (
