@@ -422,7 +422,7 @@ def run_prefill(args) -> None:
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_prefill_run(args.workload, 3, budget_s=25.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
@@ -435,7 +435,7 @@ def run_reference(args) -> None:
     if args.workload in PREFILL_WORKLOADS:
         result = cpu_prefill_run(args.workload, args.steps, budget_s=120.0)
         preset, batch, tokens = PREFILL_WORKLOADS[args.workload]
-        print(json.dumps({
+        emit({
             "impl": "reference", "metric": "prefill_tokens_per_s", "value": result["value"],
             "unit": "tok/s", "n_gpus": args.gpus, "steps": result["steps"], "warmup": 0,
             "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
@@ -446,7 +446,7 @@ def run_reference(args) -> None:
             "e2e": {"value": result["value"], "unit": "tok/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
-        }), flush=True)
+        })
         return
     result = cpu_reference_run(args.workload, args.steps, min(args.warmup, 2), budget_s=120.0)
     preset, batch, keys = WORKLOADS[args.workload]
@@ -462,7 +462,7 @@ def run_reference(args) -> None:
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_ours(args) -> None:
@@ -670,14 +670,30 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_reference_run(args.workload, 8, 1, budget_s=25.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if distributed:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
 
 
+_RESULT_STREAM = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line of the run, on the process's original stdout."""
+    stream = _RESULT_STREAM or sys.stdout
+    stream.write(json.dumps(line) + "\n")
+    stream.flush()
+
+
 def main() -> None:
+    # Libraries print banners on stdout (NCCL's version line under torchrun): keep the original
+    # stdout for the result line alone and send everything else to stderr.
+    global _RESULT_STREAM
+    sys.stdout.flush()
+    _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
