@@ -7,11 +7,15 @@
 // logit: the kernel below writes the chosen id straight into the `input_ids` tensor the next
 // decode launch reads, advances `position_ids`, and logs the id.
 //
-// One CTA of 1,024 threads per batch row.  Each thread scans a strided share of the row's logits
-// with 16-byte loads, four in flight (inputs come from L2: the LM head wrote them a moment ago,
-// and the scan is bound by that latency), keeping (value, first index of that value);
-// shuffles and one shared-memory step reduce the CTA.  Ties go to the lowest index and a NaN
-// beats every number, which is what torch.argmax does.
+// One CTA of 1,024 threads per batch row, two sweeps over the row (inputs come from L2: the LM
+// head wrote them a moment ago).  Sweep 1 finds the row maximum on packed bf16 pairs
+// (`__hmax2_nan`: one instruction per two logits, a NaN wins); sweep 2 finds the first index
+// that holds it (`__heq2_mask` on pairs, so -0 and +0 count as equal), each thread stopping at
+// its own first hit.  Keeping (value, index) in one sweep costs about 14 instructions per
+// logit and made the scan issue-bound; the two sweeps cost about 3.  Shuffles and one
+// shared-memory step reduce the CTA each time.  Ties go to the lowest index and a NaN beats
+// every number, which is what torch.argmax does.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -22,30 +26,35 @@ namespace mb {
 namespace greedy {
 
 constexpr int kThreads = 1024;
-constexpr int kUnroll = 4;  // 16-byte loads in flight per thread: the scan is L2-latency bound
+constexpr int kWarps = kThreads / 32;
+constexpr int kUnroll = 4;  // 16-byte loads in flight per thread: the sweeps are latency bound
+constexpr int kNone = 0x7fffffff;
 
-struct Pick {
-    float value;
-    int index;
-};
-
-// true when candidate (v, i) should replace (best, bi)
-__device__ __forceinline__ bool beats(float v, int i, float best, int bi) {
-    const bool v_nan = v != v, b_nan = best != best;
-    if (v_nan || b_nan) return v_nan && (!b_nan || i < bi);
-    return v > best || (v == best && i < bi);
+// maximum with a NaN winning over every number
+__device__ __forceinline__ float max_nan(float a, float b) {
+    return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b);
 }
 
 __device__ __forceinline__ float bf16_bits(unsigned int bits16) {
     return __uint_as_float(bits16 << 16);
 }
 
+__device__ __forceinline__ __nv_bfloat162 as_pair(unsigned int word) {
+    return *reinterpret_cast<const __nv_bfloat162*>(&word);
+}
+
+__device__ __forceinline__ bool hits(float v, float target) {
+    return target != target ? v != v : v == target;
+}
+
 __global__ void __launch_bounds__(kThreads)
 greedy_pick_kernel(const unsigned short* __restrict__ logits, int vocab, long long* ids,
                    long long* positions, long long* out_tokens, int out_capacity, int* cursor) {
-    const int row = blockIdx.x, tid = threadIdx.x;
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned short* x = logits + static_cast<size_t>(row) * vocab;
-    Pick mine = {-INFINITY, 0x7fffffff};
+    __shared__ float warp_max[kWarps];
+    __shared__ int warp_first[kWarps];
+    __shared__ float row_max;
 
     // 16-byte body when the row starts on a 16-byte boundary, scalar head/tail otherwise
     const uintptr_t address = reinterpret_cast<uintptr_t>(x);
@@ -53,57 +62,107 @@ greedy_pick_kernel(const unsigned short* __restrict__ logits, int vocab, long lo
     if (head > vocab) head = vocab;
     const int vectors = (vocab - head) / 8;
     const uint4* body = reinterpret_cast<const uint4*>(x + head);
+    const int tail0 = head + 8 * vectors;
+
+    // ---- sweep 1: the maximum
+    const unsigned int lowest = 0xff80ff80u;  // (-inf, -inf)
+    __nv_bfloat162 best2 = as_pair(lowest);
     for (int v0 = tid; v0 < vectors; v0 += kThreads * kUnroll) {
         uint4 raw[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int v = v0 + u * kThreads;
-            raw[u] = v < vectors ? __ldg(body + v) : make_uint4(0u, 0u, 0u, 0u);
+            raw[u] = v < vectors ? __ldg(body + v) : make_uint4(lowest, lowest, lowest, lowest);
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const int v = v0 + u * kThreads;
-            if (v >= vectors) break;
-            const unsigned int w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-            const int base = head + 8 * v;
+            best2 = __hmax2_nan(best2, as_pair(raw[u].x));
+            best2 = __hmax2_nan(best2, as_pair(raw[u].y));
+            best2 = __hmax2_nan(best2, as_pair(raw[u].z));
+            best2 = __hmax2_nan(best2, as_pair(raw[u].w));
+        }
+    }
+    float best = max_nan(__bfloat162float(best2.x), __bfloat162float(best2.y));
+    for (int i = tid; i < head; i += kThreads) best = max_nan(best, bf16_bits(x[i]));
+    for (int i = tail0 + tid; i < vocab; i += kThreads) best = max_nan(best, bf16_bits(x[i]));
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float lo = bf16_bits(w[q] & 0xffffu), hi = bf16_bits(w[q] >> 16);
-                if (beats(lo, base + 2 * q, mine.value, mine.index)) mine = {lo, base + 2 * q};
-                if (beats(hi, base + 2 * q + 1, mine.value, mine.index))
-                    mine = {hi, base + 2 * q + 1};
+    for (int offset = 16; offset > 0; offset >>= 1)
+        best = max_nan(best, __shfl_xor_sync(0xffffffffu, best, offset));
+    if (lane == 0) warp_max[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        float m = warp_max[lane];
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1)
+            m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, offset));
+        if (lane == 0) row_max = m;
+    }
+    __syncthreads();
+    const float target = row_max;
+
+    // ---- sweep 2: the first index holding it (every thread's indices only grow)
+    int first = kNone;
+    for (int i = tid; i < head; i += kThreads)
+        if (hits(bf16_bits(x[i]), target)) {
+            first = i;
+            break;
+        }
+    if (first == kNone) {
+        const bool nan_target = target != target;
+        const __nv_bfloat16 t16 = __float2bfloat16_rn(target);  // exact: it is one of the logits
+        const __nv_bfloat162 target2 = __halves2bfloat162(t16, t16);
+        for (int v0 = tid; v0 < vectors && first == kNone; v0 += kThreads * kUnroll) {
+            uint4 raw[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int v = v0 + u * kThreads;
+                raw[u] = v < vectors ? __ldg(body + v) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = kUnroll - 1; u >= 0; --u) {  // downwards: the lowest index is assigned last
+                const int v = v0 + u * kThreads;
+                if (v >= vectors) continue;
+                const unsigned int w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                if (!nan_target) {
+                    unsigned int any = 0;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) any |= __heq2_mask(as_pair(w[q]), target2);
+                    if (any == 0) continue;
+                }
+#pragma unroll
+                for (int q = 3; q >= 0; --q) {
+                    if (hits(bf16_bits(w[q] >> 16), target)) first = head + 8 * v + 2 * q + 1;
+                    if (hits(bf16_bits(w[q] & 0xffffu), target)) first = head + 8 * v + 2 * q;
+                }
             }
         }
     }
-    for (int i = tid; i < head; i += kThreads) {
-        const float v = bf16_bits(x[i]);
-        if (beats(v, i, mine.value, mine.index)) mine = {v, i};
-    }
-    for (int i = head + 8 * vectors + tid; i < vocab; i += kThreads) {
-        const float v = bf16_bits(x[i]);
-        if (beats(v, i, mine.value, mine.index)) mine = {v, i};
-    }
-
+    if (first == kNone)
+        for (int i = tail0 + tid; i < vocab; i += kThreads)
+            if (hits(bf16_bits(x[i]), target)) {
+                first = i;
+                break;
+            }
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, mine.value, offset);
-        const int oi = __shfl_xor_sync(0xffffffffu, mine.index, offset);
-        if (beats(ov, oi, mine.value, mine.index)) mine = {ov, oi};
-    }
-    __shared__ Pick warp_best[kThreads / 32];
-    if ((tid & 31) == 0) warp_best[tid >> 5] = mine;
+    for (int offset = 16; offset > 0; offset >>= 1)
+        first = min(first, __shfl_xor_sync(0xffffffffu, first, offset));
+    if (lane == 0) warp_first[warp] = first;
     __syncthreads();
-    if (tid == 0) {
-        for (int w = 1; w < kThreads / 32; ++w)
-            if (beats(warp_best[w].value, warp_best[w].index, mine.value, mine.index))
-                mine = warp_best[w];
-        const long long chosen = mine.index;
-        ids[row] = chosen;
-        if (positions != nullptr) positions[row] += 1;
-        if (out_tokens != nullptr) {
-            const int at = cursor[row];
-            if (at < out_capacity) out_tokens[static_cast<size_t>(row) * out_capacity + at] = chosen;
-            cursor[row] = at + 1;  // keeps counting past the end: the host sees an overrun
+    if (warp == 0) {
+        int f = warp_first[lane];
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1)
+            f = min(f, __shfl_xor_sync(0xffffffffu, f, offset));
+        if (lane == 0) {
+            const long long chosen = f;
+            ids[row] = chosen;
+            if (positions != nullptr) positions[row] += 1;
+            if (out_tokens != nullptr) {
+                const int at = cursor[row];
+                if (at < out_capacity)
+                    out_tokens[static_cast<size_t>(row) * out_capacity + at] = chosen;
+                cursor[row] = at + 1;  // keeps counting past the end: the host sees an overrun
+            }
         }
     }
 }
