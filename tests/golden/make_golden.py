@@ -3,7 +3,7 @@
 Run in the build container only (needs the reference checkout; the fixtures travel, the
 reference does not):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference     (or MEGABAKE_REFERENCE=/path/to/reference)
 
 It imports the reference's own operators and decode wrappers
 (``src/megabake/ops/attention.py``, ``tests/fixtures.py::StatefulSmolLM``,
@@ -29,7 +29,11 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+import os  # noqa: E402
+
+if len(sys.argv) < 2 and "MEGABAKE_REFERENCE" not in os.environ:
+    raise SystemExit("usage: make_golden.py /path/to/reference (a checkout of the reference)")
+REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["MEGABAKE_REFERENCE"])
 
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REFERENCE / "src"))
