@@ -281,7 +281,9 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     if (stages < 2) return MB_ERR_RESOURCE;
     const int smem = fixed + static_cast<int>(desc->activation_bytes) + stages * stage;
 
-    MB_CUDA(mb::decode_configure(smem));
+    // The attribute belongs to the kernel, not to a plan: set it to the device's opt-in limit so
+    // that plans of different sizes (two batch sizes, two models) can be launched in any order.
+    MB_CUDA(mb::decode_configure(limit));
     int per_sm = 0;
     MB_CUDA(mb::decode_occupancy(smem, &per_sm));
     if (per_sm < 1) return MB_ERR_RESOURCE;

@@ -94,3 +94,21 @@ def logits_close(logits: torch.Tensor, reference: torch.Tensor) -> tuple[bool, f
     exponent = torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -126)))
     allowed = torch.maximum(torch.full_like(ref, LOGIT_MAX_ABS), 2.0 * torch.exp2(exponent - 7))
     return bool((error <= allowed).all()), float(error.max())
+
+
+def ulp_histogram(logits: torch.Tensor, reference: torch.Tensor) -> dict:
+    """Distribution of |logits - reference| in bf16 ulps of the reference element: the share of
+    elements that are bit-equal, one, two, three to four, and more than four steps apart."""
+    got = logits.detach().float().cpu().flatten()
+    ref = reference.detach().float().cpu().flatten()
+    exponent = torch.floor(torch.log2(ref.abs().clamp_min(2.0 ** -126)))
+    steps = (got - ref).abs() / torch.exp2(exponent - 7)
+    total = float(steps.numel())
+    return {
+        "0": float((steps == 0).sum()) / total,
+        "<=1": float(((steps > 0) & (steps <= 1)).sum()) / total,
+        "<=2": float(((steps > 1) & (steps <= 2)).sum()) / total,
+        "<=4": float(((steps > 2) & (steps <= 4)).sum()) / total,
+        ">4": float((steps > 4).sum()) / total,
+        "max": float(steps.max()),
+    }

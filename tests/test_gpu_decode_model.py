@@ -165,3 +165,20 @@ def test_kv_overflow_raises_and_recovers():
     for tensor in h.state[2::3]:
         tensor.zero_()
     h.step(ids, torch.tensor([[0]]))
+
+
+def test_plans_of_different_sizes_launch_in_any_order():
+    """Two plans in one process: a batch-8 plan (more shared memory) created first, a batch-1 plan
+    after it; the large one must still launch -- the shared-memory attribute is per kernel, not
+    per plan."""
+    large = Harness("tiny-qwen2", 8, 16, seed=2)
+    small = Harness("tiny-llama", 1, 16, seed=2)
+    assert large.decoder.plan.smem_bytes != small.decoder.plan.smem_bytes
+    ids8 = torch.randint(0, large.spec.vocab, (8, 1), generator=torch.Generator().manual_seed(1))
+    ids1 = torch.randint(0, small.spec.vocab, (1, 1), generator=torch.Generator().manual_seed(1))
+    ref_state = oracle.make_state(large.cfg, 8, 16)
+    ref = oracle.decode_step(large.cfg, large.ow, ids8, torch.zeros(8, 1, dtype=torch.int64), ref_state)
+    small.step(ids1, torch.zeros(1, 1, dtype=torch.int64))
+    logits = large.step(ids8, torch.zeros(8, 1, dtype=torch.int64))
+    assert logits_close(logits, ref)[0]
+    small.step(ids1, torch.ones(1, 1, dtype=torch.int64))
