@@ -4,8 +4,20 @@
  * The Python host (megabake_b200.planner) turns one captured decoder invocation into a
  * table of fixed-size phase records plus a table of device addresses ("slots") and hands
  * both to this library.  One call of mb_plan_launch() is one cooperative persistent
- * kernel launch that executes every phase in order, separated by grid barriers where a
- * record asks for one.
+ * kernel launch that executes every phase in order.  Phases hand their activations to one
+ * another either through flagged cells (below) that the consumers poll -- no barrier at all --
+ * or, where a record asks for one, across a grid barrier.
+ *
+ * Flagged cells.  An activation tensor [rows, N] of bf16 that one phase produces and a later
+ * phase of the same launch consumes can be kept as [rows, N / 2] 64-bit cells: two bf16 values
+ * in the low word, a 32-bit sequence number in the high word (launch epoch x phases + producing
+ * phase + 1), written with one 8-byte store.  A consumer loads the cells it needs and retries
+ * until the sequence number is the one it expects: data and "ready" arrive in one round trip
+ * through L2.  This is the per-region flag wait of the reference's event-counter scheduler
+ * (src/megabake/runtime.py:279-316) taken down to the single activation element.  A cell
+ * buffer may be overwritten at the earliest two phases after its last reader; the kernel checks
+ * that (a counter of CTAs that finished each phase) before every cell store.  Cell buffers
+ * belong to the plan's workspace and start zeroed.
  *
  * What each entry point replaces in the reference (paths relative to the reference
  * project root):
@@ -43,7 +55,7 @@
 extern "C" {
 #endif
 
-#define MB_ABI_VERSION 1
+#define MB_ABI_VERSION 2
 
 /* ---- return codes of the host API ------------------------------------------------ */
 enum mb_error {
@@ -64,7 +76,8 @@ enum mb_status_code {
     MB_ST_KV_OVERFLOW = 3,     /* valid_length + 1 > cache capacity                      */
     MB_ST_TOKEN_RANGE = 4,     /* an input id outside [0, vocab)                         */
     MB_ST_BAD_PHASE = 5,       /* unknown body id in the phase table                     */
-    MB_ST_TMEM = 6             /* tensor-memory allocation failed                        */
+    MB_ST_TMEM = 6,            /* tensor-memory allocation failed                        */
+    MB_ST_HANDOFF_TIMEOUT = 7  /* a flagged cell never showed the expected sequence number */
 };
 
 typedef struct mb_status {
@@ -99,8 +112,15 @@ enum mb_body {
 
 /* mb_phase.flags */
 #define MB_FLAG_BARRIER 1      /* grid barrier after the phase                            */
-#define MB_FLAG_BUMP_LENGTH 2  /* after that barrier CTA 0 adds 1 to the int32 at
-                                  slot[MB_AT_S_LEN] (attention phases only)                */
+#define MB_FLAG_BUMP_LENGTH 2  /* attention phases: when the launch has finished without a
+                                  fault, 1 is added to every valid length at
+                                  slot[MB_AT_S_LEN]                                         */
+
+/* bits of MB_GV_I_CELLS / MB_AT_I_CELLS: which tensors of the phase are flagged cells */
+#define MB_CELLS_X 1           /* activations in (GEMV x; attention q, k and v)            */
+#define MB_CELLS_OUT 2         /* every output segment                                     */
+#define MB_CELLS_RESIDUAL 4    /* the residual operand                                     */
+#define MB_CELLS_XSTORE 8      /* the copy of the gathered rows                            */
 
 /* GEMV / GEMM prologues (applied to the activation rows) */
 enum mb_prologue {
@@ -134,17 +154,22 @@ typedef struct mb_phase {
 #define MB_GV_I_ROWS 0     /* activation rows (batch), 1..8                               */
 #define MB_GV_I_K 1        /* reduction length, multiple of 16                            */
 #define MB_GV_I_NSEG 2     /* weight segments, 1..3                                       */
-#define MB_GV_I_N0 3       /* output features of segment 0 (1 and 2 follow)               */
+#define MB_GV_I_N0 3       /* output features of segment 0 (1 and 2 follow), each even    */
 #define MB_GV_I_NMAT 6     /* 1, or 2 for a paired gate/up phase (then NSEG == 1)         */
 #define MB_GV_I_PROLOGUE 7
 #define MB_GV_I_EPILOGUE 8
-#define MB_GV_I_ROW_TILE 9 /* weight rows per pipeline stage: 8,16,32,64,128              */
+#define MB_GV_I_ROW_TILE 9 /* output rows per pipeline stage: 8 (always for a paired phase)
+                              or 16 (two 8-row tiles per stage: rows of at most 1,024
+                              elements, so that a stage still carries ~30 KB)              */
 #define MB_GV_I_K_CHUNK 10 /* reduction elements per pipeline stage, multiple of 16       */
 #define MB_GV_I_GATHER 11  /* 1: activation rows are gathered from an embedding table     */
 #define MB_GV_I_VOCAB 12   /* rows of that table (range check)                            */
 #define MB_GV_I_STORE_X 13 /* 1: CTA 0 also stores the un-normalised rows at S_XSTORE     */
-#define MB_GV_I_SPLIT_Q 14 /* filled by mb_plan_create: output rows per CTA (floor) ...      */
-#define MB_GV_I_SPLIT_R 15 /* ... and how many leading CTAs take one row more               */
+#define MB_GV_I_SPLIT_Q 14 /* filled by mb_plan_create: output row PAIRS per CTA (floor) ...  */
+#define MB_GV_I_SPLIT_R 15 /* ... and how many leading CTAs take one pair more              */
+#define MB_GV_I_CELLS 20   /* MB_CELLS_* bits                                             */
+#define MB_GV_I_X_SOURCE 21   /* phase index that wrote the x cells                        */
+#define MB_GV_I_RES_SOURCE 22 /* phase index that wrote the residual cells                 */
 /* floats */
 #define MB_GV_F_EPS 0
 #define MB_GV_F_EMBED_SCALE 1 /* 0 = none; else gathered rows are bf16(row * scale)       */
@@ -171,6 +196,11 @@ typedef struct mb_phase {
 #define MB_AT_I_EXACT_KEYS 8 /* contexts up to this many keys (<= 128, 0 = never) use the
                                 softmax that rounds normalised probabilities to bf16
                                 like the eager operator                                */
+#define MB_AT_I_CELLS 9      /* MB_CELLS_X: q, k and v are cells; MB_CELLS_OUT: out is      */
+#define MB_AT_I_QKV_SOURCE 10 /* phase index that wrote the q, k and v cells               */
+#define MB_AT_I_LEN_COUNT 11 /* valid lengths at MB_AT_S_LEN: 1 (shared by the batch; 0 means
+                                1) or batch (one per row: rows may hold different numbers of
+                                keys)                                                     */
 #define MB_AT_F_SCALE 0      /* head_dim ** -0.5, applied in fp32                          */
 #define MB_AT_F_ROPE_SCALE 1 /* attention_scaling multiplied into cos/sin                  */
 #define MB_AT_F_Q_SCALE 2    /* 0 or 1 = none; else q = bf16(q * this) after RoPE          */
@@ -179,7 +209,7 @@ typedef struct mb_phase {
 #define MB_AT_S_V 2
 #define MB_AT_S_KCACHE 3     /* [B, capacity, Hkv, D] bf16                                 */
 #define MB_AT_S_VCACHE 4
-#define MB_AT_S_LEN 5        /* int32 [1]                                                  */
+#define MB_AT_S_LEN 5        /* int32 [1] or [batch] (MB_AT_I_LEN_COUNT)                    */
 #define MB_AT_S_POS 6        /* int64 [B]                                                  */
 #define MB_AT_S_INVFREQ 7    /* [D/2]                                                      */
 #define MB_AT_S_OUT 8        /* [B, Hq*D] bf16                                             */
@@ -264,7 +294,10 @@ typedef struct mb_plan_desc {
     uint32_t stage_bytes;     /* decode: bytes of one weight-ring stage, a multiple of 1024 up
                                  to mb_stage_bytes(); 0 = mb_stage_bytes().  Small stages give
                                  a deeper ring when the reduction length is short            */
-    uint32_t reserved[3];
+    uint32_t wait_limit_ms;   /* bound of every device-side wait (hand-off cells, pipeline
+                                 stages, grid barrier) in milliseconds; 0 = 2000.  When a wait
+                                 runs out the kernel records a status, drains and returns   */
+    uint32_t reserved[2];
 } mb_plan_desc;
 
 typedef struct mb_plan_info {
