@@ -116,11 +116,22 @@ enum mb_body {
                                   fault, 1 is added to every valid length at
                                   slot[MB_AT_S_LEN]                                         */
 
+#define MB_FLAG_FENCE 4        /* the phase's results are plain memory that a later phase reads
+                                  after MB_CELLS_X_WAIT: every CTA makes its stores visible
+                                  (a gpu-scope fence) before it reports the phase finished   */
+
 /* bits of MB_GV_I_CELLS / MB_AT_I_CELLS: which tensors of the phase are flagged cells */
 #define MB_CELLS_X 1           /* activations in (GEMV x; attention q, k and v)            */
 #define MB_CELLS_OUT 2         /* every output segment                                     */
 #define MB_CELLS_RESIDUAL 4    /* the residual operand                                     */
 #define MB_CELLS_XSTORE 8      /* the copy of the gathered rows                            */
+#define MB_CELLS_X_WAIT 16     /* GEMV: before x is read, wait until every CTA has reported
+                                  phase MB_GV_I_X_SOURCE finished (one thread polls one
+                                  counter: thousands of threads polling their cells would
+                                  queue up in front of the very stores they wait for).  With
+                                  cell x it is a hint -- the sequence numbers still decide;
+                                  with plain x it is the synchronisation, and the producing
+                                  phase must carry MB_FLAG_FENCE                              */
 
 /* GEMV / GEMM prologues (applied to the activation rows) */
 enum mb_prologue {

@@ -64,6 +64,7 @@ struct mb_plan {
     int stages = 0;
     int stage_bytes = 0;
     int barriers = 0;
+    unsigned int wait_limit_us = 2000000u;
     mb::PhaseEntry* d_entries = nullptr;
     mb::Control* d_ctl = nullptr;
     unsigned long long trace = 0;
@@ -102,10 +103,27 @@ int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     if (nseg < 1 || nseg > 3) return MB_ERR_INVALID;
     if (nmat != 1 && nmat != 2) return MB_ERR_INVALID;
     if (nmat == 2 && nseg != 1) return MB_ERR_INVALID;
-    if (rt != mb::decode_row_tile()) return MB_ERR_INVALID;
+    // a stage holds one 8-row tile, or two: the gate and up tiles of a paired phase, or 16
+    // consecutive rows of a plain one
+    if (rt != mb::decode_row_tile() && !(nmat == 1 && rt == 2 * mb::decode_row_tile()))
+        return MB_ERR_INVALID;
     if (kc < 32 || kc % 32 != 0 || kc > K) return MB_ERR_INVALID;
     if (static_cast<long long>(rt) * nmat * (kc * 2 + mb::decode_row_pad()) > plan_stage_bytes(d))
         return MB_ERR_RESOURCE;
+    const int cells = P.i[MB_GV_I_CELLS];
+    if (cells & ~(MB_CELLS_X | MB_CELLS_OUT | MB_CELLS_RESIDUAL | MB_CELLS_XSTORE | MB_CELLS_X_WAIT))
+        return MB_ERR_INVALID;
+    if ((cells & MB_CELLS_X_WAIT) &&
+        (P.i[MB_GV_I_X_SOURCE] < 0 || static_cast<unsigned int>(P.i[MB_GV_I_X_SOURCE]) >= d->n_phases))
+        return MB_ERR_INVALID;
+    if ((cells & MB_CELLS_X) && (P.i[MB_GV_I_GATHER] || K % 4 != 0)) return MB_ERR_INVALID;
+    if ((cells & MB_CELLS_X) &&
+        (P.i[MB_GV_I_X_SOURCE] < 0 || static_cast<unsigned int>(P.i[MB_GV_I_X_SOURCE]) >= d->n_phases))
+        return MB_ERR_INVALID;
+    if ((cells & MB_CELLS_RESIDUAL) &&
+        (P.i[MB_GV_I_RES_SOURCE] < 0 ||
+         static_cast<unsigned int>(P.i[MB_GV_I_RES_SOURCE]) >= d->n_phases))
+        return MB_ERR_INVALID;
     // activation rows, plus one staged row of norm weights when the phase normalises
     const long long staged_rows = rows + (P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE ? 1 : 0);
     if (staged_rows * (K + 32) * 2 > d->activation_bytes) return MB_ERR_RESOURCE;
@@ -114,7 +132,9 @@ int validate_gemv(const mb_plan_desc* d, const mb_phase& P) {
     const bool paired_epi = epi == MB_EPI_SILU_MUL || epi == MB_EPI_GELU_TANH_MUL;
     if (paired_epi != (nmat == 2)) return MB_ERR_INVALID;
     for (int s = 0; s < nseg; ++s) {
-        if (P.i[MB_GV_I_N0 + s] < 1) return MB_ERR_INVALID;
+        if (P.i[MB_GV_I_N0 + s] < 2) return MB_ERR_INVALID;
+        // results are stored as pairs of neighbouring rows (one 4-byte store or one cell)
+        if (P.i[MB_GV_I_N0 + s] % 2 != 0) return MB_ERR_UNSUPPORTED;
         if (check_slot(d, P.slot[MB_GV_S_W0 + s], true)) return MB_ERR_INVALID;
         if (check_slot(d, P.slot[MB_GV_S_OUT0 + s], true)) return MB_ERR_INVALID;
         if (check_slot(d, P.slot[MB_GV_S_BIAS0 + s], false)) return MB_ERR_INVALID;
@@ -148,7 +168,14 @@ int validate_attention(const mb_plan_desc* d, const mb_phase& P) {
         return MB_ERR_RESOURCE;
     for (int s = MB_AT_S_Q; s <= MB_AT_S_COUNTER; ++s)
         if (check_slot(d, P.slot[s], true)) return MB_ERR_INVALID;
-    if ((P.flags & MB_FLAG_BUMP_LENGTH) && !(P.flags & MB_FLAG_BARRIER)) return MB_ERR_INVALID;
+    const int cells = P.i[MB_AT_I_CELLS];
+    if (cells & ~(MB_CELLS_X | MB_CELLS_OUT)) return MB_ERR_INVALID;
+    if ((cells & MB_CELLS_X) &&
+        (P.i[MB_AT_I_QKV_SOURCE] < 0 ||
+         static_cast<unsigned int>(P.i[MB_AT_I_QKV_SOURCE]) >= d->n_phases))
+        return MB_ERR_INVALID;
+    const int lengths = P.i[MB_AT_I_LEN_COUNT];
+    if (lengths != 0 && lengths != 1 && lengths != B) return MB_ERR_INVALID;
     return MB_OK;
 }
 
@@ -219,6 +246,7 @@ const char* mb_status_string(int status_code) {
         case MB_ST_TOKEN_RANGE: return "token id outside the embedding table";
         case MB_ST_BAD_PHASE: return "unknown body in the phase table";
         case MB_ST_TMEM: return "tensor memory allocation failed";
+        case MB_ST_HANDOFF_TIMEOUT: return "an activation hand-off wait timed out";
         default: return "unknown status";
     }
 }
@@ -298,10 +326,11 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     for (mb_phase& P : plan->phases) {
         if (P.body != MB_BODY_GEMV) continue;
         // balanced split of the output rows over the CTAs, so the kernel needs no division
+        // (in pairs of rows: a lane's two neighbouring results are stored together)
         int total = 0;
         for (int s = 0; s < P.i[MB_GV_I_NSEG]; ++s) total += P.i[MB_GV_I_N0 + s];
-        P.i[MB_GV_I_SPLIT_Q] = total / ctas;
-        P.i[MB_GV_I_SPLIT_R] = total % ctas;
+        P.i[MB_GV_I_SPLIT_Q] = (total / 2) / ctas;
+        P.i[MB_GV_I_SPLIT_R] = (total / 2) % ctas;
     }
     plan->slots.assign(desc->n_slots, 0ull);
     plan->n_dynamic = desc->n_dynamic;
@@ -313,6 +342,8 @@ int mb_plan_create(const mb_plan_desc* desc, mb_plan** out) {
     plan->stages = stages;
     plan->stage_bytes = stage;
     plan->barriers = barriers;
+    if (desc->wait_limit_ms != 0)
+        plan->wait_limit_us = desc->wait_limit_ms > 4000000u ? 4000000000u : desc->wait_limit_ms * 1000u;
 
     cudaError_t err = cudaMalloc(&plan->d_entries, sizeof(mb::PhaseEntry) * desc->n_phases);
     if (err == cudaSuccess) err = cudaMalloc(&plan->d_ctl, sizeof(mb::Control));
@@ -409,6 +440,7 @@ int mb_plan_launch(mb_plan* plan, const uint64_t* dynamic_addresses, size_t n, v
     params.stages = plan->stages;
     params.stage_bytes = plan->stage_bytes;
     params.activation_bytes = static_cast<int>(plan->activation_bytes);
+    params.wait_limit_us = plan->wait_limit_us;
     DeviceGuard guard(plan->device);
     if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
     MB_CUDA(mb::decode_launch(params, plan->ctas, plan->smem_bytes,
@@ -446,7 +478,13 @@ int mb_plan_reset(mb_plan* plan) {
     DeviceGuard guard(plan->device);
     if (guard.error != cudaSuccess) return cuda_fail(guard.error, "cudaSetDevice");
     MB_CUDA(cudaDeviceSynchronize());
+    // Everything starts over except the epoch, which moves on: hand-off cells written by the
+    // abandoned launch must never look like cells of the next one.
+    unsigned int epoch = 0;
+    MB_CUDA(cudaMemcpy(&epoch, &plan->d_ctl->epoch, sizeof(epoch), cudaMemcpyDeviceToHost));
+    epoch += 1;
     MB_CUDA(cudaMemset(plan->d_ctl, 0, sizeof(mb::Control)));
+    MB_CUDA(cudaMemcpy(&plan->d_ctl->epoch, &epoch, sizeof(epoch), cudaMemcpyHostToDevice));
     return MB_OK;
 }
 

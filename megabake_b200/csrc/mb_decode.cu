@@ -1,5 +1,7 @@
 // Decode megakernel: one cooperative persistent launch runs every phase of a one-token
-// decoder step.  Thread layout per CTA (one CTA per SM):
+// decoder step.  Phases hand activations to one another through flagged cells (two bf16 values
+// and a sequence number per 8-byte store, polled by the consumers), so that a layer needs no
+// grid barrier; a record may still ask for one.  Thread layout per CTA (one CTA per SM):
 //   warps 0..7   consumers: activation prologues (RMSNorm, embedding gather), the skinny
 //                GEMM inner loop on mma.sync with fp32 accumulation, epilogues, decode
 //                attention, and the grid barriers between barrier intervals
@@ -29,7 +31,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxStages = 16;
-constexpr int kRowTile = 8;          // weight rows per stage = one n8 MMA tile
+constexpr int kRowTile = 8;          // weight rows of one n8 MMA tile; a stage holds one or two
 constexpr int kRowPad = 64;          // bytes added to each staged row: with row lengths that are
                                      // multiples of 128 B this makes 16-byte fragment loads of
                                      // two neighbouring rows hit disjoint banks
@@ -53,11 +55,15 @@ __device__ __forceinline__ void trace_stamp(const KernelParams& p, int ph, int e
 struct SharedCtl {
     unsigned long long full[kMaxStages];
     unsigned long long empty[kMaxStages];
-    unsigned long long act_full;     // the activation rows of the current GEMV phase have landed
+    unsigned long long act_full;     // bulk copies of the current GEMV phase's prologue have landed
+    unsigned long long limit_ns;     // bound of every wait of this launch
     volatile int abort_flag;
     volatile unsigned int issued;    // stages the producer armed
     int bcast[4];                    // small broadcasts (attention chunking, arrival order)
     volatile int verdict;            // thread 0's go / drain decision at a barrier
+    unsigned int tag_base;           // cells of phase q carry tag_base + q + 1 in this launch
+    unsigned int calls;              // launches completed before this one
+    __align__(16) unsigned int guard[4];  // a counter of Control::finished, fetched asynchronously
     float red[kConsumerWarps][8];    // per-warp partials of the activation prologue
     __align__(16) PhaseEntry entry[2];  // current / next phase record with resolved addresses
     __align__(16) PhaseEntry producer_entry;  // the producer warp's own copy of its phase
@@ -90,16 +96,95 @@ __device__ __forceinline__ void patch_dynamic(const KernelParams& p, PhaseEntry*
     if (lane < MB_PHASE_SLOTS) e->addr[lane] = resolve_dynamic(p, e->addr[lane]);
 }
 
+// ---------------------------------------------------------------------------------------
+// Waiting for flagged cells.  The fast path (the cell already carries the expected sequence
+// number) is inline at the call sites; these are the retry loops.  A wait gives up when the
+// launch's limit has run out (status MB_ST_HANDOFF_TIMEOUT) or when this CTA or any other has
+// recorded a fault; the caller goes on with whatever it has and the CTA drains at the end of
+// the phase.
+// ---------------------------------------------------------------------------------------
+__device__ __noinline__ bool wait_gave_up(const KernelParams& p, SharedCtl* sc, int ph,
+                                          unsigned long long start) {
+    if (sc->abort_flag) return true;
+    if (peek_status(p.ctl) != 0) {
+        sc->abort_flag = 1;
+        return true;
+    }
+    if (global_timer_ns() - start > sc->limit_ns) {
+        record_status(p.ctl, MB_ST_HANDOFF_TIMEOUT, ph, static_cast<int>(blockIdx.x));
+        sc->abort_flag = 1;
+        return true;
+    }
+    return false;
+}
+
+__device__ __noinline__ void cell_pair_wait(const void* src, unsigned int tag,
+                                            unsigned long long& a, unsigned long long& b,
+                                            const KernelParams& p, SharedCtl* sc, int ph) {
+    const unsigned long long start = global_timer_ns();
+    for (unsigned int tries = 1;; ++tries) {
+        __nanosleep(32);
+        ld_cell_pair(src, a, b);
+        if (cell_tag(a) == tag && cell_tag(b) == tag) return;
+        if ((tries & 63u) == 0u && wait_gave_up(p, sc, ph, start)) return;
+    }
+}
+
+__device__ __noinline__ unsigned long long cell_wait(const void* src, unsigned int tag,
+                                                     const KernelParams& p, SharedCtl* sc,
+                                                     int ph) {
+    const unsigned long long start = global_timer_ns();
+    for (unsigned int tries = 1;; ++tries) {
+        __nanosleep(32);
+        const unsigned long long v = ld_cell(src);
+        if (cell_tag(v) == tag) return v;
+        if ((tries & 63u) == 0u && wait_gave_up(p, sc, ph, start)) return v;
+    }
+}
+
+// Lock-step within two phases.  A cell buffer is rewritten at the earliest three phases after
+// its last reader (the planner's rule).  So a CTA may enter phase q + 1 only when every CTA has
+// finished phase q - 2 ... the kernel asks for a little more, q - 2 at the END of phase q:
+// Control::finished[q % 4] counts the CTAs that finished phase q, and thread 0 of every CTA
+// checks the counter of phase q - 2 before it reports phase q finished.  `seen` is a value of
+// that counter fetched while the phase ran; in the steady state it is already large enough and
+// nothing waits.
+__device__ __forceinline__ unsigned int finished_target(const KernelParams& p, const SharedCtl* sc,
+                                                        int q) {
+    const unsigned int slot = static_cast<unsigned int>(q) & 3u;
+    // phases of one launch that count on this slot, and how many of them up to phase q
+    const unsigned int per_launch = (static_cast<unsigned int>(p.n_phases) + 3u - slot) >> 2;
+    return gridDim.x * (sc->calls * per_launch + (static_cast<unsigned int>(q) >> 2) + 1u);
+}
+
+// One thread: wait until every CTA has reported phase `q` finished.  The load is an acquire, so
+// what those CTAs stored before a fenced report is visible to this thread afterwards (and,
+// through a CTA barrier, to its CTA).
+__device__ __noinline__ void finished_wait(const KernelParams& p, SharedCtl* sc, int ph, int q) {
+    const unsigned int target = finished_target(p, sc, q);
+    const unsigned int* counter = &p.ctl->finished[q & 3].count;
+    const unsigned long long start = global_timer_ns();
+    for (unsigned int tries = 1;; ++tries) {
+        unsigned int seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+        if (static_cast<int>(seen - target) >= 0) return;
+        if ((tries & 63u) == 0u && wait_gave_up(p, sc, ph, start)) return;
+        __nanosleep(40);
+    }
+}
+
 // Geometry of one GEMV phase for one CTA; producer and consumers derive it identically.
-// A CTA owns weight rows [r0, r1) of the phase's (virtually concatenated) output rows and
-// streams them as row blocks of 8, each cut into n_chunks stages of k_chunk elements.
+// A CTA owns output rows [r0, r1) of the phase's (virtually concatenated) output rows -- whole
+// pairs of rows, so that a lane's two neighbouring results always form one cell -- and streams
+// their weight rows as blocks of `row_tile` rows (8, or 16 = two MMA tiles), each cut into
+// n_chunks stages of k_chunk elements.
 struct GemvGeom {
     int rows, K, nseg, nmat, n[3], ntotal;
-    int k_chunk, n_chunks, pitch;
+    int k_chunk, n_chunks, pitch, row_tile;
     int r0, r1, n_blocks;
 };
 
-__device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, int ctas) {
+__device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta) {
     GemvGeom g;
     g.rows = P.i[MB_GV_I_ROWS];
     g.K = P.i[MB_GV_I_K];
@@ -112,12 +197,13 @@ __device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, in
     g.k_chunk = P.i[MB_GV_I_K_CHUNK];
     g.n_chunks = (g.K + g.k_chunk - 1) / g.k_chunk;  // small operands: cheap
     g.pitch = g.k_chunk * 2 + kRowPad;
-    // balanced split precomputed by the host: the first `rem` CTAs own one row more
+    g.row_tile = P.i[MB_GV_I_ROW_TILE];
+    // balanced split precomputed by the host, in pairs of rows: the first `rem` CTAs own one
+    // pair more
     const int q = P.i[MB_GV_I_SPLIT_Q], rem = P.i[MB_GV_I_SPLIT_R];
-    (void)ctas;
-    g.r0 = cta * q + min(cta, rem);
-    g.r1 = g.r0 + q + (cta < rem ? 1 : 0);
-    g.n_blocks = (g.r1 - g.r0 + kRowTile - 1) / kRowTile;
+    g.r0 = 2 * (cta * q + min(cta, rem));
+    g.r1 = g.r0 + 2 * (q + (cta < rem ? 1 : 0));
+    g.n_blocks = (g.r1 - g.r0 + g.row_tile - 1) / g.row_tile;
     return g;
 }
 
@@ -127,7 +213,7 @@ __device__ __forceinline__ GemvGeom gemv_geometry(const mb_phase& P, int cta, in
 // ---------------------------------------------------------------------------------------
 __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc, char* ring,
                                            int lane) {
-    const int cta = blockIdx.x, ctas = gridDim.x;
+    const int cta = blockIdx.x;
     unsigned int it = 0;
     // The producer runs phases ahead of the consumers, so it would meet every phase entry
     // cold in DRAM and chase its fields one dependent load at a time.  Instead: pull the whole
@@ -163,7 +249,7 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
             continue;
         }
         if (E->rec.body != MB_BODY_GEMV) continue;
-        const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
+        const GemvGeom g = gemv_geometry(E->rec, cta);
         if (E->rec.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE) {
             // norm weights are read by every CTA right after the barrier: have them in L2
             const char* nw = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
@@ -192,8 +278,8 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
         int stage = static_cast<int>(it % static_cast<unsigned int>(p.stages));
         unsigned int wraps = it / static_cast<unsigned int>(p.stages);
         for (int blk = 0; blk < g.n_blocks; ++blk) {
-            const int block0 = g.r0 + blk * kRowTile;
-            const int nrows = min(kRowTile, g.r1 - block0);
+            const int block0 = g.r0 + blk * g.row_tile;
+            const int nrows = min(g.row_tile, g.r1 - block0);
             // this lane's copy: matrix m, row r of the block (at most 16 copies per stage)
             const int m = lane / nrows, r = lane - m * nrows;
             const bool mine = lane < nrows * g.nmat;
@@ -216,7 +302,7 @@ __device__ __noinline__ void producer_loop(const KernelParams& p, SharedCtl* sc,
             }
             for (int c = 0; c < g.n_chunks; ++c) {
                 const unsigned int parity = (wraps & 1u) ^ 1u;
-                if (!mbar_wait_bounded(&sc->empty[stage], parity, &sc->abort_flag)) {
+                if (!mbar_wait_bounded(&sc->empty[stage], parity, &sc->abort_flag, sc->limit_ns)) {
                     if (lane == 0 && !sc->abort_flag) {
                         record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
                         sc->abort_flag = 1;
@@ -277,50 +363,98 @@ __device__ __forceinline__ void cp_async16_or_zero(void* dst_smem, const void* s
                  "l"(src_gmem), "r"(valid ? 16 : 0)
                  : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+
+// Does this GEMV phase arm the activation mbarrier?  Plain activations come by bulk copy (one
+// per row); so do the norm weights (one more row).  Cell activations with no norm arm nothing.
+__device__ __forceinline__ bool activation_arms(const mb_phase& P) {
+    return !(P.i[MB_GV_I_CELLS] & MB_CELLS_X) || P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE;
 }
 
-// One global round trip: every activation row (and the norm weight vector, staged as one
-// extra row) is copied global -> shared by ONE bulk copy per row, issued by a single warp and
-// counted on an mbarrier; scaling, sums of squares and the normalisation then run out of shared
-// memory.  (16-byte cp.async copies by all threads moved the same bytes, but issuing a few
-// hundred of them stalled the issuing warps for about a microsecond on the load/store unit's
-// miss tracking; the bulk-copy engine takes the rows in one instruction.)
-// Part 1 (activation_issue) only starts the copies; part 2 (activation_finish) waits for them
-// and normalises.  The GEMV body runs its own address arithmetic and epilogue-operand loads
-// between the two, under the latency of the copies.
-// `round` counts the GEMV phases this CTA has run: the parity of the activation barrier.
+// Part 1 (activation_issue) starts the bulk copies global -> shared of whatever the phase takes
+// from plain memory: every activation row when they are plain bf16 (one copy per row: the
+// bulk-copy engine takes a row in one instruction, where 16-byte cp.async copies by all threads
+// stalled the issuing warps for about a microsecond on the load/store unit's miss tracking), and
+// the norm weight vector, staged as one extra row.  Part 2 waits for them (activation_finish for
+// plain rows, activation_cells for rows that arrive as flagged cells) and normalises.
+// `round` counts the phases of this CTA that armed the barrier: its parity.
 __device__ __noinline__ void activation_issue(const KernelParams& p, const PhaseEntry* E, int ph,
                                               SharedCtl* sc, __nv_bfloat16* xs, int tid) {
     if (tid >= 32) return;
     const mb_phase& P = E->rec;
+    const int cells = P.i[MB_GV_I_CELLS];
+    const bool waits = (cells & MB_CELLS_X_WAIT) != 0;  // x was written earlier in this launch
     const int rows = P.i[MB_GV_I_ROWS];
     const int K = P.i[MB_GV_I_K];
     const int xpitch = K + 32;
     const bool gather = P.i[MB_GV_I_GATHER] != 0;
     const bool normed = P.i[MB_GV_I_PROLOGUE] != MB_PRO_NONE;
+    const bool plain = !(cells & MB_CELLS_X);
+    const unsigned int row_bytes = static_cast<unsigned int>(K) * 2u;
+    const int lane = tid;
+    if (sc->abort_flag) return;  // a faulted CTA arms nothing (part 2 will not wait)
+    if (activation_arms(P)) {
+        if (lane == 0) {
+            // The destination was last touched by ordinary loads and stores: hand it to the
+            // async proxy.  All bytes of the phase are expected on one barrier phase; the norm
+            // weights (they depend on nothing in this launch) are requested at once, the rows
+            // below when their producers are done.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_expect_tx(&sc->act_full,
+                                  row_bytes * static_cast<unsigned int>((plain ? rows : 0) + (normed ? 1 : 0)));
+            if (normed)  // the norm weights travel as row number `rows`
+                bulk_copy_g2s(xs + static_cast<size_t>(rows) * xpitch,
+                              reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W)),
+                              row_bytes, &sc->act_full);
+        }
+    }
+    if (waits) {
+        // lane 0 polls one counter until every CTA has reported the producing phase finished
+        if (lane == 0) finished_wait(p, sc, ph, P.i[MB_GV_I_X_SOURCE]);
+        __syncwarp();
+        if (sc->abort_flag) return;
+    }
+    if (!plain) return;
     const char* xbase = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X));
     const long long* ids =
         gather ? reinterpret_cast<const long long*>(entry_address(p, E, MB_GV_S_IDS)) : nullptr;
-    const unsigned int row_bytes = static_cast<unsigned int>(K) * 2u;
-    const int lane = tid;
     bool bad_token = false;
     const char* src = nullptr;
     if (lane < rows) src = activation_row(E, xbase, ids, lane, K, &bad_token);
-    if (lane == rows && normed)  // the norm weights travel as row number `rows`
-        src = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_NORM_W));
-    if (sc->abort_flag) return;  // a faulted CTA arms nothing (activation_finish will not wait)
-    if (lane == 0) {
-        // the rows' shared memory was last touched by ordinary loads and stores
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_expect_tx(&sc->act_full, row_bytes * static_cast<unsigned int>(rows + (normed ? 1 : 0)));
-    }
+    // Rows written with ordinary stores by other CTAs earlier in this launch were made visible
+    // by their fence and this warp's acquire; the bulk copies below read them through the async
+    // proxy, which is ordered after that by this fence.
+    if (waits) asm volatile("fence.proxy.async.global;" ::: "memory");
     __syncwarp();
     if (src != nullptr)
         bulk_copy_g2s(xs + static_cast<size_t>(lane) * xpitch, src, row_bytes, &sc->act_full);
     if (__any_sync(0xffffffffu, bad_token) && lane == 0)
         record_status(p.ctl, MB_ST_TOKEN_RANGE, ph, blockIdx.x);
+}
+
+__device__ __forceinline__ void wait_activation_copies(const KernelParams& p, int ph, SharedCtl* sc,
+                                                       unsigned int round) {
+    if (!mbar_wait_bounded(&sc->act_full, round & 1u, &sc->abort_flag, sc->limit_ns)) {
+        if (!sc->abort_flag) {
+            record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, blockIdx.x);
+            sc->abort_flag = 1;
+        }
+        // fall through: the rows are garbage, the CTA drains at the end of the phase
+    }
+}
+
+// Eight raw bf16 values of the gathered (un-normalised) rows go to the residual stream, as
+// plain bf16 or as four cells.
+__device__ __forceinline__ void store_gathered(char* store, bool cells, unsigned int tag,
+                                               size_t element, uint4 raw) {
+    if (cells) {
+        char* c = store + element * 4;
+        st_cell(c, raw.x, tag);
+        st_cell(c + 8, raw.y, tag);
+        st_cell(c + 16, raw.z, tag);
+        st_cell(c + 24, raw.w, tag);
+    } else {
+        *reinterpret_cast<uint4*>(store + element * 2) = raw;
+    }
 }
 
 __device__ __noinline__ void activation_finish(const KernelParams& p, const PhaseEntry* E, int ph,
@@ -335,16 +469,12 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
     const float embed_scale = P.f[MB_GV_F_EMBED_SCALE];
     const bool scaled = gather && embed_scale != 0.f;
     const bool store_x = gather && P.i[MB_GV_I_STORE_X] && blockIdx.x == 0;
+    const bool store_cells = (P.i[MB_GV_I_CELLS] & MB_CELLS_XSTORE) != 0;
+    const unsigned int tag = sc->tag_base + static_cast<unsigned int>(ph) + 1u;
     const int warp = tid >> 5, lane = tid & 31;
     const int vec_per_row = K / 8;  // 16-byte vectors
     const __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;  // staged norm weights
-    if (!mbar_wait_bounded(&sc->act_full, round & 1u, &sc->abort_flag)) {
-        if (!sc->abort_flag) {
-            record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, blockIdx.x);
-            sc->abort_flag = 1;
-        }
-        // fall through: the rows are garbage, the CTA drains at the next barrier
-    }
+    wait_activation_copies(p, ph, sc, round);
 
     if (rows >= 2 && (pro != MB_PRO_NONE || gather)) {
         // one warp per row: sum of squares and normalisation of a row need no CTA barrier
@@ -363,7 +493,7 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
                 }
                 ss += sum_squares(raw);
                 if (store_x)
-                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) = raw;
+                    store_gathered(store, store_cells, tag, static_cast<size_t>(r) * K + v * 8, raw);
             }
             if (pro != MB_PRO_NONE) {
 #pragma unroll
@@ -395,7 +525,7 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
                 }
                 ss += sum_squares(raw);
                 if (store_x)  // the residual stream needs the un-normalised rows
-                    *reinterpret_cast<uint4*>(store + (static_cast<size_t>(r) * K + v * 8) * 2) = raw;
+                    store_gathered(store, store_cells, tag, static_cast<size_t>(r) * K + v * 8, raw);
             }
             if (pro != MB_PRO_NONE) {
 #pragma unroll
@@ -422,6 +552,103 @@ __device__ __noinline__ void activation_finish(const KernelParams& p, const Phas
     named_barrier(kBarConsumers, kConsumerThreads);
 }
 
+// Two packed pairs of bf16 values (four elements) through the RMSNorm.
+__device__ __forceinline__ uint2 normalise_quad(uint2 x, uint2 w, float inv, int kind) {
+    unsigned int xv[2] = {x.x, x.y};
+    const unsigned int wv[2] = {w.x, w.y};
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        float a = lo_bf16(xv[q]), b = hi_bf16(xv[q]);
+        const float wa = lo_bf16(wv[q]), wb = hi_bf16(wv[q]);
+        if (kind == MB_PRO_RMS_LLAMA) {
+            a = bf16_round(a * inv) * wa;
+            b = bf16_round(b * inv) * wb;
+        } else {
+            a = (a * inv) * (1.0f + wa);
+            b = (b * inv) * (1.0f + wb);
+        }
+        xv[q] = pack_bf16(a, b);
+    }
+    return make_uint2(xv[0], xv[1]);
+}
+
+// Activation rows that arrive as flagged cells, written by other CTAs earlier in this launch:
+// every thread loads its share of the cells (two per 16-byte load, four loads in flight) and
+// retries the ones that do not yet carry the producing phase's sequence number -- the wait for
+// the producers and the fetch of their data are one round trip through L2.  The values go to
+// shared memory as plain bf16 rows; sums of squares are gathered on the way.
+// A row is shared by `S` warps (8 for one row, 4 for two, 2 for up to four, else 1), each lane
+// works on the same quads in both passes, so RMSNorm needs a CTA barrier only when S > 1.
+__device__ __noinline__ void activation_cells(const KernelParams& p, const PhaseEntry* E, int ph,
+                                              SharedCtl* sc, __nv_bfloat16* xs, unsigned int round,
+                                              int tid) {
+    const mb_phase& P = E->rec;
+    const int rows = P.i[MB_GV_I_ROWS];
+    const int K = P.i[MB_GV_I_K];
+    const int xpitch = K + 32;
+    const int pro = P.i[MB_GV_I_PROLOGUE];
+    const unsigned int tag = sc->tag_base + static_cast<unsigned int>(P.i[MB_GV_I_X_SOURCE]) + 1u;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int quads = K / 4;  // 16-byte loads (two cells, four values) per row
+    const int S = rows >= 5 ? 1 : (rows >= 3 ? 2 : (rows == 2 ? 4 : 8));
+    const int r = warp / S, s = warp - r * S;
+    const bool works = r < rows;
+    const char* src = reinterpret_cast<const char*>(entry_address(p, E, MB_GV_S_X)) +
+                      static_cast<size_t>(r) * K * 4;
+    __nv_bfloat16* row = xs + static_cast<size_t>(r) * xpitch;
+    const int first = s * 32 + lane, step = 32 * S;
+    float ss = 0.f;
+    // warp 0 has waited for the producers in activation_issue; the others wait for warp 0
+    if (P.i[MB_GV_I_CELLS] & MB_CELLS_X_WAIT) named_barrier(kBarConsumers, kConsumerThreads);
+    if (works) {
+        constexpr int kInFlight = 8;
+        for (int j0 = first; j0 < quads; j0 += kInFlight * step) {
+            unsigned long long c[kInFlight][2];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const int j = j0 + u * step;
+                if (j < quads) ld_cell_pair(src + static_cast<size_t>(j) * 16, c[u][0], c[u][1]);
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const int j = j0 + u * step;
+                if (j < quads) {
+                    if (cell_tag(c[u][0]) != tag || cell_tag(c[u][1]) != tag)
+                        cell_pair_wait(src + static_cast<size_t>(j) * 16, tag, c[u][0], c[u][1], p,
+                                       sc, ph);
+                    const unsigned int lo = cell_data(c[u][0]), hi = cell_data(c[u][1]);
+                    const float a0 = lo_bf16(lo), a1 = hi_bf16(lo), a2 = lo_bf16(hi), a3 = hi_bf16(hi);
+                    ss += a0 * a0;
+                    ss += a1 * a1;
+                    ss += a2 * a2;
+                    ss += a3 * a3;
+                    *reinterpret_cast<uint2*>(row + 4 * j) = make_uint2(lo, hi);
+                }
+            }
+        }
+    }
+    if (pro != MB_PRO_NONE) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (S > 1) {
+            if (lane == 0) sc->red[warp][0] = ss;
+            named_barrier(kBarConsumers, kConsumerThreads);
+            ss = 0.f;
+            for (int w = 0; w < S; ++w) ss += sc->red[min(r, rows - 1) * S + w][0];
+        }
+        wait_activation_copies(p, ph, sc, round);  // the norm weights (row number `rows`)
+        if (works) {
+            const float inv = 1.0f / sqrtf(ss / static_cast<float>(K) + P.f[MB_GV_F_EPS]);
+            const __nv_bfloat16* wrow = xs + static_cast<size_t>(rows) * xpitch;
+            for (int j = first; j < quads; j += step) {
+                uint2* cell = reinterpret_cast<uint2*>(row + 4 * j);
+                *cell = normalise_quad(*cell, *reinterpret_cast<const uint2*>(wrow + 4 * j), inv, pro);
+            }
+        }
+    }
+    named_barrier(kBarConsumers, kConsumerThreads);
+}
+
 // ---------------------------------------------------------------------------------------
 // Consumer side of a GEMV phase.
 // ---------------------------------------------------------------------------------------
@@ -431,22 +658,33 @@ struct EpilogueCtx {
     const char* residual;
     int n[3];
     int epilogue;
+    bool out_cells, res_cells;
+    unsigned int tag, res_tag;
 };
 
-// Where one output element lives: segment lookup without dynamically indexed arrays (those
-// would be placed in local memory).
-struct OutputCell {
-    unsigned short* out;
-    const unsigned short* bias;
-    size_t index;
-    int local;
+// One lane's pair of neighbouring results: token `gid`, output rows v and v + 1 (v even, both in
+// the same segment because segment sizes are even).  Operands that come from global memory are
+// fetched before the reduction loop so that their latency hides behind it.
+struct PairIO {
+    char* out;             // address of the pair: a cell, or two bf16
+    const char* res;       // address of the residual pair (a cell, or two bf16)
+    unsigned long long residual;  // what was loaded from there
+    unsigned int bias;     // packed bf16 pair, 0 if absent
+    bool live;
 };
 
-__device__ __forceinline__ OutputCell locate_output(const EpilogueCtx& e, int token, int vrow) {
+__device__ __forceinline__ PairIO locate_pair(const EpilogueCtx& e, int token, int vrow, bool live) {
+    PairIO io;
+    io.live = live;
+    io.out = nullptr;
+    io.res = nullptr;
+    io.residual = 0ull;
+    io.bias = 0u;
+    if (!live) return io;
     int local = vrow, n = e.n[0];
     char* out = e.out[0];
     const char* bias = e.bias[0];
-    if (local >= e.n[0]) {
+    if (local >= e.n[0]) {  // segment lookup without dynamically indexed arrays
         local -= e.n[0];
         n = e.n[1];
         out = e.out[1];
@@ -458,78 +696,87 @@ __device__ __forceinline__ OutputCell locate_output(const EpilogueCtx& e, int to
             bias = e.bias[2];
         }
     }
-    OutputCell cell;
-    cell.out = reinterpret_cast<unsigned short*>(out);
-    cell.bias = reinterpret_cast<const unsigned short*>(bias);
-    cell.local = local;
-    cell.index = static_cast<size_t>(token) * n + local;
-    return cell;
+    const size_t index = static_cast<size_t>(token) * n + local;  // even
+    io.out = out + index * (e.out_cells ? 4 : 2);
+    if (bias != nullptr) io.bias = __ldg(reinterpret_cast<const unsigned int*>(bias + local * 2));
+    if (e.epilogue == MB_EPI_RESIDUAL) {
+        io.res = e.residual + index * (e.res_cells ? 4 : 2);
+        io.residual = e.res_cells ? ld_cell(io.res) : static_cast<unsigned long long>(ld_cg_u32(io.res));
+    }
+    return io;
 }
 
-// Operands of the epilogue that come from global memory, fetched before the reduction loop
-// so that their latency hides behind it.
-struct EpilogueOperands {
-    float bias, residual;
-};
-
-__device__ __forceinline__ EpilogueOperands fetch_epilogue(const EpilogueCtx& e,
-                                                           const OutputCell& cell) {
-    EpilogueOperands op;
-    op.bias = cell.bias != nullptr ? bf16_bits_to_float(__ldg(cell.bias + cell.local)) : 0.f;
-    op.residual = e.epilogue == MB_EPI_RESIDUAL
-                      ? bf16_bits_to_float(ld_cg_u16(
-                            reinterpret_cast<const unsigned short*>(e.residual) + cell.index))
-                      : 0.f;
-    return op;
-}
-
-__device__ __forceinline__ void store_output(const EpilogueCtx& e, const OutputCell& cell,
-                                             const EpilogueOperands& op, float acc,
-                                             float acc_pair) {
-    const float y = bf16_round(acc + op.bias);
-    float result;
+__device__ __forceinline__ void store_pair(const KernelParams& p, SharedCtl* sc, int ph,
+                                           const EpilogueCtx& e, PairIO& io, float acc0, float acc1,
+                                           float pair0, float pair1) {
+    const float y0 = bf16_round(acc0 + lo_bf16(io.bias));
+    const float y1 = bf16_round(acc1 + hi_bf16(io.bias));
+    float r0, r1;
     switch (e.epilogue) {
-        case MB_EPI_RESIDUAL:
-            result = op.residual + y;
+        case MB_EPI_RESIDUAL: {
+            if (e.res_cells && cell_tag(io.residual) != e.res_tag)
+                io.residual = cell_wait(io.res, e.res_tag, p, sc, ph);
+            const unsigned int res = cell_data(io.residual);
+            r0 = lo_bf16(res) + y0;
+            r1 = hi_bf16(res) + y1;
             break;
+        }
         case MB_EPI_SILU_MUL:
-            result = bf16_round(silu_f32(y)) * bf16_round(acc_pair);
+            r0 = bf16_round(silu_f32(y0)) * bf16_round(pair0);
+            r1 = bf16_round(silu_f32(y1)) * bf16_round(pair1);
             break;
         case MB_EPI_GELU_TANH_MUL:
-            result = bf16_round(gelu_tanh_f32(y)) * bf16_round(acc_pair);
+            r0 = bf16_round(gelu_tanh_f32(y0)) * bf16_round(pair0);
+            r1 = bf16_round(gelu_tanh_f32(y1)) * bf16_round(pair1);
             break;
         default:
-            result = y;
+            r0 = y0;
+            r1 = y1;
             break;
     }
-    cell.out[cell.index] = float_to_bf16_bits(result);
+    const unsigned int packed = pack_bf16(r0, r1);
+    if (e.out_cells)
+        st_cell(io.out, packed, e.tag);
+    else
+        *reinterpret_cast<unsigned int*>(io.out) = packed;
 }
 
 // All consumer warps work on every stage together, in ring order (so no warp is ever more
-// than one mbarrier phase behind the slot it waits on): a stage holds 8 weight rows x k_chunk
-// elements, its 32-element groups are dealt round-robin to the 8 warps.  A = activations
-// (row = token), B = weights (n = weight row); the reduction index is permuted identically in
-// both so that every lane reads 16 contiguous bytes per group.  Each warp parks its partial
-// sums of a row block in shared memory; once a group of row blocks is through, one CTA barrier
-// lets warp w add up the eight partials of block w and run that block's epilogue.  That is one
-// barrier pair per 8 (paired: 4) row blocks instead of a reduction per stage.
-template <int NMAT>
+// than one mbarrier phase behind the slot it waits on).  A stage holds SUBS tiles of 8 weight
+// rows x k_chunk elements: the gate and up rows of a paired phase (PAIRED), or 16 consecutive
+// output rows of a plain one (SUBS == 2, rows of at most 1,024 elements: more bytes per stage
+// and so more bytes in flight per SM), or 8 rows.  The 32-element groups of a stage are dealt
+// round-robin to the 8 warps.  A = activations (row = token), B = weights (n = weight row); the
+// reduction index is permuted identically in both so that every lane reads 16 contiguous bytes
+// per group.  Each warp parks its partial sums of a block in shared memory; once a group of
+// blocks is through, one CTA barrier lets warp w add up the eight partials of block w and run
+// that block's epilogue.  That is one barrier pair per 8 (SUBS == 2: 4) blocks instead of a
+// reduction per stage.
+template <int SUBS, bool PAIRED>
 __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntry* E, int ph,
-                                             SharedCtl* sc, const __nv_bfloat16* xs, float* red,
-                                             const char* ring, unsigned int& it,
-                                             unsigned int act_round, int tid) {
-    constexpr int NB = NMAT == 1 ? 8 : 4;  // row blocks per reduction group
-    constexpr int PV = 2 * NMAT;           // partial values per lane and block
-    const int cta = blockIdx.x, ctas = gridDim.x;
-    const GemvGeom g = gemv_geometry(E->rec, cta, ctas);
+                                          SharedCtl* sc, const __nv_bfloat16* xs, float* red,
+                                          const char* ring, unsigned int& it,
+                                          unsigned int act_round, int tid) {
+    static_assert(!PAIRED || SUBS == 2, "a paired phase stages two tiles");
+    constexpr int NB = SUBS == 1 ? 8 : 4;     // blocks per reduction group
+    constexpr int PV = 2 * SUBS;              // partial values per lane and block
+    constexpr int OUTS = PAIRED ? 1 : SUBS;   // result pairs per lane and block
+    constexpr int RT = 8 * OUTS;              // output rows per block
+    const int cta = blockIdx.x;
+    const GemvGeom g = gemv_geometry(E->rec, cta);
     trace_stamp(p, ph, 7, tid);
     const int warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tq = lane & 3;
     const int xpitch = g.K + 32;
     const __nv_bfloat16* xrow = xs + static_cast<size_t>(min(gid, g.rows - 1)) * xpitch + 8 * tq;
+    const int cells = E->rec.i[MB_GV_I_CELLS];
 
     EpilogueCtx e;
     e.epilogue = E->rec.i[MB_GV_I_EPILOGUE];
+    e.out_cells = (cells & MB_CELLS_OUT) != 0;
+    e.res_cells = (cells & MB_CELLS_RESIDUAL) != 0;
+    e.tag = sc->tag_base + static_cast<unsigned int>(ph) + 1u;
+    e.res_tag = sc->tag_base + static_cast<unsigned int>(E->rec.i[MB_GV_I_RES_SOURCE]) + 1u;
 #pragma unroll
     for (int s = 0; s < 3; ++s) {
         e.n[s] = g.n[s];
@@ -550,36 +797,34 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
     unsigned int wraps = it / static_cast<unsigned int>(p.stages);
     for (int group0 = 0; group0 < g.n_blocks; group0 += NB) {
         const int nb = min(NB, g.n_blocks - group0);
-        // The block this warp finalises, this lane's two output cells in it (token gid, rows
-        // v0 and v0 + 1) and their global epilogue operands: requested now, used after the
-        // reduction.
-        const int v0 = g.r0 + (group0 + warp) * kRowTile + 2 * tq;
-        const bool finalises = warp < nb && gid < g.rows;
-        const bool live0 = finalises && v0 < g.r1, live1 = finalises && v0 + 1 < g.r1;
-        OutputCell cell0 = {}, cell1 = {};
-        EpilogueOperands op0 = {0.f, 0.f}, op1 = {0.f, 0.f};
-        if (live0) {
-            cell0 = locate_output(e, gid, v0);
-            op0 = fetch_epilogue(e, cell0);
-        }
-        if (live1) {
-            cell1 = locate_output(e, gid, v0 + 1);
-            op1 = fetch_epilogue(e, cell1);
+        // The block this warp finalises, this lane's result pairs in it and their global
+        // epilogue operands: requested now, used after the reduction.
+        PairIO io[OUTS];
+#pragma unroll
+        for (int o = 0; o < OUTS; ++o) {
+            const int v = g.r0 + (group0 + warp) * RT + 8 * o + 2 * tq;
+            io[o] = locate_pair(e, gid, v, warp < nb && gid < g.rows && v < g.r1);
         }
 
         if (!staged) {
-            activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
+            if (cells & MB_CELLS_X)
+                activation_cells(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
+            else
+                activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
             staged = true;
         }
         for (int b = 0; b < nb; ++b) {
-            // two accumulator sets per matrix keep the MMA dependency chains short
-            float acc[NMAT][4][4];
+            // two accumulator sets per tile keep the MMA dependency chains short
+            float acc[SUBS][4][4];
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m)
+            for (int m = 0; m < SUBS; ++m)
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
 #pragma unroll
                     for (int q = 0; q < 4; ++q) acc[m][u][q] = 0.f;
+            // a plain 16-row block whose second tile is past the CTA's rows multiplies one tile
+            const bool both = PAIRED || SUBS == 1 ||
+                              g.r1 - (g.r0 + (group0 + b) * RT) > kRowTile;
 
             for (int c = 0; c < g.n_chunks; ++c) {
                 const int this_stage = stage;
@@ -594,7 +839,8 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                 // at the next CTA barrier.  It records the fault, and every warp then falls
                 // through the remaining loops without waiting or computing.
                 // (the bounded wait itself watches the CTA's abort flag while it spins)
-                if (dead || !mbar_wait_bounded(&sc->full[this_stage], parity, &sc->abort_flag)) {
+                if (dead || !mbar_wait_bounded(&sc->full[this_stage], parity, &sc->abort_flag,
+                                               sc->limit_ns)) {
                     if (!dead && !sc->abort_flag) {
                         record_status(p.ctl, MB_ST_PIPE_TIMEOUT, ph, cta);
                         sc->abort_flag = 1;
@@ -617,7 +863,8 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
                     const uint4 a2 = second ? *reinterpret_cast<const uint4*>(xk + 32 * grp2)
                                             : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
+                    for (int m = 0; m < SUBS; ++m) {
+                        if (m == 1 && !both) break;
                         const char* wm = wrow + static_cast<size_t>(m) * kRowTile * g.pitch;
                         const uint4 w = *reinterpret_cast<const uint4*>(wm + 64 * grp);
                         const uint4 w2 = second ? *reinterpret_cast<const uint4*>(wm + 64 * grp2)
@@ -633,7 +880,7 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
             }
             float* cell = red + (static_cast<size_t>(b * kConsumerWarps + warp) * 32 + lane) * PV;
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
+            for (int m = 0; m < SUBS; ++m) {
                 cell[2 * m] = (acc[m][0][0] + acc[m][1][0]) + (acc[m][2][0] + acc[m][3][0]);
                 cell[2 * m + 1] = (acc[m][0][1] + acc[m][1][1]) + (acc[m][2][1] + acc[m][3][1]);
             }
@@ -651,13 +898,28 @@ __device__ __noinline__ bool gemv_consume(const KernelParams& p, const PhaseEntr
 #pragma unroll
                 for (int v = 0; v < PV; ++v) total[v] += cell[v];
             }
-            if (live0) store_output(e, cell0, op0, total[0], NMAT > 1 ? total[2] : 0.f);
-            if (live1) store_output(e, cell1, op1, total[1], NMAT > 1 ? total[3] : 0.f);
+            if (PAIRED) {
+                if (io[0].live) store_pair(p, sc, ph, e, io[0], total[0], total[1], total[2], total[3]);
+            } else {
+#pragma unroll
+                for (int o = 0; o < OUTS; ++o)
+                    if (io[o].live)
+                        store_pair(p, sc, ph, e, io[o], total[2 * o], total[2 * o + 1], 0.f, 0.f);
+            }
         }
         if (group0 + NB < g.n_blocks) named_barrier(kBarConsumers, kConsumerThreads);
     }
-    if (!staged)  // no rows here
-        activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
+    if (!staged) {
+        // No rows here.  Plain activations still run their prologue (CTA 0 may have to store the
+        // gathered rows for the residual stream); cells are simply not read, but a bulk copy
+        // of norm weights this CTA started must land before its shared memory is used again.
+        if (!(cells & MB_CELLS_X)) {
+            activation_finish(p, E, ph, sc, const_cast<__nv_bfloat16*>(xs), act_round, tid);
+        } else if (activation_arms(E->rec)) {
+            wait_activation_copies(p, ph, sc, act_round);
+            named_barrier(kBarConsumers, kConsumerThreads);
+        }
+    }
     return !dead && !sc->abort_flag;
 }
 
@@ -719,8 +981,10 @@ __device__ __forceinline__ int choose_chunks(int pairs, int nblocks, int ctas, i
 //          averages out far below one bf16 ulp of the result.
 // The new key/value row is appended to the cache in global memory and, for this launch's own
 // arithmetic, taken from shared memory, so nothing waits on that store.
+// `Lmax` is the largest valid length of the batch (the chunk count is chosen for it); every
+// (row, kv head) item reads its own row's length, so rows may hold different numbers of keys.
 template <int D, bool EXACT>
-__device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEntry* E, int L,
+__device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEntry* E, int Lmax,
                                             int ph, SharedCtl* sc, char* scratch, int tid) {
     constexpr int QP = D + 32;  // bf16 pitch of the rotated query rows
     constexpr int DC = D / 32;  // 32-element chunks of the head dimension (QK^T)
@@ -743,14 +1007,20 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     // they are needed instead of being kept in registers across the key loop.
     auto slot = [&](int j) { return entry_address(p, E, j); };
 
-    const int nkeys = L + 1;
-    const int nblocks = (nkeys + 15) >> 4;
     const int pairs = B * Hkv;
-    constexpr bool exact = EXACT;  // contexts of at most 128 keys: nblocks <= 8
+    constexpr bool exact = EXACT;  // contexts of at most 128 keys: at most 8 blocks
+    const int cells = P->i[MB_AT_I_CELLS];
+    const bool in_cells = (cells & MB_CELLS_X) != 0, out_cells = (cells & MB_CELLS_OUT) != 0;
+    const unsigned int in_tag =
+        sc->tag_base + static_cast<unsigned int>(P->i[MB_AT_I_QKV_SOURCE]) + 1u;
+    const unsigned int out_tag = sc->tag_base + static_cast<unsigned int>(ph) + 1u;
+    const int* lengths = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
+    const bool per_row = P->i[MB_AT_I_LEN_COUNT] > 1;
     int nc = 1;
     if (!exact) {
         if (warp == 0) {
-            const int nc_pick = choose_chunks(pairs, nblocks, ctas, P->i[MB_AT_I_MAX_CHUNKS], lane);
+            const int nc_pick = choose_chunks(pairs, (Lmax + 16) >> 4, ctas,
+                                              P->i[MB_AT_I_MAX_CHUNKS], lane);
             if (lane == 0) sc->bcast[0] = nc_pick;
         }
         named_barrier(kBarConsumers, kConsumerThreads);
@@ -779,11 +1049,18 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     for (int item = cta; item < items; item += ctas) {
         const int pair = item / nc, chunk = item - pair * nc;
         const int b = pair / Hkv, h = pair - b * Hkv;
+        // this row's own length: it may need fewer chunks than the longest row
+        const int L = __ldg(lengths + (per_row ? b : 0));
+        const int nkeys = L + 1;
+        const int nblocks = (nkeys + 15) >> 4;
+        const int row_chunks = min(nc, nblocks);
+        if (chunk >= row_chunks) continue;  // the whole CTA takes this branch together
         // chunk * nblocks stays far below 2^32: 32-bit division is enough
         const int blk0 = static_cast<int>(static_cast<unsigned>(chunk) * static_cast<unsigned>(nblocks) /
-                                          static_cast<unsigned>(nc));
+                                          static_cast<unsigned>(row_chunks));
         const int blk1 = static_cast<int>(static_cast<unsigned>(chunk + 1) *
-                                          static_cast<unsigned>(nblocks) / static_cast<unsigned>(nc));
+                                          static_cast<unsigned>(nblocks) /
+                                          static_cast<unsigned>(row_chunks));
         const size_t cache_row0 =
             (static_cast<size_t>(b) * P->i[MB_AT_I_CAPACITY] * Hkv + h) * D;  // (b, key 0, h)
         const unsigned short* kc0 =
@@ -881,7 +1158,44 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         // held across the trigonometry below); cos/sin are computed meanwhile; the first K/V
         // tiles are requested right after, so they fly during the barrier and the rotation.
         constexpr int kRowVectors = D / 8;  // 16-byte vectors per head row
-        for (int v = tid; v < (group + 2) * kRowVectors; v += kConsumerThreads) {
+        const int first = blk0 + warp;
+        if (kStaged && in_cells) {
+            // the cache tiles do not depend on this layer's projections: request the first one
+            // before waiting for q, k and v
+            if (first < blk1)
+                issue_tile(first, 0);
+            else
+                asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        if (in_cells) {
+            // q, k and v of this (row, kv head) as flagged cells of the projection phase: load,
+            // retry until they carry its sequence number, park the values in shared memory
+            constexpr int kRowQuads = D / 4;  // 16-byte loads (two cells, four values) per row
+            for (int v = tid; v < (group + 2) * kRowQuads; v += kConsumerThreads) {
+                const int row = v / kRowQuads, part = v - row * kRowQuads;
+                const char* src;
+                __nv_bfloat16* dst;
+                if (row < group) {
+                    src = reinterpret_cast<const char*>(slot(MB_AT_S_Q)) +
+                          ((static_cast<size_t>(b) * Hq + h * group + row) * D + part * 4) * 4;
+                    dst = qs + row * QP;
+                } else if (row == group) {
+                    src = reinterpret_cast<const char*>(slot(MB_AT_S_K)) +
+                          ((static_cast<size_t>(b) * Hkv + h) * D + part * 4) * 4;
+                    dst = kn;
+                } else {
+                    src = reinterpret_cast<const char*>(slot(MB_AT_S_V)) +
+                          ((static_cast<size_t>(b) * Hkv + h) * D + part * 4) * 4;
+                    dst = vn;
+                }
+                unsigned long long c0, c1;
+                ld_cell_pair(src, c0, c1);
+                if (cell_tag(c0) != in_tag || cell_tag(c1) != in_tag)
+                    cell_pair_wait(src, in_tag, c0, c1, p, sc, ph);
+                *reinterpret_cast<uint2*>(dst + part * 4) = make_uint2(cell_data(c0), cell_data(c1));
+            }
+        }
+        for (int v = tid; !in_cells && v < (group + 2) * kRowVectors; v += kConsumerThreads) {
             const int row = v / kRowVectors, part = v - row * kRowVectors;
             const unsigned short* src;
             __nv_bfloat16* dst;
@@ -900,7 +1214,7 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             }
             cp_async16(dst + part * 8, src + part * 8);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (!in_cells) asm volatile("cp.async.commit_group;" ::: "memory");
         if (tid < D / 2) {
             const void* invf = reinterpret_cast<const void*>(slot(MB_AT_S_INVFREQ));
             const float f =
@@ -917,7 +1231,6 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         }
         uint4 kt[2][DC];
         uint4 vt[DB][4];
-        const int first = blk0 + warp;
         if (first < blk1) {
             if (kEarlyKeys) load_keys(first, kt);
             if (kEarlyValues) load_values(first, vt);
@@ -925,18 +1238,20 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         if (kStaged) {
             // the first tile flies during the barrier and the rotation below; an empty group
             // keeps the group count the same for warps without a tile
-            if (first < blk1)
-                issue_tile(first, 0);
-            else
-                asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 1;" ::: "memory");  // the prologue rows only
+            if (!in_cells) {
+                if (first < blk1)
+                    issue_tile(first, 0);
+                else
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 1;" ::: "memory");  // the prologue rows only
+            }
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         named_barrier(kBarConsumers, kConsumerThreads);
         // rotate in place: thread e owns the element pair (i, i + D/2) of row e / (D/2); rows
         // 0..group-1 are query heads, row `group` is the new key
-        const bool appends = chunk == nc - 1;  // the chunk that holds key L stores the new row
+        const bool appends = chunk == row_chunks - 1;  // the chunk that holds key L stores the new row
         const size_t new_row = cache_row0 + static_cast<size_t>(L) * key_stride;
         const float q_scale = P->f[MB_AT_F_Q_SCALE];
         unsigned short* kcache = reinterpret_cast<unsigned short*>(slot(MB_AT_S_KCACHE));
@@ -1198,12 +1513,21 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
         const float* state = running + static_cast<size_t>((rounds - 1) & 1) * group * SW;
         trace_stamp(p, ph, 6, tid);
 
-        unsigned short* out = reinterpret_cast<unsigned short*>(slot(MB_AT_S_OUT));
-        if (nc == 1) {
-            for (int e = tid; e < group * D; e += kConsumerThreads) {
-                const int gq = e / D, d = e - gq * D;
-                const float v = state[gq * SW + 2 + d] / state[gq * SW + 1];
-                out[(static_cast<size_t>(b) * Hq + h * group + gq) * D + d] = float_to_bf16_bits(v);
+        // results leave in pairs of neighbouring elements: one 4-byte store, or one cell
+        char* out = reinterpret_cast<char*>(slot(MB_AT_S_OUT));
+        auto store_out = [&](int gq, int d, float v0, float v1) {
+            const size_t index = (static_cast<size_t>(b) * Hq + h * group + gq) * D + d;
+            const unsigned int packed = pack_bf16(v0, v1);
+            if (out_cells)
+                st_cell(out + index * 4, packed, out_tag);
+            else
+                *reinterpret_cast<unsigned int*>(out + index * 2) = packed;
+        };
+        if (row_chunks == 1) {
+            for (int e = tid; e < group * (D / 2); e += kConsumerThreads) {
+                const int gq = e / (D / 2), d = 2 * (e - gq * (D / 2));
+                const float denom_ = state[gq * SW + 1];
+                store_out(gq, d, state[gq * SW + 2 + d] / denom_, state[gq * SW + 3 + d] / denom_);
             }
         } else {
             float* partial = reinterpret_cast<float*>(slot(MB_AT_S_PARTIAL));
@@ -1220,7 +1544,8 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             }
             named_barrier(kBarConsumers, kConsumerThreads);
             trace_stamp(p, ph, 7, tid);
-            if (sc->bcast[1] == nc - 1) {
+            const int nc_row = row_chunks;
+            if (sc->bcast[1] == nc_row - 1) {
                 // Last chunk of this (row, kv head) to arrive folds all chunks, in chunk order.
                 // Step 1: (max, sum) of every chunk into shared memory, all loads in flight
                 // together, then the per-chunk weights and the denominator.
@@ -1228,8 +1553,8 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 float* weight = fold;          // [group][nc] chunk maxima, then weights
                 float* denom = fold + 8 * 64;  // [group]
                 float* sums = merge;           // [group][nc] chunk sums (merge slots are free)
-                for (int e = tid; e < group * nc; e += kConsumerThreads) {
-                    const int gq = e / nc, c = e - gq * nc;
+                for (int e = tid; e < group * nc_row; e += kConsumerThreads) {
+                    const int gq = e / nc_row, c = e - gq * nc_row;
                     const float* st = all + (static_cast<size_t>(c) * group + gq) * SW;
                     weight[e] = ld_cg_f32(st);
                     sums[e] = ld_cg_f32(st + 1);
@@ -1237,34 +1562,39 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                 named_barrier(kBarConsumers, kConsumerThreads);
                 if (tid < group) {
                     float mx = -INFINITY;
-                    for (int c = 0; c < nc; ++c) mx = fmaxf(mx, weight[tid * nc + c]);
+                    for (int c = 0; c < nc_row; ++c) mx = fmaxf(mx, weight[tid * nc_row + c]);
                     float total = 0.f;
-                    for (int c = 0; c < nc; ++c) {
-                        const float wgt = expf(weight[tid * nc + c] - mx);
-                        weight[tid * nc + c] = wgt;
-                        total += sums[tid * nc + c] * wgt;
+                    for (int c = 0; c < nc_row; ++c) {
+                        const float wgt = expf(weight[tid * nc_row + c] - mx);
+                        weight[tid * nc_row + c] = wgt;
+                        total += sums[tid * nc_row + c] * wgt;
                     }
                     denom[tid] = total;
                 }
                 named_barrier(kBarConsumers, kConsumerThreads);
-                // Step 2: weighted sums of the value partials; loads are independent.
-                for (int e = tid; e < group * D; e += kConsumerThreads) {
-                    const int gq = e / D, d = e - gq * D;
+                // Step 2: weighted sums of the value partials, two neighbouring elements per
+                // thread; loads are independent.
+                for (int e = tid; e < group * (D / 2); e += kConsumerThreads) {
+                    const int gq = e / (D / 2), d = 2 * (e - gq * (D / 2));
                     const float* col = all + static_cast<size_t>(gq) * SW + 2 + d;
-                    float sum_v = 0.f;
-                    for (int c0 = 0; c0 < nc; c0 += 8) {  // eight loads in flight per batch
-                        float part[8];
+                    float sum0 = 0.f, sum1 = 0.f;
+                    for (int c0 = 0; c0 < nc_row; c0 += 8) {  // eight loads in flight per batch
+                        float2 part[8];
 #pragma unroll
                         for (int u = 0; u < 8; ++u)
-                            part[u] = c0 + u < nc
-                                          ? ld_cg_f32(col + static_cast<size_t>(c0 + u) * group * SW)
-                                          : 0.f;
+                            part[u] = c0 + u < nc_row
+                                          ? __ldcg(reinterpret_cast<const float2*>(
+                                                col + static_cast<size_t>(c0 + u) * group * SW))
+                                          : make_float2(0.f, 0.f);
 #pragma unroll
                         for (int u = 0; u < 8; ++u)
-                            if (c0 + u < nc) sum_v += part[u] * weight[gq * nc + c0 + u];
+                            if (c0 + u < nc_row) {
+                                const float wgt = weight[gq * nc_row + c0 + u];
+                                sum0 += part[u].x * wgt;
+                                sum1 += part[u].y * wgt;
+                            }
                     }
-                    out[(static_cast<size_t>(b) * Hq + h * group + gq) * D + d] =
-                        float_to_bf16_bits(sum_v / denom[gq]);
+                    store_out(gq, d, sum0 / denom[gq], sum1 / denom[gq]);
                 }
                 if (tid == 0) counter[pair] = 0;  // ready for the next launch
             }
@@ -1273,26 +1603,37 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     }
 }
 
-// Reads the valid length once, refuses a full cache (every thread of every CTA sees the same
-// length, so all of them take the same branch) and picks the softmax mode.  The two modes are
-// separate functions so that a launch only ever executes one of them: instruction-cache
-// footprint matters more here than code sharing.
+// Reads the valid lengths (one shared by the batch, or one per row), refuses a full cache --
+// every thread of every CTA sees the same lengths, so all of them take the same branch -- and
+// picks the softmax mode from the longest row.  The two modes are separate functions so that a
+// launch only ever executes one of them: instruction-cache footprint matters more here than
+// code sharing.  The lengths do not change during a launch (they are advanced when it ends).
 template <int D>
 __device__ __forceinline__ void attention_decode(const KernelParams& p, const PhaseEntry* E,
                                                  int ph, SharedCtl* sc, char* scratch, int tid) {
     const int* lenp = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
-    const int L = __ldcg(lenp);
-    if (L < 0 || L + 1 > E->rec.i[MB_AT_I_CAPACITY]) {
+    const int count = E->rec.i[MB_AT_I_LEN_COUNT] > 1 ? E->rec.i[MB_AT_I_BATCH] : 1;
+    const int capacity = E->rec.i[MB_AT_I_CAPACITY];
+    int longest = 0, bad = 0, bad_length = 0;
+    for (int r = 0; r < count; ++r) {
+        const int L = __ldg(lenp + r);
+        if (L < 0 || L + 1 > capacity) {
+            bad = 1;
+            bad_length = L;
+        }
+        longest = max(longest, L);
+    }
+    if (bad) {
         if (tid == 0) {
-            record_status(p.ctl, MB_ST_KV_OVERFLOW, ph, L);
+            record_status(p.ctl, MB_ST_KV_OVERFLOW, ph, bad_length);
             sc->abort_flag = 1;
         }
         return;
     }
-    if (L + 1 <= E->rec.i[MB_AT_I_EXACT_KEYS])
-        attention_body<D, true>(p, E, L, ph, sc, scratch, tid);
+    if (longest + 1 <= E->rec.i[MB_AT_I_EXACT_KEYS])
+        attention_body<D, true>(p, E, longest, ph, sc, scratch, tid);
     else
-        attention_body<D, false>(p, E, L, ph, sc, scratch, tid);
+        attention_body<D, false>(p, E, longest, ph, sc, scratch, tid);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1300,7 +1641,7 @@ __device__ __forceinline__ void attention_decode(const KernelParams& p, const Ph
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_entry(const PhaseEntry* src, PhaseEntry* dst, int tid) {
     // 16-byte asynchronous copies global -> shared of one phase entry
-    if (tid < kEntryVectors) {
+    if (src != nullptr && tid < kEntryVectors) {
         const unsigned int d = smem_u32(reinterpret_cast<char*>(dst) + 16 * tid);
         const char* g = reinterpret_cast<const char*>(src) + 16 * tid;
         asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(g) : "memory");
@@ -1308,11 +1649,21 @@ __device__ __forceinline__ void prefetch_entry(const PhaseEntry* src, PhaseEntry
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// Thread 0, at the start of phase `ph`: fetch the counter of phase ph - 2 from L2 (not L1: other
+// SMs add to it) into shared memory, in the same group as the entry prefetch, so that the check
+// at the end of the phase finds it there without a round trip of its own.
+__device__ __forceinline__ void prefetch_guard(const KernelParams& p, SharedCtl* sc, int ph) {
+    const unsigned int d = smem_u32(sc->guard);
+    const void* g = &p.ctl->finished[(ph - 2) & 3];
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(g) : "memory");
+}
+
 // Every thread waits for its own copies; the 16-byte vectors of one address pair (two slots)
 // were copied by one thread, which then patches them -- no extra barrier is needed before the
 // CTA barrier that publishes the entry.
 __device__ __forceinline__ void wait_entry(const KernelParams& p, PhaseEntry* dst, int tid) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (dst == nullptr) return;
     constexpr int kFirstAddrVector = offsetof(PhaseEntry, addr) / 16;
     static_assert(offsetof(PhaseEntry, addr) % 16 == 8, "addr[] starts mid-vector");
     // vector kFirstAddrVector holds addr[0] in its upper half; vector v > that holds
@@ -1341,6 +1692,12 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         mbar_init(&sc->act_full, 1);
         sc->abort_flag = peek_status(p.ctl) != 0 ? 1 : 0;  // a faulted plan runs nothing
         sc->issued = 0;
+        sc->limit_ns = static_cast<unsigned long long>(p.wait_limit_us) * 1000ull;
+        // Both words only change after the closing barrier of a launch (or by a host reset).
+        const unsigned int calls = *reinterpret_cast<volatile unsigned int*>(&p.ctl->calls);
+        const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(&p.ctl->epoch);
+        sc->tag_base = epoch * static_cast<unsigned int>(p.n_phases);
+        sc->calls = calls;
         mbar_init_fence();
     }
     if (tid < kConsumerThreads) {
@@ -1360,8 +1717,8 @@ decode_kernel(const __grid_constant__ KernelParams p) {
         int barrier_index = 0;
         bool ok = true;
         // Optional per-phase trace: thread 0 of every CTA stamps the global timer at phase
-        // start (0), after the activation prologue (1), after the body (2) and after the
-        // closing grid barrier (3).
+        // start (0), after the activation copies were started (1), after the body (2) and after
+        // the closing grid barrier, if the phase has one (3).
         auto stamp = [&](int ph, int event) {
             if (p.trace != nullptr && tid == 0)
                 p.trace[(static_cast<size_t>(blockIdx.x) * p.n_phases + ph) * kTraceEvents + event] =
@@ -1372,7 +1729,8 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             // that no phase starts with a dependent chain of global loads.
             const PhaseEntry* E = &sc->entry[ph & 1];
             const bool more = ph + 1 < p.n_phases;
-            if (more) prefetch_entry(p.entries + ph + 1, &sc->entry[(ph + 1) & 1], tid);
+            if (ph >= 2 && tid == 0) prefetch_guard(p, sc, ph);
+            prefetch_entry(more ? p.entries + ph + 1 : nullptr, &sc->entry[(ph + 1) & 1], tid);
             stamp(ph, 0);
             switch (E->rec.body) {
                 case MB_BODY_NOP:
@@ -1382,10 +1740,12 @@ decode_kernel(const __grid_constant__ KernelParams p) {
                     activation_issue(p, E, ph, sc, xs, tid);
                     stamp(ph, 1);
                     if (E->rec.i[MB_GV_I_NMAT] == 2)
-                        gemv_consume<2>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
+                        gemv_consume<2, true>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
+                    else if (E->rec.i[MB_GV_I_ROW_TILE] == 2 * kRowTile)
+                        gemv_consume<2, false>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
                     else
-                        gemv_consume<1>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
-                    ++act_round;
+                        gemv_consume<1, false>(p, E, ph, sc, xs, red, ring, it, act_round, tid);
+                    if (activation_arms(E->rec)) ++act_round;
                     break;
                 }
                 case MB_BODY_ATTN_DECODE: {
@@ -1410,31 +1770,55 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             // except for conditions every thread evaluates identically).
             stamp(ph, 2);
             const int flags = E->rec.flags;
-            const unsigned long long length_address =
-                (flags & MB_FLAG_BUMP_LENGTH) ? entry_address(p, E, MB_AT_S_LEN) : 0ull;
-            if (more) wait_entry(p, &sc->entry[(ph + 1) & 1], tid);  // published by the barrier below
+            wait_entry(p, more ? &sc->entry[(ph + 1) & 1] : nullptr, tid);  // published by the barrier below
+            if (ph >= 2 && tid == 0 && !sc->abort_flag) {
+                const unsigned int target = finished_target(p, sc, ph - 2);
+                if (static_cast<int>(sc->guard[0] - target) < 0) finished_wait(p, sc, ph, ph - 2);
+            }
             if (flags & MB_FLAG_BARRIER) {
                 ++barrier_index;
                 ok = grid_barrier(p.ctl, base + barrier_index, kBarConsumers, kConsumerThreads, tid,
-                                  &sc->abort_flag, &sc->verdict, ph);
-                if (ok && length_address != 0ull && blockIdx.x == 0 && tid == 0) {
-                    int* lenp = reinterpret_cast<int*>(length_address);
-                    *lenp = *lenp + 1;
-                }
+                                  &sc->abort_flag, &sc->verdict, ph, sc->limit_ns);
                 stamp(ph, 3);
-            } else if (more) {
-                named_barrier(kBarConsumers, kConsumerThreads);
-                if (tid == 0) sc->verdict = sc->abort_flag == 0 ? 1 : 0;
-                named_barrier(kBarConsumers, kConsumerThreads);
-                ok = sc->verdict != 0;
+            } else {
+                // one CTA barrier: every warp is done with the phase's shared memory, and all of
+                // them learn together whether one of them raised the abort flag
+                ok = !named_barrier_or(kBarConsumers, kConsumerThreads, sc->abort_flag != 0);
+            }
+            // This CTA has finished phase `ph` (all its loads of the phase's inputs are done):
+            // counted for the CTAs that are about to leave phase ph + 2.  No ordering is needed
+            // beyond the CTA barrier above.
+            if (ok && tid == 0) {
+                // plain results that a later phase fetches after waiting on this counter: make
+                // the CTA's stores (ordered before this point by the CTA barrier) visible first
+                if (flags & MB_FLAG_FENCE) asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(
+                                 &p.ctl->finished[ph & 3].count)
+                             : "memory");
             }
         }
         if (ok) {
-            // Closing barrier: nobody may still read `calls` when CTA 0 advances it.
+            // Closing barrier: every CTA has read the valid lengths, `calls` and `epoch` and is
+            // done with them; CTA 0 may now advance them.
             ++barrier_index;
             ok = grid_barrier(p.ctl, base + barrier_index, kBarConsumers, kConsumerThreads, tid,
-                              &sc->abort_flag, &sc->verdict, p.n_phases);
-            if (ok && blockIdx.x == 0 && tid == 0) p.ctl->calls = calls + 1;
+                              &sc->abort_flag, &sc->verdict, p.n_phases, sc->limit_ns);
+            if (ok && blockIdx.x == 0) {
+                // valid_length += 1 for every attention phase that asks for it, one thread per
+                // phase (the table is in L2: the producers prefetched it)
+                for (int q = tid; q < p.n_phases; q += kConsumerThreads) {
+                    const PhaseEntry* G = p.entries + q;
+                    if (G->rec.body != MB_BODY_ATTN_DECODE || !(G->rec.flags & MB_FLAG_BUMP_LENGTH))
+                        continue;
+                    int* lenp = reinterpret_cast<int*>(resolve_dynamic(p, G->addr[MB_AT_S_LEN]));
+                    const int count = G->rec.i[MB_AT_I_LEN_COUNT] > 1 ? G->rec.i[MB_AT_I_BATCH] : 1;
+                    for (int r = 0; r < count; ++r) lenp[r] = lenp[r] + 1;
+                }
+                if (tid == 0) {
+                    p.ctl->calls = calls + 1;
+                    p.ctl->epoch = *reinterpret_cast<volatile unsigned int*>(&p.ctl->epoch) + 1u;
+                }
+            }
         }
     }
 
@@ -1509,7 +1893,11 @@ namespace mb {
 namespace decode {
 
 constexpr size_t kStaticScratchBytes = 4u << 20;
-constexpr size_t kStaticControlBytes = 256;        // Control + "CTAs done" counter
+constexpr size_t kStaticControlBytes = 256;        // status words of Control + "CTAs done" counter
+// The attention body only touches Control::status through the pointer it is given (record_status,
+// peek_status); those words must lie inside the first 128 bytes, before the "done" counter.
+static_assert(offsetof(Control, status) + sizeof(int) * 4 <= 128,
+              "the status words must precede the done counter of the static control area");
 constexpr size_t kStaticCounterBytes = 4096;       // arrival counters: up to 1024 (row, kv head)
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -1522,7 +1910,12 @@ attention_static_kernel(const __grid_constant__ PhaseEntry entry, Control* ctl, 
     const int tid = threadIdx.x;
     if (tid < kEntryVectors)
         reinterpret_cast<uint4*>(&sc->entry[0])[tid] = reinterpret_cast<const uint4*>(&entry)[tid];
-    if (tid == 0) sc->abort_flag = 0;
+    if (tid == 0) {
+        sc->abort_flag = 0;
+        sc->tag_base = 0;
+        sc->calls = 0;
+        sc->limit_ns = kPipeTimeoutNs;
+    }
     __syncthreads();
     KernelParams p;
     p.entries = nullptr;
@@ -1534,6 +1927,7 @@ attention_static_kernel(const __grid_constant__ PhaseEntry entry, Control* ctl, 
     p.stages = 0;
     p.stage_bytes = 0;
     p.activation_bytes = 0;
+    p.wait_limit_us = 2000000u;
     const PhaseEntry* E = &sc->entry[0];
     const int D = E->rec.i[MB_AT_I_HEAD_DIM];
     if (D == 64)
@@ -1598,6 +1992,9 @@ extern "C" int mb_attention_decode_static(const mb_attention_args* a, void* stre
         if (ptr == 0) return MB_ERR_INVALID;
     if ((a->query | a->key | a->value | a->key_cache | a->value_cache | a->out) & 15ull)
         return MB_ERR_INVALID;
+    if ((a->position_ids & 7ull) || (a->valid_length & 3ull) || (a->inv_freq & 3ull) ||
+        (a->status & 3ull))
+        return MB_ERR_INVALID;
 
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return MB_ERR_CUDA;
@@ -1654,6 +2051,7 @@ extern "C" int mb_attention_decode_static(const mb_attention_args* a, void* stre
     entry.rec.i[MB_AT_I_MAX_CHUNKS] = max_chunks;
     entry.rec.i[MB_AT_I_MERGE_SLOTS] = merge_slots;
     entry.rec.i[MB_AT_I_EXACT_KEYS] = a->capacity < 128 ? a->capacity : 128;
+    entry.rec.i[MB_AT_I_LEN_COUNT] = 1;
     entry.rec.f[MB_AT_F_SCALE] = 1.0f / sqrtf(static_cast<float>(a->head_dim));
     entry.rec.f[MB_AT_F_ROPE_SCALE] = a->rope_scale;
     entry.rec.f[MB_AT_F_Q_SCALE] = a->query_scale;

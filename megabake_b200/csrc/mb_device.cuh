@@ -16,10 +16,21 @@ namespace mb {
 // ---------------------------------------------------------------------------------------
 constexpr int kBarrierLanes = 8;
 struct Control {
-    unsigned int reserved;
+    unsigned int epoch;     // base of the hand-off sequence numbers: grows with every completed
+                            // launch and every reset, so that no cell of an earlier launch can
+                            // ever be mistaken for one of this launch
     unsigned int calls;     // completed launches; the barrier targets derive from it
     int status[4];          // code, phase, detail, (unused)
-    unsigned int pad[26];
+    unsigned int pad0[26];
+    // CTAs that finished a phase: a ring of four counters (a line each), phase q counts on
+    // counter q % 4.  Every CTA, before it leaves phase q, waits until all CTAs have finished
+    // phase q - 2; so no CTA is ever more than two phases ahead of another, a counter never
+    // mixes arrivals of two phases, and a cell buffer may be overwritten from the third phase
+    // after its last reader on.
+    struct Finished {
+        unsigned int count;
+        unsigned int pad[31];
+    } finished[4];
     // Counting grid barrier, spread over eight counters 128 bytes apart: CTA c arrives on
     // counter c % 8, so the arrivals (atomics on one address serialise in L2) proceed on eight
     // addresses at once.  Counter j grows by the number of CTAs mapped to it per barrier.
@@ -51,10 +62,12 @@ struct KernelParams {
     int stages;            // weight-ring depth
     int stage_bytes;       // bytes of one ring stage
     int activation_bytes;  // shared bytes reserved for activations / attention scratch
+    unsigned int wait_limit_us;  // bound of every device-side wait, microseconds
 };
 
 // Wait limits.  Every wait in the kernels is bounded: when one runs out the kernel records
-// a status, raises the CTA's abort flag and drains instead of spinning forever.
+// a status, raises the CTA's abort flag and drains instead of spinning forever.  The decode
+// kernel takes its limit from the plan (KernelParams::wait_limit_us); these are the defaults.
 constexpr unsigned long long kBarrierTimeoutNs = 2000000000ull;  // 2 s
 constexpr unsigned long long kPipeTimeoutNs = 2000000000ull;     // 2 s
 constexpr unsigned int kDrainTryLimit = 1000000u;                 // try_wait calls while draining
@@ -178,6 +191,55 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Named barrier that also ORs a predicate over the arriving threads.
+__device__ __forceinline__ bool named_barrier_or(int id, int threads, bool value) {
+    unsigned int out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %3, 0;\n\t"
+        "barrier.cta.red.or.pred q, %1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(out)
+        : "r"(id), "r"(threads), "r"(value ? 1u : 0u)
+        : "memory");
+    return out != 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Flagged cells: 64 bits = two bf16 values (low word) + a 32-bit sequence number (high word),
+// written and read as ONE 8-byte access, so a reader that sees the number it expects has the
+// data of that very store.  Loads go to L2 (gpu scope): the cells are written by other SMs.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_cell(void* p, unsigned int data, unsigned int tag) {
+    const unsigned long long v =
+        static_cast<unsigned long long>(data) | (static_cast<unsigned long long>(tag) << 32);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_cell(const void* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// two neighbouring cells (16-byte aligned); each is read atomically
+__device__ __forceinline__ void ld_cell_pair(const void* p, unsigned long long& a,
+                                             unsigned long long& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];"
+                 : "=l"(a), "=l"(b)
+                 : "l"(p)
+                 : "memory");
+}
+__device__ __forceinline__ unsigned int cell_tag(unsigned long long v) {
+    return static_cast<unsigned int>(v >> 32);
+}
+__device__ __forceinline__ unsigned int cell_data(unsigned long long v) {
+    return static_cast<unsigned int>(v);
+}
+__device__ __forceinline__ unsigned int ld_relaxed_u32(const void* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
                  : "memory");
@@ -209,14 +271,15 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 // Bounded mbarrier wait.  `abort_flag` is a CTA-shared int that any thread raises when a
 // wait of its own ran out; everybody else then stops waiting too.
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned int parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag,
+                                                  unsigned long long limit_ns = kPipeTimeoutNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = global_timer_ns();
     for (unsigned int tries = 1;; ++tries) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((tries & 127u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - start > kPipeTimeoutNs) return false;
+            if (global_timer_ns() - start > limit_ns) return false;
         }
     }
 }
@@ -257,7 +320,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned int a0, u
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int generation, int bar_id,
                                              int threads, int tid, volatile int* abort_flag,
-                                             volatile int* verdict, int phase) {
+                                             volatile int* verdict, int phase,
+                                             unsigned long long limit_ns = kBarrierTimeoutNs) {
     named_barrier(bar_id, threads);
     if (tid < kBarrierLanes) {
         constexpr unsigned int kMask = (1u << kBarrierLanes) - 1u;
@@ -285,7 +349,7 @@ __device__ __forceinline__ bool grid_barrier(Control* ctl, unsigned int generati
                 if ((++polls & 63u) == 0u) {  // the eight lanes take this branch together
                     if (start == 0) start = global_timer_ns();
                     const bool faulted = peek_status(ctl) != 0 || *abort_flag != 0;
-                    const bool late = global_timer_ns() - start > kBarrierTimeoutNs;
+                    const bool late = global_timer_ns() - start > limit_ns;
                     if (__any_sync(kMask, faulted || late)) {
                         if (tid == 0 && !faulted)
                             record_status(ctl, MB_ST_BARRIER_TIMEOUT, phase,

@@ -39,7 +39,8 @@ def _require_native_device(device: torch.device) -> None:
 class BoundDecoder:
     """A planned decoder step bound to live tensors."""
 
-    def __init__(self, layout: PlanLayout, args: Sequence[torch.Tensor], *, ctas: int = 0):
+    def __init__(self, layout: PlanLayout, args: Sequence[torch.Tensor], *, ctas: int = 0,
+                 wait_limit_ms: int = 0):
         self.layout = layout
         self.program = layout.program
         p = self.program
@@ -57,7 +58,7 @@ class BoundDecoder:
             self.plan = rt.Plan(layout.phases, n_slots=len(layout.slots), n_dynamic=3,
                                 activation_bytes=layout.activation_bytes,
                                 device=self.device.index or 0, mode=layout.mode, ctas=ctas,
-                                stage_bytes=layout.stage_bytes)
+                                stage_bytes=layout.stage_bytes, wait_limit_ms=wait_limit_ms)
             # tensors the plan itself owns: a non-causal mask, and the positions 0..T-1 of
             # every row when the captured graph held them as constants
             self._constants = {name: tensor.to(self.device)

@@ -2,9 +2,11 @@
 
 The counterpart of the reference's phase profiler (``tools/phase_profile.py:104-238`` on top of
 the ``MEGABAKE_PHASE_TIMER`` stamps, ``src/megabake/runtime.py:22-47``): thread 0 of every CTA
-records the time at phase start, after the activation prologue, after the body and after the
-closing grid barrier.  From those this module derives, per phase, how long the critical CTA
-worked, how long the others waited for it, and what the barrier itself cost.
+records the time at phase start, after the activation copies were started, after the body and,
+where a phase ends in a grid barrier, after that barrier.  From those this module derives, per
+phase, how long the critical CTA worked and how long the others waited; with flagged-cell
+hand-offs (no barrier) a phase's wait shows up inside the next phase's body, as the time its
+consumers spent polling.
 """
 
 from __future__ import annotations

@@ -1,14 +1,23 @@
-"""Execution planner: packs a ``DecoderProgram`` into barrier intervals and emits the
-phase records + address-table layout of the C ABI.
+"""Execution planner: packs a ``DecoderProgram`` into phases and emits the phase records +
+address-table layout of the C ABI.
 
-Decode packing (one grid barrier closes each interval):
+Decode packing (five phases per layer; the activations between them travel as flagged cells,
+so no grid barrier separates them -- a consumer polls the very cells it needs and starts on
+them as soon as their producers have stored them):
 
-    [embed gather (layer 0) . rmsnorm . q|k|v (+bias)]          |
-    [rope(q, new k) . kv append . split-key attention . merge]   |  (+ valid_length += 1)
-    [o_proj + residual]                                          |
-    [rmsnorm . gate|up . act(gate) * up]                         |
-    [down + residual]                                            |   x layers
-    [rmsnorm . lm head]
+    [embed gather (layer 0) . rmsnorm . q|k|v (+bias)]          -> q, k, v cells
+    [rope(q, new k) . kv append . split-key attention . merge]   -> attention cells
+    [o_proj + residual]                                          -> hidden cells (buffer B)
+    [rmsnorm . gate|up . act(gate) * up]                         -> gated cells
+    [down + residual]                                            -> hidden cells (A or C)   x layers
+    [rmsnorm . lm head]                                          -> logits (plain bf16)
+
+The kernel keeps its CTAs within two phases of one another, so a cell buffer may be rewritten
+from the third phase after its last reader on.  Every buffer is five phases apart from itself
+except the residual stream, which o_proj reads (as the residual) three phases after ``down`` of
+the layer before wrote it: it rotates through three buffers -- a layer reads its input from A
+(even layers) or C (odd layers), o_proj writes B, ``down`` writes the other of A and C.  The
+valid lengths are advanced when the launch ends.
 
 RMSNorm, the embedding gather, RoPE, bias, residual adds and the gated activation never get
 an interval of their own: they are folded into the consumer's prologue (recomputed by every
@@ -37,6 +46,13 @@ N_DYNAMIC = 3
 CONSUMER_WARPS = 8
 EXACT_SOFTMAX_KEYS = 128  # contexts up to here use the reference-rounding softmax (one CTA)
 MAX_GEMV_ROWS = 8
+# Activations that EVERY CTA reads whole (the input rows of a skinny GEMM) stay plain bf16: their
+# producers fence and report the phase finished, a consumer waits on that one counter and fetches
+# the rows with bulk copies -- measured on B200, the copy engine brings 14-78 KB per CTA into
+# shared memory in about a microsecond, where polling as many flagged cells with ordinary loads
+# took 5-13.  Flagged cells carry what a consumer reads a FEW rows of: q, k and v on their way to
+# the attention items (always), and GEMV inputs up to this many bytes per CTA (0: none).
+CELL_LIMIT_BYTES = 0
 
 
 @dataclass(frozen=True)
@@ -70,6 +86,7 @@ class PlannerOptions:
     merge_slots: int | None = None
     exact_keys: int = EXACT_SOFTMAX_KEYS
     stage_bytes: int | None = None  # force the ring stage size (tuning sweeps)
+    cell_limit: int = CELL_LIMIT_BYTES  # largest per-CTA copy of an activation kept as cells
 
     @classmethod
     def from_env(cls, **overrides) -> "PlannerOptions":
@@ -130,8 +147,19 @@ def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, 
     64 so that staged rows stay bank-staggered) that fit one ring stage together with the
     paired matrix.  Whole rows per copy whenever they fit: the bulk-copy engine is at its best
     from 2 KB per copy upwards.
+
+    Rows of at most 1,024 elements (Qwen2-0.5B, SmolLM-135M) would leave a stage half empty,
+    and with three stages per SM too few bytes in flight to cover the HBM latency: a plain
+    (unpaired) phase then stages 16 rows, two MMA tiles, per stage.
     """
-    del n_total, ctas, forced_row_tile
+    del n_total, ctas
+    tile = ROW_TILE
+    if forced_row_tile in (ROW_TILE, 2 * ROW_TILE) and nmat == 1:
+        tile = forced_row_tile
+    elif nmat == 1 and 2 * ROW_TILE * (k * 2 + row_pad) <= stage_bytes:
+        tile = 2 * ROW_TILE
+    if tile == 2 * ROW_TILE:
+        return tile, k
     limit = ((stage_bytes // (ROW_TILE * nmat)) - row_pad) // 2 // 32 * 32
     if limit < 32:
         fail("resource-admission", f"a ring stage cannot hold 8 rows of {nmat} matrices")
@@ -222,12 +250,15 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
     pro = rt.PRO_RMS_LLAMA if p.norm == "llama" else rt.PRO_RMS_GEMMA
     act = rt.EPI_SILU_MUL if p.activation == "silu" else rt.EPI_GELU_TANH_MUL
 
-    hidden = slots.buffer(B * H * 2, "hidden")
-    q_buf = slots.buffer(B * q_dim * 2, "q")
-    k_buf = slots.buffer(B * kv_dim * 2, "k")
-    v_buf = slots.buffer(B * kv_dim * 2, "v")
-    attn = slots.buffer(B * q_dim * 2, "attention")
-    glu = slots.buffer(B * p.intermediate * 2, "gated")
+    # activations between phases: flagged cells, 8 bytes per pair of bf16 values, zero at first
+    hidden_a = slots.buffer(B * H * 4, "hidden_a", zero=True)
+    hidden_b = slots.buffer(B * H * 4, "hidden_b", zero=True)
+    hidden_c = slots.buffer(B * H * 4, "hidden_c", zero=True)
+    q_buf = slots.buffer(B * q_dim * 4, "q", zero=True)
+    k_buf = slots.buffer(B * kv_dim * 4, "k", zero=True)
+    v_buf = slots.buffer(B * kv_dim * 4, "v", zero=True)
+    attn = slots.buffer(B * q_dim * 4, "attention", zero=True)
+    glu = slots.buffer(B * p.intermediate * 4, "gated", zero=True)
     max_chunks = max(1, min(options.max_chunks, math.ceil(p.capacity / 16)))
     pairs = B * p.kv_heads
     partial = slots.buffer(pairs * max_chunks * p.group * (D + 2) * 4, "attention_partials")
@@ -240,14 +271,33 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
 
     phases: list[rt.Phase] = []
 
+    def as_cells(width: int) -> bool:
+        return B * width * 4 <= options.cell_limit
+
     def gemv(*, k, segments, x_slot, prologue=rt.PRO_NONE, norm_slot=-1, epilogue=rt.EPI_NONE,
-             pair_slot=-1, residual_slot=-1, barrier=True, gather=False, store_x=-1):
+             pair_slot=-1, residual_slot=-1, gather=False, store_x=-1, x_source=-1,
+             residual_source=-1, out_cells=True, out_fenced=False, x_cells=True,
+             residual_cells=True, store_x_cells=True):
+        """``x_source`` / ``residual_source``: index of the phase that wrote that operand earlier
+        in the launch (-1: it comes from outside).  ``*_cells``: the operand is flagged cells
+        (else plain bf16, whose producing phase fences: ``out_fenced``).  Returns the index of
+        the new phase."""
         nonlocal activation
         n_total = sum(n for n, _, _, _ in segments)
         nmat = 2 if pair_slot >= 0 else 1
         row_tile, k_chunk = gemv_geometry(n_total, k, nmat, options.ctas, stage_bytes, row_pad,
                                           options.row_tile)
-        phase = rt.Phase.blank(rt.BODY_GEMV, rt.FLAG_BARRIER if barrier else 0)
+        phase = rt.Phase.blank(rt.BODY_GEMV, rt.FLAG_FENCE if out_fenced else 0)
+        cells = rt.CELLS_OUT if out_cells else 0
+        if x_source >= 0:
+            cells |= rt.CELLS_X_WAIT | (rt.CELLS_X if x_cells else 0)
+            phase.i[rt.GV_I_X_SOURCE] = x_source
+        if residual_source >= 0 and residual_cells:
+            cells |= rt.CELLS_RESIDUAL
+            phase.i[rt.GV_I_RES_SOURCE] = residual_source
+        if store_x >= 0 and store_x_cells:
+            cells |= rt.CELLS_XSTORE
+        phase.i[rt.GV_I_CELLS] = cells
         phase.i[rt.GV_I_ROWS] = B
         phase.i[rt.GV_I_K] = k
         phase.i[rt.GV_I_NSEG] = len(segments)
@@ -277,13 +327,17 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         staged_rows = B + (1 if prologue != rt.PRO_NONE else 0)  # + the norm weight row
         activation = max(activation, staged_rows * (k + 32) * 2)
         phases.append(phase)
+        return len(phases) - 1
 
     inv_freq = slots.arg(p.inv_freq, "inv_freq")
     embed = slots.arg(p.embed_weight, "embed_tokens.weight")
+    hidden_source = 0  # phase that last wrote the residual stream (buffer A): the gather
+    hidden_cells, attn_cells, glu_cells = as_cells(H), as_cells(q_dim), as_cells(p.intermediate)
     for index, layer in enumerate(p.layers):
         tag = f"layers.{index}."
         first = index == 0
-        gemv(
+        layer_in, layer_out = (hidden_a, hidden_c) if index % 2 == 0 else (hidden_c, hidden_a)
+        qkv_phase = gemv(
             k=H,
             segments=[
                 (q_dim, slots.arg(layer.q_weight, tag + "q_proj.weight"),
@@ -293,13 +347,18 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
                 (kv_dim, slots.arg(layer.v_weight, tag + "v_proj.weight"),
                  slots.arg(layer.v_bias, tag + "v_proj.bias"), v_buf),
             ],
-            x_slot=embed if first else hidden,
+            x_slot=embed if first else layer_in,
+            x_source=-1 if first else hidden_source,
+            x_cells=hidden_cells,
             prologue=pro,
             norm_slot=slots.arg(layer.input_norm, tag + "input_layernorm.weight"),
             gather=first,
-            store_x=hidden if first else -1,
+            store_x=hidden_a if first else -1,
+            store_x_cells=hidden_cells,
+            out_fenced=first and not hidden_cells,  # the gathered rows, stored plain
         )
-        attention = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BARRIER | rt.FLAG_BUMP_LENGTH)
+        attention = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BUMP_LENGTH
+                                   | (0 if attn_cells else rt.FLAG_FENCE))
         attention.i[rt.AT_I_BATCH] = B
         attention.i[rt.AT_I_HEADS] = p.heads
         attention.i[rt.AT_I_KV_HEADS] = p.kv_heads
@@ -309,6 +368,9 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         attention.i[rt.AT_I_MAX_CHUNKS] = max_chunks
         attention.i[rt.AT_I_MERGE_SLOTS] = merge_slots
         attention.i[rt.AT_I_EXACT_KEYS] = exact_keys
+        attention.i[rt.AT_I_CELLS] = rt.CELLS_X | (rt.CELLS_OUT if attn_cells else 0)
+        attention.i[rt.AT_I_QKV_SOURCE] = qkv_phase
+        attention.i[rt.AT_I_LEN_COUNT] = p.length_count
         attention.f[rt.AT_F_SCALE] = p.softmax_scale
         attention.f[rt.AT_F_ROPE_SCALE] = p.rope_scale
         attention.f[rt.AT_F_Q_SCALE] = float(p.q_scale or 0.0)
@@ -324,42 +386,61 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         attention.slot[rt.AT_S_PARTIAL] = partial
         attention.slot[rt.AT_S_COUNTER] = counters
         phases.append(attention)
-        gemv(
+        attention_phase = len(phases) - 1
+        o_phase = gemv(
             k=q_dim,
             segments=[(H, slots.arg(layer.o_weight, tag + "o_proj.weight"),
-                       slots.arg(layer.o_bias, tag + "o_proj.bias"), hidden)],
+                       slots.arg(layer.o_bias, tag + "o_proj.bias"), hidden_b)],
             x_slot=attn,
+            x_source=attention_phase,
+            x_cells=attn_cells,
             epilogue=rt.EPI_RESIDUAL,
-            residual_slot=hidden,
+            residual_slot=layer_in,
+            residual_source=hidden_source,
+            residual_cells=hidden_cells,
+            out_cells=hidden_cells,
+            out_fenced=not hidden_cells,
         )
         if layer.gate_bias is not None or layer.up_bias is not None:
             fail("pattern-recognition", "biased gate/up projections are not covered")
-        gemv(
+        gated_phase = gemv(
             k=H,
             segments=[(p.intermediate, slots.arg(layer.gate_weight, tag + "gate_proj.weight"),
                        -1, glu)],
-            x_slot=hidden,
+            x_slot=hidden_b,
+            x_source=o_phase,
+            x_cells=hidden_cells,
             prologue=pro,
             norm_slot=slots.arg(layer.post_norm, tag + "post_attention_layernorm.weight"),
             epilogue=act,
             pair_slot=slots.arg(layer.up_weight, tag + "up_proj.weight"),
+            out_cells=glu_cells,
+            out_fenced=not glu_cells,
         )
-        gemv(
+        hidden_source = gemv(
             k=p.intermediate,
             segments=[(H, slots.arg(layer.down_weight, tag + "down_proj.weight"),
-                       slots.arg(layer.down_bias, tag + "down_proj.bias"), hidden)],
+                       slots.arg(layer.down_bias, tag + "down_proj.bias"), layer_out)],
             x_slot=glu,
+            x_source=gated_phase,
+            x_cells=glu_cells,
             epilogue=rt.EPI_RESIDUAL,
-            residual_slot=hidden,
+            residual_slot=hidden_b,
+            residual_source=o_phase,
+            residual_cells=hidden_cells,
+            out_cells=hidden_cells,
+            out_fenced=not hidden_cells,
         )
     gemv(
         k=H,
         segments=[(p.vocab, slots.arg(p.lm_head_weight, "lm_head.weight"),
                    slots.arg(p.lm_head_bias, "lm_head.bias"), DYN_LOGITS)],
-        x_slot=hidden,
+        x_slot=hidden_a if len(p.layers) % 2 == 0 else hidden_c,
+        x_source=hidden_source,
+        x_cells=hidden_cells,
         prologue=pro,
         norm_slot=slots.arg(p.final_norm, "norm.weight"),
-        barrier=False,
+        out_cells=False,
     )
 
     activation = _align(activation, 128)
@@ -368,6 +449,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
              f"activations need {activation} B of shared memory; with {fixed_bytes} B fixed and two "
              f"{stage_bytes} B weight stages that exceeds {max_smem} B",
              requirement="batch * max(hidden, intermediate) * 2 B must leave room for the ring")
+    # grid barriers per launch: none between phases, one closes the launch
     intervals = sum(1 for phase in phases if phase.flags & rt.FLAG_BARRIER) + 1
     return PlanLayout(
         program=p,
@@ -377,7 +459,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         zero_ranges=slots.zero,
         activation_bytes=activation,
         intervals=intervals,
-        notes=[f"{len(phases)} phases in {intervals} barrier intervals",
+        notes=[f"{len(phases)} phases handed off through flagged cells, {intervals} grid barrier(s)",
                f"attention: max_chunks={max_chunks} merge_slots={merge_slots} "
                f"exact_keys={exact_keys}", f"ring stage {stage_bytes} B"],
         stage_bytes=stage_bytes,

@@ -71,6 +71,7 @@ class DecoderProgram:
     layers: tuple[LayerBinding, ...] = field(default_factory=tuple)
     lm_head_bias: int | None = None
     embed_scale_arg: int | None = None  # graph input holding the embedding scale (read at bind)
+    length_count: int = 1  # valid lengths per layer: 1 (shared by the batch) or ``batch``
     causal: bool = True  # prefill mask kind
     mask: object = field(default=None, compare=False, repr=False)  # additive bf16 mask tensor of a
     # non-causal prefill, [1 or batch, 1, tokens, tokens]

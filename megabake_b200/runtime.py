@@ -15,7 +15,7 @@ from pathlib import Path
 
 from .diagnostics import CompilerDiagnostic, CompilerError
 
-MB_ABI_VERSION = 1
+MB_ABI_VERSION = 2
 MB_MAX_DYNAMIC = 8
 MB_PHASE_INTS = 24
 MB_PHASE_FLOATS = 4
@@ -26,7 +26,8 @@ MODE_DECODE, MODE_PREFILL = 0, 1
 (BODY_NOP, BODY_GEMV, BODY_ATTN_DECODE, BODY_EMBED_ROWS, BODY_RMSNORM_ROWS, BODY_GEMM_TC,
  BODY_ROPE_ROWS, BODY_ATTN_PREFILL) = range(8)
 
-FLAG_BARRIER, FLAG_BUMP_LENGTH = 1, 2
+FLAG_BARRIER, FLAG_BUMP_LENGTH, FLAG_FENCE = 1, 2, 4
+CELLS_X, CELLS_OUT, CELLS_RESIDUAL, CELLS_XSTORE, CELLS_X_WAIT = 1, 2, 4, 8, 16
 PRO_NONE, PRO_RMS_LLAMA, PRO_RMS_GEMMA = 0, 1, 2
 EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_GELU_TANH_MUL = 0, 1, 2, 3
 
@@ -34,6 +35,7 @@ EPI_NONE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_GELU_TANH_MUL = 0, 1, 2, 3
 GV_I_ROWS, GV_I_K, GV_I_NSEG, GV_I_N0 = 0, 1, 2, 3
 GV_I_NMAT, GV_I_PROLOGUE, GV_I_EPILOGUE, GV_I_ROW_TILE, GV_I_K_CHUNK = 6, 7, 8, 9, 10
 GV_I_GATHER, GV_I_VOCAB, GV_I_STORE_X, GV_I_SPLIT_Q, GV_I_SPLIT_R = 11, 12, 13, 14, 15
+GV_I_CELLS, GV_I_X_SOURCE, GV_I_RES_SOURCE = 20, 21, 22
 GV_F_EPS, GV_F_EMBED_SCALE = 0, 1
 GV_S_X, GV_S_NORM_W, GV_S_W0, GV_S_BIAS0, GV_S_OUT0 = 0, 1, 2, 5, 8
 GV_S_W_PAIR, GV_S_RESIDUAL, GV_S_IDS, GV_S_XSTORE = 11, 12, 13, 14
@@ -41,6 +43,7 @@ GV_S_W_PAIR, GV_S_RESIDUAL, GV_S_IDS, GV_S_XSTORE = 11, 12, 13, 14
 # MB_BODY_ATTN_DECODE field indices
 AT_I_BATCH, AT_I_HEADS, AT_I_KV_HEADS, AT_I_HEAD_DIM, AT_I_CAPACITY = 0, 1, 2, 3, 4
 AT_I_INVFREQ_BF16, AT_I_MAX_CHUNKS, AT_I_MERGE_SLOTS, AT_I_EXACT_KEYS = 5, 6, 7, 8
+AT_I_CELLS, AT_I_QKV_SOURCE, AT_I_LEN_COUNT = 9, 10, 11
 AT_F_SCALE, AT_F_ROPE_SCALE, AT_F_Q_SCALE = 0, 1, 2
 (AT_S_Q, AT_S_K, AT_S_V, AT_S_KCACHE, AT_S_VCACHE, AT_S_LEN, AT_S_POS, AT_S_INVFREQ, AT_S_OUT,
  AT_S_PARTIAL, AT_S_COUNTER) = range(11)
@@ -64,7 +67,7 @@ AP_S_Q, AP_S_K, AP_S_V, AP_S_OUT, AP_S_MASK, AP_S_VT = 0, 1, 2, 3, 4, 5
 
 STATUS_NAMES = {
     0: "ok", 1: "barrier-timeout", 2: "pipeline-timeout", 3: "kv-overflow", 4: "token-range",
-    5: "bad-phase", 6: "tensor-memory",
+    5: "bad-phase", 6: "tensor-memory", 7: "handoff-timeout",
 }
 
 
@@ -99,7 +102,8 @@ class PlanDesc(ctypes.Structure):
         ("activation_bytes", ctypes.c_uint32),
         ("ctas", ctypes.c_uint32),
         ("stage_bytes", ctypes.c_uint32),
-        ("reserved", ctypes.c_uint32 * 3),
+        ("wait_limit_ms", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint32 * 2),
     ]
 
 
@@ -287,7 +291,7 @@ class Plan:
 
     def __init__(self, phases: list[Phase], *, n_slots: int, n_dynamic: int,
                  activation_bytes: int, device: int, mode: int = MODE_DECODE, ctas: int = 0,
-                 stage_bytes: int = 0):
+                 stage_bytes: int = 0, wait_limit_ms: int = 0):
         self._lib = load_library()
         self._handle = ctypes.c_void_p()
         self.n_slots = n_slots
@@ -304,6 +308,7 @@ class Plan:
         desc.activation_bytes = activation_bytes
         desc.ctas = ctas
         desc.stage_bytes = stage_bytes
+        desc.wait_limit_ms = wait_limit_ms
         code = self._lib.mb_plan_create(ctypes.byref(desc), ctypes.byref(self._handle))
         _check(self._lib, code, "resource-admission" if code in (3, 4) else "planning",
                "mb_plan_create")

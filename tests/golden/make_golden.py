@@ -4,6 +4,7 @@ Run in the build container only (needs the reference checkout; the fixtures trav
 reference does not):
 
     python tests/golden/make_golden.py /path/to/reference     (or MEGABAKE_REFERENCE=/path/to/reference)
+    python tests/golden/make_golden.py /path/to/reference --per-row    (only ops_per_row.npz)
 
 It imports the reference's own operators and decode wrappers
 (``src/megabake/ops/attention.py``, ``tests/fixtures.py::StatefulSmolLM``,
@@ -31,9 +32,10 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 import os  # noqa: E402
 
-if len(sys.argv) < 2 and "MEGABAKE_REFERENCE" not in os.environ:
+if not [a for a in sys.argv[1:] if not a.startswith("--")] and "MEGABAKE_REFERENCE" not in os.environ:
     raise SystemExit("usage: make_golden.py /path/to/reference (a checkout of the reference)")
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["MEGABAKE_REFERENCE"])
+REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--")
+                 else os.environ["MEGABAKE_REFERENCE"])
 
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REFERENCE / "src"))
@@ -167,6 +169,39 @@ def op_cases():
     return out
 
 
+def per_row_cases():
+    """``kv_attention`` over rows that hold different numbers of keys: the reference's operator
+    (one length shared by the batch, ``src/megabake/ops/attention.py:52-87``) called row by row
+    on batch-1 views, each row with its own length.  This pins what a per-row ``valid_length``
+    of shape ``[batch]`` has to compute."""
+    out = {}
+    g = torch.Generator().manual_seed(321)
+    for tag, (heads, kv_heads, dim, capacity, lengths) in {
+        "gqa": (4, 2, 64, 40, (0, 5, 17, 39)), "mqa": (8, 1, 64, 160, (1, 130, 159)),
+    }.items():
+        batch = len(lengths)
+        q = torch.randn(batch, 1, heads, dim, generator=g).to(torch.bfloat16)
+        k = torch.randn(batch, 1, kv_heads, dim, generator=g).to(torch.bfloat16)
+        v = torch.randn(batch, 1, kv_heads, dim, generator=g).to(torch.bfloat16)
+        kc = torch.randn(batch, capacity, kv_heads, dim, generator=g).to(torch.bfloat16)
+        vc = torch.randn(batch, capacity, kv_heads, dim, generator=g).to(torch.bfloat16)
+        for name, t in (("q", q), ("k", k), ("v", v), ("kc_in", kc), ("vc_in", vc)):
+            out[f"{tag}_{name}"] = bits(t)
+        out[f"{tag}_len_in"] = np.array(lengths)
+        rows, after = [], []
+        for row, cached in enumerate(lengths):
+            length = torch.tensor([cached], dtype=torch.int32)
+            # batch-1 views share storage with kc / vc, so the append lands in the full caches
+            rows.append(ref_kv_attention(q[row:row + 1], k[row:row + 1], v[row:row + 1],
+                                         kc[row:row + 1], vc[row:row + 1], length))
+            after.append(int(length))
+        out[f"{tag}_out"] = bits(torch.cat(rows, dim=0))
+        out[f"{tag}_kc_out"] = bits(kc)
+        out[f"{tag}_vc_out"] = bits(vc)
+        out[f"{tag}_len_out"] = np.array(after)
+    return out
+
+
 def prefill_case(name: str, batch: int, length: int, seed: int, token_seed: int):
     """Hugging Face prefill through the reference's declared attention op."""
     from megabake.fx_handler.hf_attention import register_transformers_attention
@@ -182,11 +217,30 @@ def prefill_case(name: str, batch: int, length: int, seed: int, token_seed: int)
             dict(model=name, batch=batch, length=length, seed=seed, token_seed=token_seed))
 
 
+def reference_identity() -> str:
+    """What the fixtures were made from, without a path of the build machine: a hash over the
+    reference files this script imports."""
+    import hashlib
+
+    digest = hashlib.sha256()
+    for relative in ("src/megabake/ops/attention.py", "tests/fixtures.py",
+                     "benchmarks/stateful_models.py", "src/megabake/fx_handler/hf_attention.py"):
+        digest.update((REFERENCE / relative).read_bytes())
+    return "sha256:" + digest.hexdigest()[:16]
+
+
 def main() -> None:
     torch.manual_seed(0)
     torch.set_num_threads(8)
     import json
 
+    if "--per-row" in sys.argv:  # only the per-row operator fixture (the others are untouched)
+        np.savez_compressed(HERE / "ops_per_row.npz", **per_row_cases())
+        index = json.loads((HERE / "index.json").read_text())
+        index["ops_per_row"] = {"seed": 321}
+        index["_versions"]["reference"] = reference_identity()
+        (HERE / "index.json").write_text(json.dumps(index, indent=1, sort_keys=True))
+        return
     index = {}
     decode = [
         ("tiny-llama", "smollm", 2, 12, 8, 11, 21),
@@ -210,6 +264,8 @@ def main() -> None:
           float((arrays["top2"][:, 0] - arrays["top2"][:, 1]).min()))
     np.savez_compressed(HERE / "ops.npz", **op_cases())
     index["ops"] = {"seed": 123}
+    np.savez_compressed(HERE / "ops_per_row.npz", **per_row_cases())
+    index["ops_per_row"] = {"seed": 321}
     for case in [("tiny-gemma", 2, 12, 15, 35), ("tiny-llama", 1, 16, 11, 31),
                  ("tiny-qwen2", 2, 10, 13, 33)]:
         arrays, meta = prefill_case(*case)
@@ -218,7 +274,7 @@ def main() -> None:
         index[key] = meta
     index["_versions"] = {"torch": torch.__version__,
                           "transformers": __import__("transformers").__version__,
-                          "reference": str(REFERENCE)}
+                          "reference": reference_identity()}
     (HERE / "index.json").write_text(json.dumps(index, indent=1, sort_keys=True))
 
 

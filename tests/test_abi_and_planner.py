@@ -51,13 +51,56 @@ def test_decode_plan_tables(name, batch):
     lib = rt.load_library()
     stage = lib.mb_stage_bytes(rt.MODE_DECODE)
     assert len(layout.phases) == 5 * spec.layers + 1
-    assert layout.intervals == 5 * spec.layers + 1  # + the closing barrier, - the unflagged head
-    for phase in layout.phases:
+    assert layout.intervals == 1  # activations travel as flagged cells: only the closing barrier
+    writers = {}  # workspace slot -> phase that last wrote its cells
+    last_read = {}  # workspace slot -> last phase that read its cells
+
+    def written(slot, index):
+        # the kernel keeps CTAs within two phases of one another: a cell buffer may be rewritten
+        # from the third phase after its last reader on
+        assert slot not in last_read or index - last_read[slot] >= 3, (slot, index, last_read[slot])
+        writers[slot] = index
+
+    for index, phase in enumerate(layout.phases):
+        assert not phase.flags & rt.FLAG_BARRIER
         if phase.body == rt.BODY_GEMV:
             tile, chunk, nmat = phase.i[rt.GV_I_ROW_TILE], phase.i[rt.GV_I_K_CHUNK], phase.i[rt.GV_I_NMAT]
-            assert tile == 8 and chunk % 32 == 0 and chunk <= phase.i[rt.GV_I_K]
+            assert tile in (8, 16) and chunk % 32 == 0 and chunk <= phase.i[rt.GV_I_K]
+            assert tile == 8 or (nmat == 1 and chunk == phase.i[rt.GV_I_K] <= 1024)
             assert tile * nmat * (chunk * 2 + 64) <= stage
             assert batch * (phase.i[rt.GV_I_K] + 32) * 2 <= layout.activation_bytes
+            cells = phase.i[rt.GV_I_CELLS]
+            # every operand written earlier in the launch names the phase that really wrote it
+            if index > 0:
+                assert cells & rt.CELLS_X_WAIT
+                assert writers[phase.slot[rt.GV_S_X]] == phase.i[rt.GV_I_X_SOURCE] < index
+                last_read[phase.slot[rt.GV_S_X]] = index
+                if not cells & rt.CELLS_X:  # plain x: its producer fenced
+                    assert layout.phases[phase.i[rt.GV_I_X_SOURCE]].flags & rt.FLAG_FENCE
+                    assert batch * phase.i[rt.GV_I_K] * 4 > planner.CELL_LIMIT_BYTES
+            if phase.slot[rt.GV_S_RESIDUAL] >= 0:
+                assert phase.slot[rt.GV_S_RESIDUAL] != phase.slot[rt.GV_S_OUT0]
+                last_read[phase.slot[rt.GV_S_RESIDUAL]] = index
+                if cells & rt.CELLS_RESIDUAL:
+                    assert writers[phase.slot[rt.GV_S_RESIDUAL]] == phase.i[rt.GV_I_RES_SOURCE] < index
+                else:
+                    assert layout.phases[writers[phase.slot[rt.GV_S_RESIDUAL]]].flags & rt.FLAG_FENCE
+            if phase.slot[rt.GV_S_XSTORE] >= 0:
+                written(phase.slot[rt.GV_S_XSTORE], index)
+            if index < len(layout.phases) - 1:
+                assert bool(cells & rt.CELLS_OUT) != bool(phase.flags & rt.FLAG_FENCE) or index == 0
+                for seg in range(phase.i[rt.GV_I_NSEG]):
+                    written(phase.slot[rt.GV_S_OUT0 + seg], index)
+            else:
+                assert not cells & rt.CELLS_OUT  # the logits are plain
+        elif phase.body == rt.BODY_ATTN_DECODE:
+            assert phase.flags & rt.FLAG_BUMP_LENGTH
+            assert phase.i[rt.AT_I_CELLS] & rt.CELLS_X
+            assert bool(phase.i[rt.AT_I_CELLS] & rt.CELLS_OUT) != bool(phase.flags & rt.FLAG_FENCE)
+            for s in (rt.AT_S_Q, rt.AT_S_K, rt.AT_S_V):
+                assert writers[phase.slot[s]] == phase.i[rt.AT_I_QKV_SOURCE] == index - 1
+                last_read[phase.slot[s]] = index
+            written(phase.slot[rt.AT_S_OUT], index)
         for slot in phase.slot:
             assert -1 <= slot < len(layout.slots)
     kinds = [s.kind for s in layout.slots]
@@ -76,6 +119,9 @@ def test_geometry_whole_rows_when_they_fit():
     assert planner.gemv_geometry(16384, 2048, 2, 148, stage, 64) == (8, 1024)
     # Qwen2's paired gate/up rows (K = 896) travel as whole rows
     assert planner.gemv_geometry(4864, 896, 2, 148, stage, 64) == (8, 896)
+    # short rows of an unpaired phase: two 8-row tiles per stage
+    assert planner.gemv_geometry(151936, 896, 1, 148, stage, 64) == (16, 896)
+    assert planner.gemv_geometry(49152, 576, 1, 148, stage, 64) == (16, 576)
     for k in (576, 896, 1536, 2048, 4864, 8192, 16384):
         for nmat in (1, 2):
             tile, chunk = planner.gemv_geometry(4096, k, nmat, 148, stage, 64)

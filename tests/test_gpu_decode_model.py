@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 
 
 class Harness:
-    def __init__(self, name, batch, capacity, seed=0):
+    def __init__(self, name, batch, capacity, seed=0, options=None):
         self.spec = models.get_spec(name)
         self.batch, self.capacity = batch, capacity
         self.weights = models.init_weights(self.spec, seed)
@@ -31,7 +31,7 @@ class Harness:
         self.dev_inv = self.inv_freq.cuda()
         self.state = models.make_state(self.spec, batch, capacity, "cuda")
         program = models.direct_program(self.spec, batch, capacity)
-        self.layout = plan_decode(program, PlannerOptions())
+        self.layout = plan_decode(program, options or PlannerOptions())
         self.ids = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
         self.pos = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
         self.args = models.direct_arguments(self.spec, self.dev_weights, self.dev_inv, self.ids,
@@ -81,6 +81,26 @@ def test_tiny_models_match_oracle(name, batch):
         ref = ref_logits[call]
         assert logits_close(logits, ref)[0], (call, max_abs(logits, ref))
         assert cosine(logits, ref) >= LOGIT_COSINE, (call, cosine(logits, ref))
+        assert greedy_pick_matches(logits[:, -1], ref[:, -1])[0], call
+    _compare_state(h, ref_state, prompt_len + steps)
+
+
+@pytest.mark.parametrize("name,batch", [("tiny-llama", 3), ("tiny-qwen2", 8), ("tiny-gemma", 1)])
+def test_tiny_models_with_cell_handoffs(name, batch):
+    """The same models with EVERY activation handed from phase to phase as flagged cells (the
+    planner's default keeps cells for q, k and v only): same answers."""
+    prompt_len, steps, capacity = 4, 4, 12
+    h = Harness(name, batch, capacity, seed=3, options=PlannerOptions(cell_limit=1 << 20))
+    assert all(p.i[20] & 1 for p in h.layout.phases[2:] if p.body == 1)  # GEMV x as cells
+    prompt = torch.randint(0, h.spec.vocab, (batch, prompt_len),
+                           generator=torch.Generator().manual_seed(7))
+    ref_ids, ref_logits, ref_state = oracle.greedy_decode(h.cfg, h.ow, prompt, steps, capacity)
+    tokens = torch.cat([prompt, ref_ids[:, prompt_len - 1:-1]], dim=1)
+    for call in range(prompt_len + steps):
+        pos = torch.full((batch, 1), call, dtype=torch.int64)
+        logits = h.step(tokens[:, call:call + 1].contiguous(), pos)
+        ref = ref_logits[call]
+        assert logits_close(logits, ref)[0], (call, max_abs(logits, ref))
         assert greedy_pick_matches(logits[:, -1], ref[:, -1])[0], call
     _compare_state(h, ref_state, prompt_len + steps)
 
