@@ -260,14 +260,16 @@ typedef struct mb_phase {
 #define MB_RP_I_INVFREQ_BF16 4
 #define MB_RP_I_K_TOKENS 5    /* > 0: k rows live in a cache, row r at (r / TOKENS) * CAPACITY   */
 #define MB_RP_I_K_CAPACITY 6  /*      + r % TOKENS                                                */
-#define MB_RP_I_LEN_VALUE 7   /* written to the int32 at MB_RP_S_LEN, if that slot is given       */
+#define MB_RP_I_LEN_VALUE 7   /* written to the int32(s) at MB_RP_S_LEN, if that slot is given    */
+#define MB_RP_I_LEN_COUNT 8   /* how many: 1 (0 means 1), or up to 256 (one per batch row)       */
 #define MB_RP_F_ROPE_SCALE 0
 #define MB_RP_F_Q_SCALE 1    /* 0 or 1 = none; else q = bf16(q * this) after the rotation  */
 #define MB_RP_S_Q 0          /* [rows, heads * D] bf16                                     */
 #define MB_RP_S_K 1          /* [rows, kv_heads * D] bf16                                  */
 #define MB_RP_S_POS 2        /* int64 [rows]                                               */
 #define MB_RP_S_INVFREQ 3    /* [D / 2]                                                    */
-#define MB_RP_S_LEN 4        /* optional int32 [1]: the layer's valid length (state handoff) */
+#define MB_RP_S_LEN 4        /* optional int32 [MB_RP_I_LEN_COUNT]: the layer's valid length(s)
+                                (state handoff)                                              */
 /* MB_BODY_ATTN_PREFILL: softmax attention with the eager operator's rounding points:
  * s = bf16(q . k), s = bf16(s * scale), s = bf16(s + mask), p = bf16(softmax_fp32(s)),
  * out = bf16(sum p v).                                                                     */

@@ -169,8 +169,8 @@ int validate_attention(const mb_plan_desc* d, const mb_phase& P) {
     for (int s = MB_AT_S_Q; s <= MB_AT_S_COUNTER; ++s)
         if (check_slot(d, P.slot[s], true)) return MB_ERR_INVALID;
     const int cells = P.i[MB_AT_I_CELLS];
-    if (cells & ~(MB_CELLS_X | MB_CELLS_OUT)) return MB_ERR_INVALID;
-    if ((cells & MB_CELLS_X) &&
+    if (cells & ~(MB_CELLS_X | MB_CELLS_OUT | MB_CELLS_X_WAIT)) return MB_ERR_INVALID;
+    if ((cells & (MB_CELLS_X | MB_CELLS_X_WAIT)) &&
         (P.i[MB_AT_I_QKV_SOURCE] < 0 ||
          static_cast<unsigned int>(P.i[MB_AT_I_QKV_SOURCE]) >= d->n_phases))
         return MB_ERR_INVALID;

@@ -1016,6 +1016,11 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
     const unsigned int out_tag = sc->tag_base + static_cast<unsigned int>(ph) + 1u;
     const int* lengths = reinterpret_cast<const int*>(entry_address(p, E, MB_AT_S_LEN));
     const bool per_row = P->i[MB_AT_I_LEN_COUNT] > 1;
+    // plain q, k and v written earlier in this launch: wait until their phase is finished
+    // everywhere (the named barrier below, or the one before the rotation, publishes it)
+    if ((cells & MB_CELLS_X_WAIT) && tid == 0 && !sc->abort_flag)
+        finished_wait(p, sc, ph, P->i[MB_AT_I_QKV_SOURCE]);
+    if ((cells & MB_CELLS_X_WAIT) && exact) named_barrier(kBarConsumers, kConsumerThreads);
     int nc = 1;
     if (!exact) {
         if (warp == 0) {
@@ -1167,6 +1172,21 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             else
                 asm volatile("cp.async.commit_group;" ::: "memory");
         }
+        // cos / sin of this row's position: independent of the projections, so before the wait
+        if (tid < D / 2) {
+            const void* invf = reinterpret_cast<const void*>(slot(MB_AT_S_INVFREQ));
+            const float f =
+                P->i[MB_AT_I_INVFREQ_BF16] != 0
+                    ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(invf)[tid])
+                    : reinterpret_cast<const float*>(invf)[tid];
+            const float angle =
+                static_cast<float>(reinterpret_cast<const long long*>(slot(MB_AT_S_POS))[b]) * f;
+            const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
+            float sn, cn;
+            sincosf(angle, &sn, &cn);
+            cs[tid] = bf16_round(cn * rope_scale);
+            cs[D / 2 + tid] = bf16_round(sn * rope_scale);
+        }
         if (in_cells) {
             // q, k and v of this (row, kv head) as flagged cells of the projection phase: load,
             // retry until they carry its sequence number, park the values in shared memory
@@ -1215,20 +1235,6 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
             cp_async16(dst + part * 8, src + part * 8);
         }
         if (!in_cells) asm volatile("cp.async.commit_group;" ::: "memory");
-        if (tid < D / 2) {
-            const void* invf = reinterpret_cast<const void*>(slot(MB_AT_S_INVFREQ));
-            const float f =
-                P->i[MB_AT_I_INVFREQ_BF16] != 0
-                    ? bf16_bits_to_float(reinterpret_cast<const unsigned short*>(invf)[tid])
-                    : reinterpret_cast<const float*>(invf)[tid];
-            const float angle =
-                static_cast<float>(reinterpret_cast<const long long*>(slot(MB_AT_S_POS))[b]) * f;
-            const float rope_scale = P->f[MB_AT_F_ROPE_SCALE];
-            float sn, cn;
-            sincosf(angle, &sn, &cn);
-            cs[tid] = bf16_round(cn * rope_scale);
-            cs[D / 2 + tid] = bf16_round(sn * rope_scale);
-        }
         uint4 kt[2][DC];
         uint4 vt[DB][4];
         if (first < blk1) {
@@ -1496,13 +1502,15 @@ __device__ __noinline__ void attention_body(const KernelParams& p, const PhaseEn
                     mx = fmaxf(mx, merge[(static_cast<size_t>(w) * group + gq) * SW]);
                 float sum_l = 0.f, sum_v = 0.f;
                 if (round > 0) {
-                    const float wgt = expf(prev[gq * SW] - mx);
+                    const float wgt = __expf(prev[gq * SW] - mx);
                     sum_l = prev[gq * SW + 1] * wgt;
                     sum_v = prev[gq * SW + col] * wgt;
                 }
                 for (int w = 0; w < live; ++w) {
                     const float* st = merge + (static_cast<size_t>(w) * group + gq) * SW;
-                    const float wgt = expf(st[0] - mx);  // 0 for a warp that saw no block
+                    // weights between partial softmax states: no rounding point of the operator
+                    // sits here, the fast exponential is accurate to 2^-21
+                    const float wgt = __expf(st[0] - mx);  // 0 for a warp that saw no block
                     sum_l += st[1] * wgt;
                     sum_v += st[col] * wgt;
                 }

@@ -81,10 +81,13 @@ __global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsig
                                                         int rows, int heads, int kv_heads, int D,
                                                         int invfreq_bf16, float rope_scale,
                                                         float q_scale, int k_tokens, int k_capacity,
-                                                        int* length, int length_value) {
+                                                        int* length, int length_value,
+                                                        int length_count) {
     const int half = D / 2;
     const long long total = static_cast<long long>(rows) * half;
-    if (length != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *length = length_value;
+    // state handoff: the layer's valid length(s), one shared by the batch or one per row
+    if (length != nullptr && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < length_count)
+        length[threadIdx.x] = length_value;
     for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
          e += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int r = static_cast<int>(e / half);
@@ -1544,7 +1547,8 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                     P.i[MB_RP_I_HEADS], P.i[MB_RP_I_KV_HEADS], P.i[MB_RP_I_HEAD_DIM],
                     P.i[MB_RP_I_INVFREQ_BF16], P.f[MB_RP_F_ROPE_SCALE], P.f[MB_RP_F_Q_SCALE],
                     P.i[MB_RP_I_K_TOKENS], P.i[MB_RP_I_K_CAPACITY],
-                    reinterpret_cast<int*>(addr(P.slot[MB_RP_S_LEN])), P.i[MB_RP_I_LEN_VALUE]);
+                    reinterpret_cast<int*>(addr(P.slot[MB_RP_S_LEN])), P.i[MB_RP_I_LEN_VALUE],
+                    P.i[MB_RP_I_LEN_COUNT] > 1 ? P.i[MB_RP_I_LEN_COUNT] : 1);
                 break;
             }
             case MB_BODY_ATTN_PREFILL: {

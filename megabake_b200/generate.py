@@ -21,14 +21,19 @@ from .hf import StatefulDecoder, StatefulPrefill
 class GreedyGenerator:
     """Compiles the two wrappers once for a (batch, prompt length, capacity) and reuses them."""
 
-    def __init__(self, model: torch.nn.Module, batch: int, prompt_tokens: int, capacity: int):
+    def __init__(self, model: torch.nn.Module, batch: int, prompt_tokens: int, capacity: int,
+                 per_row_lengths: bool = False):
+        """``per_row_lengths``: every row keeps its own valid length, so that one batch can hold
+        prompts of different lengths (``prompt_lengths`` of ``__call__``); ``prompt_tokens`` is
+        then the padded prompt length the prefill is compiled for."""
         if capacity <= prompt_tokens:
             raise ValueError("capacity must exceed the prompt length")
         self.batch, self.prompt_tokens, self.capacity = batch, prompt_tokens, capacity
+        self.per_row_lengths = per_row_lengths
         self.device = next(model.parameters()).device
         prefill = StatefulPrefill(model, capacity).eval()
         decode = StatefulDecoder(model, capacity).eval()
-        self.state = prefill.make_state(batch, device=self.device)
+        self.state = prefill.make_state(batch, device=self.device, per_row_lengths=per_row_lengths)
         self.prefill_backend = make_backend(mode="prefill")
         self.decode_backend = make_backend(mode="decode")
         self._prefill = torch.compile(prefill, backend=self.prefill_backend, fullgraph=True,
@@ -37,17 +42,37 @@ class GreedyGenerator:
                                      dynamic=False)
 
     @torch.no_grad()
-    def __call__(self, input_ids: torch.Tensor, new_tokens: int) -> torch.Tensor:
-        """``input_ids`` ``[batch, prompt_tokens]`` -> generated ids ``[batch, new_tokens]``."""
+    def __call__(self, input_ids: torch.Tensor, new_tokens: int,
+                 prompt_lengths: torch.Tensor | None = None) -> torch.Tensor:
+        """``input_ids`` ``[batch, prompt_tokens]`` -> generated ids ``[batch, new_tokens]``.
+
+        ``prompt_lengths`` (int ``[batch]``, needs ``per_row_lengths``): the real length of every
+        row's prompt; rows are padded at the end up to ``prompt_tokens`` with any valid id.  The
+        causal prefill cannot see the padding from a real position; after it the valid lengths
+        are set to the real lengths, so decode overwrites the padded rows of the caches and
+        never attends to them."""
         if tuple(input_ids.shape) != (self.batch, self.prompt_tokens):
             raise ValueError("this generator was compiled for another prompt shape")
         if self.prompt_tokens + new_tokens > self.capacity:
             raise ValueError("the KV capacity cannot hold the prompt plus the new tokens")
+        if prompt_lengths is not None and not self.per_row_lengths:
+            raise ValueError("prompt_lengths needs a generator built with per_row_lengths=True")
         logits = self._prefill(input_ids.to(self.device), *self.state)
-        token = logits[:, -1].float().argmax(-1, keepdim=True)
+        if prompt_lengths is None:
+            token = logits[:, -1].float().argmax(-1, keepdim=True)
+            position = torch.full((self.batch, 1), self.prompt_tokens, dtype=torch.int64,
+                                  device=self.device)
+        else:
+            lengths = prompt_lengths.to(self.device, torch.int64)
+            if lengths.shape != (self.batch,) or int(lengths.min()) < 1 or \
+                    int(lengths.max()) > self.prompt_tokens:
+                raise ValueError("prompt_lengths must hold one length in 1..prompt_tokens per row")
+            rows = torch.arange(self.batch, device=self.device)
+            token = logits[rows, lengths - 1].float().argmax(-1, keepdim=True)
+            position = lengths[:, None].clone()
+            for index in range(2, len(self.state), 3):
+                self.state[index].copy_(lengths.to(torch.int32))
         produced = [token]
-        position = torch.full((self.batch, 1), self.prompt_tokens, dtype=torch.int64,
-                              device=self.device)
         for _ in range(new_tokens - 1):
             logits = self._decode(token, position, *self.state)
             token = logits[:, -1].float().argmax(-1, keepdim=True)

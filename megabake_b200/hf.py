@@ -170,16 +170,22 @@ class _ExplicitState(torch.nn.Module):
     capacity: int | None
 
     def state_shapes(self, batch: int = 1, dtype: torch.dtype = torch.bfloat16,
-                     capacity: int | None = None):
+                     capacity: int | None = None, per_row_lengths: bool = False):
+        """Per layer ``[key_cache, value_cache, valid_length]``.  The valid length is int32
+        ``[1]``, shared by the batch (the reference's contract,
+        ``fx_handler/hf_attention.py:194-196``), or ``[batch]`` with ``per_row_lengths``: rows
+        then hold different numbers of keys."""
         capacity = self.capacity if capacity is None else capacity
         cache = ((batch, capacity, self.kv_heads, self.head_dim), dtype)
-        return [[cache, cache, ((1,), torch.int32)] for _ in range(self.layer_count)]
+        lengths = ((batch if per_row_lengths else 1,), torch.int32)
+        return [[cache, cache, lengths] for _ in range(self.layer_count)]
 
     def make_state(self, batch: int = 1, *, capacity: int | None = None, device=None,
-                   dtype: torch.dtype = torch.bfloat16) -> list[torch.Tensor]:
+                   dtype: torch.dtype = torch.bfloat16,
+                   per_row_lengths: bool = False) -> list[torch.Tensor]:
         """Zeroed state tensors in ``forward`` order."""
         flat = []
-        for layer in self.state_shapes(batch, dtype, capacity):
+        for layer in self.state_shapes(batch, dtype, capacity, per_row_lengths):
             for shape, kind in layer:
                 flat.append(torch.zeros(shape, dtype=kind, device=device))
         return flat

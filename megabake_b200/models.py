@@ -173,7 +173,8 @@ def direct_arguments(spec: ModelSpec, weights: dict[str, torch.Tensor], inv_freq
             *[weights[name] for name, _ in parameter_shapes(spec)]]
 
 
-def direct_program(spec: ModelSpec, batch: int, capacity: int) -> DecoderProgram:
+def direct_program(spec: ModelSpec, batch: int, capacity: int,
+                   per_row_lengths: bool = False) -> DecoderProgram:
     names = [name for name, _ in parameter_shapes(spec)]
     base = 2 + 3 * spec.layers + 1
     where = {name: base + index for index, name in enumerate(names)}
@@ -206,6 +207,7 @@ def direct_program(spec: ModelSpec, batch: int, capacity: int) -> DecoderProgram
         input_ids=0, position_ids=1, embed_weight=where["model.embed_tokens.weight"],
         inv_freq=2 + 3 * spec.layers, final_norm=where["model.norm.weight"],
         lm_head_weight=where["model.embed_tokens.weight"], layers=tuple(layers),
+        length_count=batch if per_row_lengths else 1,
     )
 
 
@@ -250,13 +252,15 @@ def direct_prefill_program(spec: ModelSpec, batch: int, tokens: int) -> DecoderP
 
 
 def make_state(spec: ModelSpec, batch: int, capacity: int, device: str | torch.device = "cpu",
-               ) -> list[torch.Tensor]:
+               per_row_lengths: bool = False) -> list[torch.Tensor]:
+    """Zeroed ``[key_cache, value_cache, valid_length]`` per layer; one valid length shared by
+    the batch, or one per row."""
     state = []
     for _ in range(spec.layers):
         shape = (batch, capacity, spec.kv_heads, spec.head_dim)
         state.append(torch.zeros(shape, dtype=torch.bfloat16, device=device))
         state.append(torch.zeros(shape, dtype=torch.bfloat16, device=device))
-        state.append(torch.zeros(1, dtype=torch.int32, device=device))
+        state.append(torch.zeros(batch if per_row_lengths else 1, dtype=torch.int32, device=device))
     return state
 
 

@@ -47,12 +47,22 @@ def kv_attention(
     valid_length: torch.Tensor,
 ) -> torch.Tensor:
     """Append ``key``/``value`` (``[batch, 1, kv_heads, dim]``) to the caches
-    (``[batch, capacity, kv_heads, dim]``) at ``valid_length`` (int32 ``[1]``,
-    shared by the batch), add one to it, and attend ``source``
-    (``[batch, 1, heads, dim]``) over every valid key."""
+    (``[batch, capacity, kv_heads, dim]``) at ``valid_length``, add one to it, and attend
+    ``source`` (``[batch, 1, heads, dim]``) over every valid key.  ``valid_length`` is int32
+    ``[1]`` (one length shared by the batch: the reference's operator,
+    ``src/megabake/ops/attention.py:52-87``) or ``[batch]`` (one length per row, so that rows may
+    hold prompts of different lengths: the reference's roadmap step 12,
+    ``docs/roadmap.md:178``); with per-row lengths every row is the shared-length operator
+    applied to that row alone."""
     batch, steps, heads, dim = source.shape
     if steps != 1:
         raise RuntimeError("megabake kv_attention supports one-token decode only")
+    if valid_length.numel() not in (1, batch):
+        raise RuntimeError(f"valid_length must hold 1 or {batch} lengths, got {valid_length.numel()}")
+    if valid_length.numel() == batch and batch > 1:
+        rows = [kv_attention(source[b:b + 1], key[b:b + 1], value[b:b + 1], key_cache[b:b + 1],
+                             value_cache[b:b + 1], valid_length[b:b + 1]) for b in range(batch)]
+        return torch.cat(rows, dim=0)
     first = int(valid_length.item())
     last = first + steps
     capacity = key_cache.shape[1]

@@ -87,6 +87,7 @@ class PlannerOptions:
     exact_keys: int = EXACT_SOFTMAX_KEYS
     stage_bytes: int | None = None  # force the ring stage size (tuning sweeps)
     cell_limit: int = CELL_LIMIT_BYTES  # largest per-CTA copy of an activation kept as cells
+    qkv_cells: bool = True  # q, k and v reach the attention items as flagged cells
 
     @classmethod
     def from_env(cls, **overrides) -> "PlannerOptions":
@@ -95,6 +96,10 @@ class PlannerOptions:
             values["row_tile"] = int(os.environ["MEGABAKE_B200_ROW_TILE"])
         if os.environ.get("MEGABAKE_B200_STAGE_BYTES"):
             values["stage_bytes"] = int(os.environ["MEGABAKE_B200_STAGE_BYTES"])
+        if os.environ.get("MEGABAKE_B200_CELL_LIMIT"):
+            values["cell_limit"] = int(os.environ["MEGABAKE_B200_CELL_LIMIT"])
+        if os.environ.get("MEGABAKE_B200_QKV_CELLS"):
+            values["qkv_cells"] = os.environ["MEGABAKE_B200_QKV_CELLS"] != "0"
         values.update(overrides)
         return cls(**values)
 
@@ -333,6 +338,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
     embed = slots.arg(p.embed_weight, "embed_tokens.weight")
     hidden_source = 0  # phase that last wrote the residual stream (buffer A): the gather
     hidden_cells, attn_cells, glu_cells = as_cells(H), as_cells(q_dim), as_cells(p.intermediate)
+    qkv_cells = options.qkv_cells
     for index, layer in enumerate(p.layers):
         tag = f"layers.{index}."
         first = index == 0
@@ -355,7 +361,9 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
             gather=first,
             store_x=hidden_a if first else -1,
             store_x_cells=hidden_cells,
-            out_fenced=first and not hidden_cells,  # the gathered rows, stored plain
+            out_cells=qkv_cells,
+            # fenced for plain q, k, v and for the gathered rows stored plain
+            out_fenced=not qkv_cells or (first and not hidden_cells),
         )
         attention = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BUMP_LENGTH
                                    | (0 if attn_cells else rt.FLAG_FENCE))
@@ -368,7 +376,8 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         attention.i[rt.AT_I_MAX_CHUNKS] = max_chunks
         attention.i[rt.AT_I_MERGE_SLOTS] = merge_slots
         attention.i[rt.AT_I_EXACT_KEYS] = exact_keys
-        attention.i[rt.AT_I_CELLS] = rt.CELLS_X | (rt.CELLS_OUT if attn_cells else 0)
+        attention.i[rt.AT_I_CELLS] = ((rt.CELLS_X if qkv_cells else rt.CELLS_X_WAIT)
+                                      | (rt.CELLS_OUT if attn_cells else 0))
         attention.i[rt.AT_I_QKV_SOURCE] = qkv_phase
         attention.i[rt.AT_I_LEN_COUNT] = p.length_count
         attention.f[rt.AT_F_SCALE] = p.softmax_scale
@@ -580,6 +589,7 @@ def plan_prefill(program: DecoderProgram, options: PlannerOptions | None = None,
         if handoff:
             rope.i[rt.RP_I_K_TOKENS], rope.i[rt.RP_I_K_CAPACITY] = T, p.capacity
             rope.i[rt.RP_I_LEN_VALUE] = T
+            rope.i[rt.RP_I_LEN_COUNT] = p.length_count
             rope.slot[rt.RP_S_LEN] = slots.arg(layer.valid_length, tag + "valid_length")
         rope.slot[rt.RP_S_POS], rope.slot[rt.RP_S_INVFREQ] = DYN_POSITION_IDS, inv_freq
         phases.append(rope)

@@ -575,6 +575,8 @@ def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
             m.refuse("gate and up projections must read one RMSNorm of the residual stream", gate.node)
         if activation not in (None, act) or norm2[3] != norm_kind:
             m.refuse("layers disagree on activation or norm spelling", gate.node)
+        if norm2[2] != eps:
+            m.refuse(f"layers disagree on the RMSNorm epsilon ({norm2[2]} vs {eps})", gate.node)
         activation = act
         # ---- attention half: h_mid = h_in + o_proj(kv_attention(rope(q), rope(k), v, state))
         pair = _binary(h_mid, aten.add.Tensor)
@@ -613,8 +615,11 @@ def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
             m.refuse("cos and sin tables disagree", q_proj.node)
         if inv_freq not in (None, tc[2]) or position not in (None, tc[3]):
             m.refuse("layers use different rotary tables", q_proj.node)
-        if q_scale not in (None, layer_q_scale) and layers:
+        # "no scale" (None) is a value like any other: every layer must agree with the first seen
+        if layers and q_scale != layer_q_scale:
             m.refuse("layers use different query scales", q_proj.node)
+        if norm1[2] != eps:
+            m.refuse(f"layers disagree on the RMSNorm epsilon ({norm1[2]} vs {eps})", q_proj.node)
         rope_scale, inv_freq, position, q_scale = tc[1], tc[2], tc[3], layer_q_scale
         if any(b is not None for b in (gate.bias, up.bias)):
             m.refuse("biased gate/up projections are not covered", gate.node)
@@ -645,7 +650,24 @@ def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
     layers.reverse()
     first = layers[0]
     cache = _val(m.placeholders[first.key_cache])
+    if cache.dim() != 4:
+        m.refuse("KV caches must be [batch, capacity, kv_heads, head_dim]")
     batch, capacity, kv_heads, head_dim = cache.shape
+    lengths = _val(m.placeholders[first.valid_length])
+    if lengths.dtype != torch.int32 or tuple(lengths.shape) not in ((1,), (batch,)):
+        m.refuse(f"valid_length must be int32 [1] (shared by the batch) or [{batch}] (one per "
+                 f"row), got {lengths.dtype} {tuple(lengths.shape)}")
+    length_count = int(lengths.shape[0])
+    for index, layer in enumerate(layers):
+        for name, position_ in (("key_cache", layer.key_cache), ("value_cache", layer.value_cache)):
+            other = _val(m.placeholders[position_])
+            if tuple(other.shape) != tuple(cache.shape) or other.dtype != cache.dtype:
+                m.refuse(f"layer {index}: {name} is {other.dtype} {tuple(other.shape)}, layer 0's "
+                         f"caches are {cache.dtype} {tuple(cache.shape)}")
+        other = _val(m.placeholders[layer.valid_length])
+        if other.dtype != torch.int32 or tuple(other.shape) != tuple(lengths.shape):
+            m.refuse(f"layer {index}: valid_length is {other.dtype} {tuple(other.shape)}, layer 0's "
+                     f"is int32 {tuple(lengths.shape)}")
     q_rows = _shape(m.placeholders[first.q_weight])[0]
     embed_weight, ids, scale_index = embed
     vocab, hidden_size = _shape(m.placeholders[head.weight])
@@ -661,7 +683,7 @@ def _recognize(graph_module: torch.fx.GraphModule, mode: str) -> DecoderProgram:
         inv_freq_dtype="bf16" if _val(m.placeholders[inv_freq]).dtype == torch.bfloat16 else "f32",
         input_ids=ids, position_ids=position, embed_weight=embed_weight, inv_freq=inv_freq,
         final_norm=final[1], lm_head_weight=head.weight, layers=tuple(layers),
-        lm_head_bias=head.bias, embed_scale_arg=scale_index,
+        lm_head_bias=head.bias, embed_scale_arg=scale_index, length_count=length_count,
     )
     return program
 
@@ -705,7 +727,7 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
         m.refuse(f"prefill takes input_ids of shape [{batch}, {tokens}]")
     # recognition runs inside the compiler's tracing modes (fake tensors): the mask constant
     # has to be computed and inspected for real
-    capacity = 0
+    capacity, length_count = 0, 1
     if first.get("causal"):  # the stateful prefill operator is causal by definition
         causal, mask_tensor = True, None
         cache = _val(m.placeholders[first["key_cache"]])
@@ -714,6 +736,11 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
         capacity = int(cache.shape[1])
         if capacity < tokens:
             m.refuse(f"prompt of {tokens} tokens exceeds the KV capacity {capacity}", first["node"])
+        lengths = _val(m.placeholders[first["valid_length"]])
+        if lengths.dtype != torch.int32 or tuple(lengths.shape) not in ((1,), (batch,)):
+            m.refuse(f"valid_length must be int32 [1] or [{batch}], got {lengths.dtype} "
+                     f"{tuple(lengths.shape)}", first["node"])
+        length_count = int(lengths.shape[0])
     elif first["mask"] is not None:
         mask = m.constant(first["mask"], graph_module)
         with _disable_current_modes():
@@ -732,4 +759,5 @@ def _prefill_program(m, graph_module, layers, calls, embed, head, final, norm_ki
         input_ids=ids, position_ids=position, embed_weight=embed_weight, inv_freq=inv_freq,
         final_norm=final[1], lm_head_weight=head.weight, layers=tuple(layers),
         lm_head_bias=head.bias, embed_scale_arg=scale_index, causal=causal, mask=mask_tensor,
+        length_count=length_count,
     )

@@ -57,7 +57,7 @@ RN_I_ROWS, RN_I_K, RN_I_KIND = 0, 1, 2
 RN_F_EPS = 0
 RN_S_X, RN_S_W, RN_S_OUT = 0, 1, 2
 RP_I_ROWS, RP_I_HEADS, RP_I_KV_HEADS, RP_I_HEAD_DIM, RP_I_INVFREQ_BF16 = 0, 1, 2, 3, 4
-RP_I_K_TOKENS, RP_I_K_CAPACITY, RP_I_LEN_VALUE = 5, 6, 7
+RP_I_K_TOKENS, RP_I_K_CAPACITY, RP_I_LEN_VALUE, RP_I_LEN_COUNT = 5, 6, 7, 8
 RP_F_ROPE_SCALE, RP_F_Q_SCALE = 0, 1
 RP_S_Q, RP_S_K, RP_S_POS, RP_S_INVFREQ, RP_S_LEN = 0, 1, 2, 3, 4
 AP_I_BATCH, AP_I_TOKENS, AP_I_HEADS, AP_I_KV_HEADS, AP_I_HEAD_DIM = 0, 1, 2, 3, 4

@@ -112,6 +112,12 @@ def kv_attention(query, key, value, key_cache, value_cache, valid_length) -> tor
     Shapes as ``megabake::kv_attention``; returns ``[B * heads, 1, D]``."""
     batch, steps, heads, dim = query.shape
     assert steps == 1
+    if valid_length.numel() == batch and batch > 1:
+        # one length per row: the shared-length operator applied to every row alone (pinned by
+        # tests/golden/ops_per_row.npz, made by calling the reference's operator row by row)
+        rows = [kv_attention(query[b:b + 1], key[b:b + 1], value[b:b + 1], key_cache[b:b + 1],
+                             value_cache[b:b + 1], valid_length[b:b + 1]) for b in range(batch)]
+        return torch.cat(rows, dim=0)
     start = int(valid_length.item())
     stop = start + 1
     if stop > key_cache.shape[1]:
@@ -255,12 +261,13 @@ def prefill(cfg: OracleConfig, w: OracleWeights, input_ids: torch.Tensor,
     return (logits, kv) if return_kv else logits
 
 
-def make_state(cfg: OracleConfig, batch: int, capacity: int, dtype=BF16) -> list[torch.Tensor]:
+def make_state(cfg: OracleConfig, batch: int, capacity: int, dtype=BF16,
+               per_row_lengths: bool = False) -> list[torch.Tensor]:
     state = []
     for _ in range(cfg.layers):
         state.append(torch.zeros(batch, capacity, cfg.kv_heads, cfg.head_dim, dtype=dtype))
         state.append(torch.zeros(batch, capacity, cfg.kv_heads, cfg.head_dim, dtype=dtype))
-        state.append(torch.zeros(1, dtype=torch.int32))
+        state.append(torch.zeros(batch if per_row_lengths else 1, dtype=torch.int32))
     return state
 
 

@@ -186,8 +186,8 @@ def test_attention_decode(batch, heads, kv_heads, dim, cached, exact):
     qd, kd, vd, kcd, vcd, invd, posd, lend = dev
     out = torch.zeros(batch, heads * dim, dtype=torch.bfloat16, device="cuda")
     max_chunks = max(1, min(64, math.ceil(capacity / 16)))
-    partial = torch.zeros(batch * kv_heads * max_chunks * group * (dim + 2), dtype=torch.float32,
-                          device="cuda")
+    partial = torch.zeros(batch * kv_heads * max_chunks * group * (dim + 2),
+                          dtype=torch.float32, device="cuda")
     counters = torch.zeros(max(4, batch * kv_heads), dtype=torch.int32, device="cuda")
     runner = PhaseRunner()
     ph = rt.Phase.blank(rt.BODY_ATTN_DECODE, rt.FLAG_BARRIER | rt.FLAG_BUMP_LENGTH)

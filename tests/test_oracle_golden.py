@@ -114,3 +114,22 @@ def test_product_operators_match_reference_ops():
         q = get("q")
         out = torch.ops.megabake.attention(q, get("k"), get("v"), get("mask"), q.shape[-1] ** -0.5)
         assert torch.equal(out, get("out"))
+
+
+@pytest.mark.parametrize("tag", ["gqa", "mqa"])
+def test_per_row_lengths_match_the_reference_operator_row_by_row(tag):
+    """``valid_length`` of shape ``[batch]``: the fixture holds the reference's operator called on
+    every row alone with that row's length; the oracle and the eager definition of
+    ``megabake::kv_attention`` must reproduce outputs, caches and lengths bit for bit."""
+    import megabake_b200  # noqa: F401  (registers the operator)
+
+    data = np.load(GOLDEN / "ops_per_row.npz")
+    for implementation in (oracle.kv_attention, torch.ops.megabake.kv_attention):
+        q, k, v = (from_bits(data[f"{tag}_{n}"]) for n in ("q", "k", "v"))
+        kc, vc = from_bits(data[f"{tag}_kc_in"]), from_bits(data[f"{tag}_vc_in"])
+        lengths = torch.from_numpy(data[f"{tag}_len_in"]).to(torch.int32)
+        out = implementation(q, k, v, kc, vc, lengths)
+        assert torch.equal(out, from_bits(data[f"{tag}_out"]))
+        assert torch.equal(kc, from_bits(data[f"{tag}_kc_out"]))
+        assert torch.equal(vc, from_bits(data[f"{tag}_vc_out"]))
+        assert lengths.tolist() == data[f"{tag}_len_out"].tolist()
