@@ -8,6 +8,7 @@ parts of it this backend keeps):
 ``graphed(function, *args)``        CUDA-graph capture of one compiled call
 ``kv_attention`` / ``attention``    the declared attention operators (``torch.ops.megabake.*``)
 ``DecodeStep``, ``StatefulDecoder`` explicit-state decode wrappers for Hugging Face models
+``GroupedStateDecoder``             the same step, state ordered all K, all V, all lengths
 ``PrefillLogits``                   ids -> logits prefill wrapper over ``megabake::attention``
 ``StatefulPrefill``                 prefill that also fills the explicit decode state
 ``GreedyGenerator``                 compiled prefill + decode loop over one KV state
@@ -20,7 +21,8 @@ from .diagnostics import CompilerDiagnostic, CompilerError
 from .ops import attention, kv_attention
 
 __all__ = [
-    "CompilerDiagnostic", "CompilerError", "DecodeStep", "GreedyGenerator", "PaddingDependence",
+    "CompilerDiagnostic", "CompilerError", "DecodeStep", "GreedyGenerator", "GroupedStateDecoder",
+    "PaddingDependence",
     "PrefillLogits", "StatefulDecoder", "StatefulPrefill", "attention", "bucketed",
     "graphed", "kv_attention", "make_backend", "register_transformers_attention",
 ]
@@ -34,8 +36,8 @@ def __getattr__(name):
     if name in ("graphed", "GraphedCall", "BoundDecoder"):
         from . import engine
         return getattr(engine, name)
-    if name in ("DecodeStep", "PrefillLogits", "StatefulDecoder", "StatefulPrefill",
-                "register_transformers_attention"):
+    if name in ("DecodeStep", "GroupedStateDecoder", "PrefillLogits", "StatefulDecoder",
+                "StatefulPrefill", "register_transformers_attention"):
         from . import hf
         return getattr(hf, name)
     if name in ("bucketed", "PaddingDependence"):

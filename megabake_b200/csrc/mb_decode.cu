@@ -1811,7 +1811,9 @@ decode_kernel(const __grid_constant__ KernelParams p) {
             ++barrier_index;
             ok = grid_barrier(p.ctl, base + barrier_index, kBarConsumers, kConsumerThreads, tid,
                               &sc->abort_flag, &sc->verdict, p.n_phases, sc->limit_ns);
-            if (ok && blockIdx.x == 0) {
+            // a launch that recorded a fault anywhere (a token outside the table ...) leaves the
+            // lengths and the launch counters alone: the host has to reset the plan anyway
+            if (ok && blockIdx.x == 0 && peek_status(p.ctl) == 0) {
                 // valid_length += 1 for every attention phase that asks for it, one thread per
                 // phase (the table is in L2: the producers prefetched it)
                 for (int q = tid; q < p.n_phases; q += kConsumerThreads) {

@@ -25,6 +25,8 @@ Inductor, Triton or CPU execution path behind a compiled call.
 from __future__ import annotations
 
 import dataclasses
+import json
+import time
 from pathlib import Path
 from types import MappingProxyType
 from typing import Any, Callable, Mapping, Sequence
@@ -94,20 +96,58 @@ class PreparedFX:
     program: Any = None  # DecoderProgram once recognised
 
 
+def _microseconds(start: float) -> float:
+    return (time.perf_counter() - start) * 1e6
+
+
+def _phase_table(layout) -> dict:
+    """The planned phase records and slot layout as plain data (``dump_dir``)."""
+    from . import runtime as rt
+
+    return {
+        "mode": "prefill" if layout.mode == rt.MODE_PREFILL else "decode",
+        "notes": list(layout.notes), "workspace_bytes": layout.workspace_bytes,
+        "activation_bytes": layout.activation_bytes, "stage_bytes": layout.stage_bytes,
+        "slots": [dataclasses.asdict(slot) for slot in layout.slots],
+        "phases": [{"body": phase.body, "flags": phase.flags, "i": list(phase.i),
+                    "f": [float(x) for x in phase.f], "slot": list(phase.slot)}
+                   for phase in layout.phases],
+    }
+
+
 class _MegakernelCall:
     """Boxed callable AOTAutograd invokes with the flat graph inputs; plans and binds on the
     first real call (capture-time inputs may be fake tensors), launches on every call."""
 
     _boxed_call = True
 
-    def __init__(self, program, owner):
+    def __init__(self, program, owner, options, plan_cache, trace):
         self.program = program
         self.owner = owner
+        self.options = options
+        self.plan_cache = plan_cache
+        self.trace = trace
         self.decoder = None
+
+    def _plan(self, program, device_index):
+        from .cache import make_plan_key
+        from .planner import PlannerOptions, plan_decode, plan_prefill
+
+        planner_options = PlannerOptions.resolve(program, device_index)
+
+        def build():
+            if program.mode == "prefill":
+                return plan_prefill(program, mask=program.mask)
+            return plan_decode(program, planner_options)
+
+        if self.plan_cache is None:
+            return build(), False
+        key = make_plan_key(program, planner_options, device_index=device_index, mask=program.mask)
+        result = self.plan_cache.get_or_compile(key, build)
+        return result.compiled, result.hit
 
     def __call__(self, args: list) -> list:
         from .engine import BoundDecoder
-        from .planner import plan_decode, plan_prefill
 
         flat = list(args)
         args.clear()
@@ -116,17 +156,29 @@ class _MegakernelCall:
             if program.embed_scale_arg is not None:
                 scale = float(flat[program.embed_scale_arg].float().reshape(-1)[0])
                 program = dataclasses.replace(program, embed_scale=scale)
-            if program.mode == "prefill":
-                layout = plan_prefill(program, mask=program.mask)
-            else:
-                layout = plan_decode(program)
+            device = flat[program.input_ids].device
+            started = time.perf_counter()
+            layout, hit = self._plan(program, device.index)
+            self.trace.append({"stage": "planning", "us": _microseconds(started),
+                               "plan_cache_hit": hit, "phases": len(layout.phases)})
+            started = time.perf_counter()
             self.decoder = BoundDecoder(layout, flat)
+            self.trace.append({"stage": "runtime-binding", "us": _microseconds(started)})
+            self.decoder.megabake_trace = self.trace
             self.owner.megabake_last_callable = self.decoder
+            self.owner.megabake_last_compile_us = sum(entry["us"] for entry in self.trace)
+            dump_dir = self.options["dump_dir"]
+            if dump_dir is not None:
+                target = Path(dump_dir)
+                target.mkdir(parents=True, exist_ok=True)
+                (target / f"{self.options['model_name']}.{program.mode}.phases.json").write_text(
+                    json.dumps(_phase_table(layout), indent=1) + "\n")
         return [self.decoder(*flat)]
 
 
 def _capture(graph: torch.fx.GraphModule, example_inputs: Sequence[Any], options: dict,
-             compile_kernel: bool, owner) -> PreparedFX:
+             compile_kernel: bool, owner, capture_cache=None, plan_cache=None,
+             trace: list | None = None) -> PreparedFX:
     from torch._functorch.aot_autograd import aot_module_simplified
     from torch._inductor.compile_fx import make_boxed_func
     from torch._inductor.decomposition import select_decomp_table
@@ -134,16 +186,40 @@ def _capture(graph: torch.fx.GraphModule, example_inputs: Sequence[Any], options
     from . import ops  # noqa: F401  (the declared operators must be registered before tracing)
 
     captured: dict[str, Any] = {}
+    trace = trace if trace is not None else []
+    capture_started = time.perf_counter()
 
     def inference_compiler(aten_graph: torch.fx.GraphModule, inputs):
         captured["graph"] = aten_graph
+        trace.append({"stage": "fx-capture", "us": _microseconds(capture_started),
+                      "nodes": len(aten_graph.graph.nodes)})
+        dump_dir = options["dump_dir"]
+        if dump_dir is not None:  # the captured ATen graph, as the reference dumps it
+            target = Path(dump_dir)
+            target.mkdir(parents=True, exist_ok=True)
+            (target / f"{options['model_name']}.{options['mode']}.aten.txt").write_text(
+                aten_graph.print_readable(print_output=False) + "\n")
         if not compile_kernel:
             return make_boxed_func(aten_graph.forward)
+        from .cache import graph_key
         from .recognize import recognize_decoder
 
-        program = recognize_decoder(aten_graph, options["mode"])
+        started = time.perf_counter()
+        if capture_cache is not None:
+            program, hit = capture_cache.get_or_recognize(
+                graph_key(aten_graph, options["mode"]),
+                lambda: recognize_decoder(aten_graph, options["mode"]))
+        else:
+            program, hit = recognize_decoder(aten_graph, options["mode"]), False
+        trace.append({"stage": "semantic-lowering", "us": _microseconds(started),
+                      "capture_cache_hit": hit})
         captured["program"] = program
-        return _MegakernelCall(program, owner)
+        if dump_dir is not None:
+            (Path(dump_dir) / f"{options['model_name']}.{options['mode']}.program.json").write_text(
+                json.dumps({f.name: repr(getattr(program, f.name))
+                            for f in dataclasses.fields(program) if f.name != "mask"}, indent=1)
+                + "\n")
+        return _MegakernelCall(program, owner, options, plan_cache, trace)
 
     with torch.no_grad():
         forward = aot_module_simplified(
@@ -161,8 +237,26 @@ def make_backend(**options: Any) -> Callable[..., Any]:
     """Create a ``torch.compile`` backend.  Options: ``mode`` ("prefill" | "decode"),
     ``fallback`` ("error" | "inductor"; never taken), ``cache``, ``model_name``, ``dump_dir``,
     ``compile_kernel`` (True | False | None = automatic), ``scheduler``."""
+    from .cache import CaptureCache, PlanCache
+
     validated = _validate_options(options)
     contexts: list[PreparedFX] = []
+    # cache=True (the default): recognised programs and planned layouts are kept for the life of
+    # the backend; cache=False: every compile recognises and plans afresh (reference
+    # frontend.py:555-561)
+    cache = CaptureCache() if validated["cache"] else None
+    plan_cache = PlanCache() if validated["cache"] else None
+
+    def prepare(graph: Any, example_inputs: Sequence[Any], *,
+                input_kinds: Mapping[str, str] | None = None,
+                parameter_names: set[str] | None = None, **_unused: Any) -> PreparedFX:
+        """Capture only: the ATen-level graph and a callable that runs it through ATen (the
+        reference's ``backend.megabake_prepare``, ``frontend.py:563-585``)."""
+        del input_kinds, parameter_names
+        _reject_symbolic_shapes(graph)
+        prepared = _capture(graph, example_inputs, validated, False, backend)
+        contexts.append(prepared)
+        return prepared
 
     def backend(graph: Any, example_inputs: Sequence[Any], *,
                 input_kinds: Mapping[str, str] | None = None,
@@ -178,8 +272,12 @@ def make_backend(**options: Any) -> Callable[..., Any]:
         compile_kernel = choice is True or (choice is None and _can_auto_compile(example_inputs))
         backend.megabake_last_compiled = None
         backend.megabake_last_callable = None
+        backend.megabake_last_compile_us = None
+        trace: list[dict] = []
+        backend.megabake_last_trace = trace if compile_kernel else None
         try:
-            prepared = _capture(graph, example_inputs, validated, compile_kernel, backend)
+            prepared = _capture(graph, example_inputs, validated, compile_kernel, backend,
+                                cache, plan_cache, trace)
         except CompilerError as error:
             error.safe_for_fallback = False  # there is nothing to fall back to
             raise
@@ -188,13 +286,21 @@ def make_backend(**options: Any) -> Callable[..., Any]:
         backend.megabake_last_fallback = None
         if compile_kernel:
             backend.megabake_last_compiled = prepared.program
+            backend.megabake_last_compile_us = sum(entry["us"] for entry in trace)
         forward = prepared.forward
         try:
             forward.megabake_contexts = contexts
+            forward.megabake_cache = cache
+            forward.megabake_plan_cache = plan_cache
         except AttributeError:  # some callables refuse attributes; the backend keeps them
             pass
         return forward
 
+    backend.megabake_cache = cache
+    backend.megabake_plan_cache = plan_cache
+    backend.megabake_prepare = prepare
+    backend.megabake_last_compile_us = None
+    backend.megabake_last_trace = None
     backend.megabake_contexts = contexts
     backend.megabake_options = MappingProxyType(validated)
     backend.megabake_last_prepared = None

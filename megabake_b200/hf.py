@@ -19,6 +19,15 @@ Two wrappers produce that convention:
                      counterpart of the reference's benchmark wrapper
                      ``benchmarks/stateful_models.py:152-187``, restricted to
                      attention layers, and batch-aware in ``state_shapes``.
+``GroupedStateDecoder`` the same step with the state in the order of the reference's Llama
+                     wrapper (``tests/fixtures.py:236-238``): all key caches, then all value
+                     caches, then all valid lengths.
+
+``megabake_attention_forward``, ``megabake_decode_attention``,
+``register_transformers_attention`` and ``_PassThroughLayer`` below restate the reference's
+``src/megabake/fx_handler/hf_attention.py:28-162`` closely -- same branches, same error texts:
+they are the operator boundary a model written against the reference binds to, and their
+signatures are dictated by ``transformers``' ``AttentionInterface`` and cache protocol.
 """
 
 from __future__ import annotations
@@ -268,6 +277,25 @@ class StatefulDecoder(_ExplicitState):
             hidden = hidden + mixed
             hidden = hidden + layer.mlp(layer.post_attention_layernorm(hidden))
         return self.lm_head(self.model.norm(hidden))
+
+
+class GroupedStateDecoder(StatefulDecoder):
+    """``StatefulDecoder`` with the state tensors grouped by kind instead of by layer:
+    ``forward(input_ids, position_ids, K_0..K_{L-1}, V_0..V_{L-1}, len_0..len_{L-1})`` -- the
+    calling convention of the reference's ``StatefulSmolLM`` (``tests/fixtures.py:220-238``), which
+    its benchmark uses for Llama-family models (``benchmarks/full_model.py:235-255``)."""
+
+    def state_shapes(self, batch: int = 1, dtype: torch.dtype = torch.bfloat16,
+                     capacity: int | None = None, per_row_lengths: bool = False):
+        per_layer = super().state_shapes(batch, dtype, capacity, per_row_lengths)
+        return [[layer[kind] for layer in per_layer] for kind in range(3)]
+
+    def forward(self, input_ids: torch.Tensor, position_ids: torch.Tensor, *state: torch.Tensor):
+        count = self.layer_count
+        if len(state) != 3 * count:
+            raise ValueError(f"expected {3 * count} state tensors, got {len(state)}")
+        by_layer = [state[kind * count + index] for index in range(count) for kind in range(3)]
+        return super().forward(input_ids, position_ids, *by_layer)
 
 
 class PrefillLogits(torch.nn.Module):

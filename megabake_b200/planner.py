@@ -88,9 +88,23 @@ class PlannerOptions:
     stage_bytes: int | None = None  # force the ring stage size (tuning sweeps)
     cell_limit: int = CELL_LIMIT_BYTES  # largest per-CTA copy of an activation kept as cells
     qkv_cells: bool = True  # q, k and v reach the attention items as flagged cells
+    distinct_buffers: bool = False  # every layer gets activation buffers of its own (race check:
+    #                                 the results must not depend on the buffers being reused)
 
     @classmethod
-    def from_env(cls, **overrides) -> "PlannerOptions":
+    def resolve(cls, program, device_index: int | None = None, **overrides) -> "PlannerOptions":
+        """Options for one program: defaults, then the tuning file's choice for this model shape
+        and device (``cache.tuned_choice``), then the sweep variables of ``from_env``, then
+        ``overrides``."""
+        from .cache import tuned_choice
+
+        values = dict(tuned_choice(program, device_index))
+        values.update(cls._env_values())
+        values.update(overrides)
+        return cls(**values)
+
+    @staticmethod
+    def _env_values() -> dict:
         values = {}
         if os.environ.get("MEGABAKE_B200_ROW_TILE"):
             values["row_tile"] = int(os.environ["MEGABAKE_B200_ROW_TILE"])
@@ -100,6 +114,13 @@ class PlannerOptions:
             values["cell_limit"] = int(os.environ["MEGABAKE_B200_CELL_LIMIT"])
         if os.environ.get("MEGABAKE_B200_QKV_CELLS"):
             values["qkv_cells"] = os.environ["MEGABAKE_B200_QKV_CELLS"] != "0"
+        return values
+
+    @classmethod
+    def from_env(cls, **overrides) -> "PlannerOptions":
+        """Defaults plus the sweep variables (``MEGABAKE_B200_STAGE_BYTES`` ...): for tuning runs
+        that compare settings inside one process; measured choices belong in the tuning file."""
+        values = cls._env_values()
         values.update(overrides)
         return cls(**values)
 
@@ -237,7 +258,7 @@ def plan_decode(program: DecoderProgram, options: PlannerOptions | None = None) 
     """Plan one decode step.  The ring stage size is the library's largest unless forced:
     measured on B200, smaller stages (a deeper ring) never paid -- the consumers' per-stage
     work, not the bytes in flight, bounds the weight stream."""
-    options = options or PlannerOptions.from_env()
+    options = options or PlannerOptions.resolve(program)
     largest = rt.load_library().mb_stage_bytes(rt.MODE_DECODE)
     return _plan_decode(program, options, options.stage_bytes or largest)
 
@@ -275,6 +296,20 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
     activation = attention_scratch_bytes(D, p.group, merge_slots)
 
     phases: list[rt.Phase] = []
+    if options.distinct_buffers:
+        shared = dict(hidden_a=hidden_a, hidden_b=hidden_b, hidden_c=hidden_c, q=q_buf, k=k_buf,
+                      v=v_buf, attention=attn, gated=glu)
+        widths = dict(hidden_a=H, hidden_b=H, hidden_c=H, q=q_dim, k=kv_dim, v=kv_dim,
+                      attention=q_dim, gated=p.intermediate)
+
+    def layer_buffers(index: int):
+        """The activation buffers layer ``index`` works in: the shared set, or its own."""
+        if not options.distinct_buffers or index == 0:
+            return hidden_a, hidden_b, hidden_c, q_buf, k_buf, v_buf, attn, glu
+        own = {name: slots.buffer(B * widths[name] * 4, f"{name}.{index}", zero=True)
+               for name in shared}
+        return (own["hidden_a"], own["hidden_b"], own["hidden_c"], own["q"], own["k"], own["v"],
+                own["attention"], own["gated"])
 
     def as_cells(width: int) -> bool:
         return B * width * 4 <= options.cell_limit
@@ -337,12 +372,19 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
     inv_freq = slots.arg(p.inv_freq, "inv_freq")
     embed = slots.arg(p.embed_weight, "embed_tokens.weight")
     hidden_source = 0  # phase that last wrote the residual stream (buffer A): the gather
+    stream = hidden_a  # the buffer that holds the residual stream at the start of a layer
     hidden_cells, attn_cells, glu_cells = as_cells(H), as_cells(q_dim), as_cells(p.intermediate)
     qkv_cells = options.qkv_cells
     for index, layer in enumerate(p.layers):
         tag = f"layers.{index}."
         first = index == 0
-        layer_in, layer_out = (hidden_a, hidden_c) if index % 2 == 0 else (hidden_c, hidden_a)
+        if options.distinct_buffers:
+            # the layer reads what the previous layer's `down` wrote and writes buffers of its own
+            _, hidden_b, layer_out, q_buf, k_buf, v_buf, attn, glu = layer_buffers(index + 1)
+            layer_in = stream
+        else:
+            layer_in, layer_out = (hidden_a, hidden_c) if index % 2 == 0 else (hidden_c, hidden_a)
+        stream_in, stream = layer_in, layer_out
         qkv_phase = gemv(
             k=H,
             segments=[
@@ -359,7 +401,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
             prologue=pro,
             norm_slot=slots.arg(layer.input_norm, tag + "input_layernorm.weight"),
             gather=first,
-            store_x=hidden_a if first else -1,
+            store_x=stream_in if first else -1,
             store_x_cells=hidden_cells,
             out_cells=qkv_cells,
             # fenced for plain q, k, v and for the gathered rows stored plain
@@ -444,7 +486,7 @@ def _plan_decode(program: DecoderProgram, options: PlannerOptions, stage_bytes: 
         k=H,
         segments=[(p.vocab, slots.arg(p.lm_head_weight, "lm_head.weight"),
                    slots.arg(p.lm_head_bias, "lm_head.bias"), DYN_LOGITS)],
-        x_slot=hidden_a if len(p.layers) % 2 == 0 else hidden_c,
+        x_slot=stream,
         x_source=hidden_source,
         x_cells=hidden_cells,
         prologue=pro,

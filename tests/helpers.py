@@ -41,10 +41,11 @@ class PhaseRunner:
         return self.names[name]
 
     def run(self, phases, activation_bytes: int = 0, ctas: int = 0,
-            mode: int = rt.MODE_DECODE) -> rt.Plan:
+            mode: int = rt.MODE_DECODE, wait_limit_ms: int = 0) -> rt.Plan:
         plan = rt.Plan(list(phases), n_slots=len(self.tensors), n_dynamic=0,
                        activation_bytes=(activation_bytes + 127) // 128 * 128,
-                       device=self.device.index or 0, ctas=ctas, mode=mode)
+                       device=self.device.index or 0, ctas=ctas, mode=mode,
+                       wait_limit_ms=wait_limit_ms)
         plan.bind([t.data_ptr() for t in self.tensors])
         plan.launch([], torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()

@@ -192,3 +192,95 @@ def test_bucketed_prefill_serves_odd_prompt_lengths():
         decoder.check()
         planned.append(decoder.program.tokens)  # the plan of the most recent capture
     assert planned == [16, 32, 32] and call.verified == {16, 32}  # the third call reused bucket 16
+
+
+def test_second_compile_of_the_same_graph_hits_the_plan_cache(tmp_path):
+    """Two wrapper instances over one model under one backend: the second compile finds the
+    recognised program and the planned phase table in the backend's caches; ``dump_dir`` holds
+    the captured graph, the program and the phase table; the trace lists the stages."""
+    import json
+
+    batch, capacity = 2, 12
+    spec, wrapper, cfg, ow = _setup("tiny-qwen2", "stateful", batch, capacity)
+    backend = make_backend(mode="decode", dump_dir=tmp_path, model_name="qwen")
+    ids = torch.randint(0, spec.vocab, (batch, 1), generator=torch.Generator().manual_seed(1)).cuda()
+    pos = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+    outputs = []
+    for attempt in range(2):
+        instance = StatefulDecoder(_hf_model_of(wrapper), capacity).eval()
+        torch._dynamo.reset()
+        step = torch.compile(instance, backend=backend, fullgraph=True, dynamic=False)
+        state = instance.make_state(batch, device="cuda")
+        with torch.no_grad():
+            outputs.append(step(ids, pos, *state).clone())
+        backend.megabake_last_callable.check()
+        cache = backend.megabake_plan_cache
+        assert (cache.misses, cache.hits) == (1, attempt)
+        trace = backend.megabake_last_trace
+        assert [entry["stage"] for entry in trace] == ["fx-capture", "semantic-lowering",
+                                                       "planning", "runtime-binding"]
+        assert trace[2]["plan_cache_hit"] == bool(attempt)
+        assert backend.megabake_last_compile_us >= sum(entry["us"] for entry in trace[:2])
+        assert backend.megabake_last_callable.megabake_trace is trace
+    assert torch.equal(outputs[0], outputs[1])
+    table = json.loads((tmp_path / "qwen.decode.phases.json").read_text())
+    assert len(table["phases"]) == 5 * spec.layers + 1 and table["mode"] == "decode"
+    assert (tmp_path / "qwen.decode.aten.txt").exists()
+    assert (tmp_path / "qwen.decode.program.json").exists()
+    # cache=False plans afresh every time
+    fresh = make_backend(mode="decode", cache=False)
+    torch._dynamo.reset()
+    step = torch.compile(StatefulDecoder(_hf_model_of(wrapper), capacity).eval(), backend=fresh,
+                         fullgraph=True, dynamic=False)
+    with torch.no_grad():
+        again = step(ids, pos, *wrapper.make_state(batch, device="cuda"))
+    assert fresh.megabake_plan_cache is None and torch.equal(again, outputs[0])
+
+
+def _hf_model_of(wrapper):
+    """The Hugging Face causal LM a ``StatefulDecoder`` was built from."""
+    class _Model(torch.nn.Module):
+        def __init__(self, inner, head, config):
+            super().__init__()
+            self.model, self.lm_head, self.config = inner, head, config
+
+    return _Model(wrapper.model, wrapper.lm_head, wrapper.config)
+
+
+def test_grouped_state_order_matches_the_reference_llama_wrapper():
+    """The state order of the reference's Llama wrapper (all K, all V, all lengths) against the
+    fixture that wrapper itself produced."""
+    import json
+    from pathlib import Path
+
+    import numpy as np
+
+    from megabake_b200 import GroupedStateDecoder
+
+    golden = Path(__file__).parent / "golden"
+    meta = json.loads((golden / "index.json").read_text())["decode_tiny-llama_smollm"]
+    data = np.load(golden / "decode_tiny-llama_smollm.npz")
+    spec = models.get_spec(meta["model"])
+    weights = models.init_weights(spec, meta["seed"])
+    model = models.build_hf_model(spec, meta["seed"], device="cuda",
+                                  weights={k: v.cuda() for k, v in weights.items()})
+    wrapper = GroupedStateDecoder(model, meta["capacity"]).eval()
+    state = wrapper.make_state(meta["batch"], device="cuda")
+    count = spec.layers
+    assert [tuple(t.shape) for t in state[2 * count:]] == [(1,)] * count      # lengths come last
+    backend = make_backend(mode="decode")
+    torch._dynamo.reset()
+    step = torch.compile(wrapper, backend=backend, fullgraph=True, dynamic=False)
+    tokens = torch.from_numpy(data["tokens"])
+    with torch.no_grad():
+        for call in range(meta["calls"]):
+            pos = torch.full((meta["batch"], 1), call, dtype=torch.int64, device="cuda")
+            got = step(tokens[:, call:call + 1].contiguous().cuda(), pos, *state)
+            ref = torch.from_numpy(data["logits"][call].copy()).view(torch.bfloat16)
+            assert logits_close(got, ref)[0], (call, max_abs(got, ref))
+            assert greedy_pick_matches(got[:, -1], ref[:, -1])[0]
+    backend.megabake_last_callable.check()
+    for index in range(count):
+        assert int(state[2 * count + index]) == meta["calls"]
+        ref_k = torch.from_numpy(data[f"k{index}"].copy()).view(torch.bfloat16)
+        assert max_abs(state[index].cpu(), ref_k) <= 6e-2

@@ -88,10 +88,26 @@ def _static_step(tensors, batch, heads, kv_heads, dim, capacity, status):
     return out
 
 
+def _oracle_step(tensors, batch, heads, kv_heads, dim):
+    """The CPU oracle on copies of the inputs: a second judge, independent of the kernel code
+    the two entry points share."""
+    from oracle import decoder_oracle as oracle
+
+    q, k, v, kc, vc, inv_freq, pos, length = (t.cpu().clone() for t in tensors)
+    cos, sin = oracle.rotary_tables(inv_freq, pos, 1.0)
+    q_r = oracle.apply_rope(q.view(batch, 1, heads, dim), cos, sin)
+    k_r = oracle.apply_rope(k.view(batch, 1, kv_heads, dim), cos, sin)
+    out = oracle.kv_attention(q_r, k_r, v.view(batch, 1, kv_heads, dim), kc, vc, length)
+    return out.reshape(batch, heads * dim), kc, vc, length
+
+
 @pytest.mark.parametrize("batch,heads,kv_heads,dim,cached", [
     (2, 14, 2, 64, 700),     # split keys: partials and arrival counters in the static array
     (1, 32, 8, 64, 40),      # short context: exact softmax, no partials
     (2, 4, 2, 128, 2500),
+    (1, 8, 1, 256, 300),     # 256-wide heads, eight query heads on one kv head
+    (2, 4, 2, 64, 126),      # the two calls cross from the exact softmax (<= 128 keys) ...
+    (2, 4, 2, 64, 127),      # ... to the split one
 ])
 def test_static_attention_matches_plan_path_twice(batch, heads, kv_heads, dim, cached):
     capacity = cached + 8
@@ -108,14 +124,59 @@ def test_static_attention_matches_plan_path_twice(batch, heads, kv_heads, dim, c
                 static_side[index].copy_(fresh)
             plan_side[6].add_(1)
             static_side[6].add_(1)
+        reference, ref_kc, ref_vc, ref_len = _oracle_step(static_side, batch, heads, kv_heads, dim)
         expected = _plan_step(plan_side, batch, heads, kv_heads, dim, capacity)
         got = _static_step(static_side, batch, heads, kv_heads, dim, capacity, status)
         torch.cuda.synchronize()
+        # against the oracle: result within the attention tolerance of the body tests, appended
+        # value row and length exact
+        assert float((got.cpu().float() - reference.float()).abs().max()) <= 2e-2
+        assert int(static_side[7].item()) == int(ref_len)
+        assert torch.equal(static_side[4].cpu(), ref_vc)
+        assert float((static_side[3].cpu().float() - ref_kc.float()).abs().max()) <= 0.04
         assert int(status.item()) == 0
         assert int(static_side[7].item()) == cached + call + 1 == int(plan_side[7].item())
         assert torch.equal(static_side[3], plan_side[3])      # key cache, appended row included
         assert torch.equal(static_side[4], plan_side[4])
         assert torch.equal(got, expected)
+
+
+def test_static_attention_reports_a_full_cache():
+    """valid_length == capacity: nothing may be appended.  The call is non-blocking, so the fault
+    arrives through ``status``: MB_ST_KV_OVERFLOW, with the caches and the length untouched; the
+    next call (room again) works."""
+    batch, heads, kv_heads, dim, capacity = 2, 4, 2, 64, 24
+    tensors = _inputs(batch, heads, kv_heads, dim, capacity, capacity, seed=5)
+    before = [t.clone() for t in tensors]
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    _static_step(tensors, batch, heads, kv_heads, dim, capacity, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 3                       # MB_ST_KV_OVERFLOW
+    assert int(tensors[7].item()) == capacity            # length untouched
+    assert torch.equal(tensors[3], before[3]) and torch.equal(tensors[4], before[4])
+    tensors[7].fill_(capacity - 1)
+    tensors[6].fill_(capacity - 1)
+    reference, _, _, _ = _oracle_step(tensors, batch, heads, kv_heads, dim)
+    got = _static_step(tensors, batch, heads, kv_heads, dim, capacity, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(tensors[7].item()) == capacity
+    assert float((got.cpu().float() - reference.float()).abs().max()) <= 2e-2
+
+
+def test_static_attention_rejects_misaligned_arguments():
+    lib = rt.load_library()
+    tensors = _inputs(1, 4, 2, 64, 3, 8, seed=1)
+    q, k, v, kc, vc, inv_freq, pos, length = tensors
+    out = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    base = dict(batch=1, heads=4, kv_heads=2, head_dim=64, capacity=8, inv_freq_is_bf16=1,
+                rope_scale=1.0, query_scale=0.0, query=q.data_ptr(), key=k.data_ptr(),
+                value=v.data_ptr(), key_cache=kc.data_ptr(), value_cache=vc.data_ptr(),
+                valid_length=length.data_ptr(), position_ids=pos.data_ptr(),
+                inv_freq=inv_freq.data_ptr(), out=out.data_ptr(), status=0)
+    for name, offset in (("position_ids", 4), ("valid_length", 2), ("query", 8), ("status", 1)):
+        args = rt.AttentionArgs(**dict(base, **{name: (base[name] or length.data_ptr()) + offset}))
+        assert lib.mb_attention_decode_static(ctypes.byref(args), None) == 1, name   # MB_ERR_INVALID
+    torch.cuda.synchronize()
 
 
 def test_static_attention_rejects_what_the_array_cannot_hold():
