@@ -12,8 +12,12 @@ number of keys (filled by a seeded prefill of uniform-random token ids).  Prints
 * ``e2e``        the same metric through the public API -- ``torch.compile(StatefulDecoder(model),
                  backend=make_backend(mode="decode"))`` captured with ``megabake_b200.graphed`` --
                  with HOST buffers: per step a pinned host->device copy of token and position ids,
-                 the graph replay (one megakernel launch), a device argmax of the logits and a
-                 device->host read of the picked ids, synchronised every step
+                 the graph replay (the megakernel launch and the greedy pick of every row on the
+                 device, ``mb_greedy_advance``) and a device->host read of the picked ids,
+                 synchronised every step
+* ``parity``     one more step of the benched workload, outside every timed region, by the kernel
+                 and by the CPU oracle on copies of the same KV cache: max-abs and cosine of the
+                 logits, greedy ids, and both forwards' distance from the fp32 forward
 * ``device_loop`` the same compiled step with the next token picked on the device
                  (``mb_greedy_advance``) and 8 steps per CUDA graph replay: no host work per token,
                  the picked ids are read once at the end (host wall clock)
@@ -190,8 +194,80 @@ def whole_job_rate(units_per_rank: float, world: int, seconds: float) -> float:
     return units_per_rank * world / seconds
 
 
+def decode_config(workload: str, world: int, cache_fill: str) -> dict:
+    """The workload description both arms print (the same keys and values, so that the two lines
+    can be compared field by field); what is particular to an arm goes elsewhere in its line."""
+    from megabake_b200 import models
+
+    preset, batch, keys = WORKLOADS[workload]
+    spec = models.get_spec(preset)
+    bytes_per_step = (models.direct_program(spec, batch, keys + 1).weight_bytes()
+                      + batch * keys * models.direct_program(spec, batch, keys + 1).kv_bytes_per_key())
+    return {
+        "workload": workload, "model": spec.name, "batch_per_gpu": batch, "cached_keys": keys,
+        "replicas": world, "parallelism": f"dp{world} replicas",
+        "weights": "seeded N(0,0.02) random init, tied embeddings", "cache_fill": cache_fill,
+        "l2": f"inputs larger than L2: weights + KV read per step {bytes_per_step / 1e6:.0f} MB "
+              "vs 126 MB L2",
+    }
+
+
+def prefill_config(workload: str, world: int) -> dict:
+    from megabake_b200 import models
+
+    preset, batch, tokens = PREFILL_WORKLOADS[workload]
+    spec = models.get_spec(preset)
+    gemm_flops, _ = prefill_flops(spec, tokens)
+    return {
+        "workload": workload, "model": spec.name, "batch_per_gpu": batch, "prompt_tokens": tokens,
+        "replicas": world, "parallelism": f"dp{world} replicas",
+        "weights": "seeded N(0,0.02) random init, tied embeddings",
+        "l2": f"inputs larger than L2: {gemm_flops / (2 * tokens) * 2 / 1e6:.0f} MB of weights read "
+              "per step vs 126 MB L2",
+    }
+
+
 def algorithmic_bytes(spec, program, batch: int, mean_keys: float) -> float:
     return program.weight_bytes() + batch * mean_keys * program.kv_bytes_per_key()
+
+
+def parity_check(spec, weights, inv_freq, state, ids, position, decoder, ids_dev, pos_dev,
+                 logits) -> dict:
+    """One decode step by the kernel against the CPU oracle on copies of the same state."""
+    import torch
+
+    from oracle import decoder_oracle as oracle
+    from oracle.adapters import oracle_config, oracle_weights
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cpu_weights = {k: v.cpu() for k, v in weights.items()}
+    cfg = oracle_config(spec)
+    ref_state = [t.cpu() for t in state]
+    wide_state = [t.float() if t.dtype == torch.bfloat16 else t.clone() for t in ref_state]
+    pos = torch.full((ids.shape[0], 1), position, dtype=torch.int64)
+    with torch.no_grad():
+        reference = oracle.decode_step(cfg, oracle_weights(cpu_weights, inv_freq.cpu()), ids, pos,
+                                       ref_state)
+        wide = oracle.decode_step(cfg, oracle_weights({k: v.float() for k, v in cpu_weights.items()},
+                                                      inv_freq.cpu().float()), ids, pos, wide_state)
+    decoder.launch_into(ids_dev, pos_dev, logits)
+    decoder.check()
+    got = logits.float().cpu()
+    ref = reference.float()
+
+    def cos(a, b):
+        a, b = a.double().flatten(), b.double().flatten()
+        return float(a @ b / (a.norm() * b.norm()))
+
+    return {
+        "max_abs": float((got - ref).abs().max()), "cosine": cos(got, ref),
+        "greedy_ids_equal": bool(torch.equal(got[:, -1].argmax(-1), ref[:, -1].argmax(-1))),
+        "kernel_vs_fp32_max_abs": float((got - wide).abs().max()),
+        "eager_vs_fp32_max_abs": float((ref - wide).abs().max()),
+        "kernel_vs_fp32_cosine": cos(got, wide), "eager_vs_fp32_cosine": cos(ref, wide),
+        "against": "CPU oracle (the reference's eager bf16 forward) and the same forward in fp32, "
+                   "one step on the benched weights and KV cache",
+    }
 
 
 def cpu_reference_run(name: str, steps: int, warmup: int, budget_s: float, rank: int = 0) -> dict:
@@ -391,15 +467,9 @@ def run_prefill(args) -> None:
             "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {
-                "workload": args.workload, "model": spec.name, "batch_per_gpu": batch,
-                "prompt_tokens": tokens, "replicas": world, "parallelism": f"dp{world} replicas",
-                "weights": "seeded N(0,0.02) random init, tied embeddings",
-                "l2": f"inputs larger than L2: {2 * gemm_flops / (2 * tokens * batch) / 1e6:.0f} MB "
-                      "of weights read per step vs 126 MB L2",
-                "kernel_launches_per_step": launches,
-                "attention_tflop_per_step": attn_flops / 1e12,
-            },
+            "config": prefill_config(args.workload, world),
+            "plan": {"kernel_launches_per_step": launches,
+                     "attention_tflop_per_step": attn_flops / 1e12},
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": None,
@@ -429,38 +499,42 @@ def run_prefill(args) -> None:
 
 
 def run_reference(args) -> None:
+    """The reference's own CPU implementation of the path -- its eager forward, restated in
+    ``oracle/`` and pinned bit for bit to fixtures the reference produced -- on this box's host
+    cores, on the same workload, metric and unit as the GPU arm.  Its compiled sm100 kernels need
+    torch 2.14 and CuTe-DSL 4.8, neither of which exists on the box, so no GPU number of the
+    reference can be measured here."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    steps, warmup = args.steps, max(args.warmup, 3)
     if args.workload in PREFILL_WORKLOADS:
-        result = cpu_prefill_run(args.workload, args.steps, budget_s=120.0)
-        preset, batch, tokens = PREFILL_WORKLOADS[args.workload]
+        result = cpu_prefill_run(args.workload, steps, budget_s=120.0)
         emit({
             "impl": "reference", "metric": "prefill_tokens_per_s", "value": result["value"],
-            "unit": "tok/s", "n_gpus": args.gpus, "steps": result["steps"], "warmup": 0,
+            "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "steps_timed": result["steps"],
             "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "model": preset, "batch": batch,
-                       "prompt_tokens": tokens, "device": "host cpu"},
+            "config": prefill_config(args.workload, world),
             "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": result["value"], "unit": "tok/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
-            "gpu_launches": 0,
+            "gpu_launches": 0, "device": "host cpu",
         })
         return
-    result = cpu_reference_run(args.workload, args.steps, min(args.warmup, 2), budget_s=120.0)
-    preset, batch, keys = WORKLOADS[args.workload]
+    result = cpu_reference_run(args.workload, steps, warmup, budget_s=120.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT,
-        "n_gpus": args.gpus, "steps": result["steps"], "warmup": min(args.warmup, 2),
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "steps_timed": result["steps"],
         "ms_per_step": result["ms_per_step"], "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "model": preset, "batch": batch,
-                   "cached_keys": keys, "device": "host cpu"},
+        "config": decode_config(args.workload, world, args.cache_fill),
         "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": result["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "device": "host cpu",
     }
     emit(line)
 
@@ -486,7 +560,7 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=device)
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    total_calls = 3 * (steps + warmup) + 96  # three timed loops plus graph warm-ups
+    total_calls = 3 * (steps + warmup) + 97  # three timed loops, graph warm-ups, the parity step
     spec, batch, keys, capacity, weights, inv_freq, state = build_workload(
         args.workload, rank, total_calls, device, args.cache_fill)
     program = models.direct_program(spec, batch, capacity)
@@ -524,6 +598,20 @@ def run_ours(args) -> None:
     device_ms = start.elapsed_time(stop)
     mean_keys = first_key + (steps - 1) / 2 + 1
 
+    # ---- parity of the benched workload (outside every timed region) ---------------------------
+    # One more step of this very workload -- same weights, same KV cache as it stands now -- by
+    # the kernel and by the CPU oracle (and by the oracle in fp32, the yardstick of the
+    # reference's own long-context test): rank 0 only, skipped when the host copy would be huge.
+    parity = None
+    state_bytes = sum(t.numel() * t.element_size() for t in state)
+    if rank == 0 and not args.no_parity and state_bytes <= 6 << 30:
+        parity = parity_check(spec, weights, inv_freq, state, ids, keys + call, decoder, ids_dev,
+                              pos_all[call], logits)
+        call += 1
+    elif rank == 0:
+        parity = {"skipped": "--no-parity" if args.no_parity else
+                  f"KV state of {state_bytes / 2**30:.1f} GiB: covered by tests/test_gpu_config_parity.py"}
+
     # ---- end-to-end timing through the public API -------------------------------------------
     # torch.compile(wrapper, backend=make_backend(mode="decode")) captured once in a CUDA graph
     # with megabake_b200.graphed (the reference's own recipe for steady-state decode).  Per
@@ -534,7 +622,7 @@ def run_ours(args) -> None:
     if args.skip_e2e:
         return _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, None,
                        mean_keys, {"ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages},
-                       sampler, rank, world, distributed, device)
+                       sampler, rank, world, distributed, device, parity=parity)
     plan_info = {"ctas": decoder.plan.ctas, "ring_stages": decoder.plan.stages}
     decoder.close()
     del decoder
@@ -550,16 +638,26 @@ def run_ours(args) -> None:
     dev_ids = torch.empty_like(ids_dev)
     dev_pos = torch.full((batch, 1), keys + call, dtype=torch.int64, device=device)
     dev_ids.copy_(ids_dev)
+    from megabake_b200 import runtime as rt
+
+    dev_pick = torch.zeros(batch, 1, dtype=torch.int64, device=device)
+
+    def step_and_pick(token, position, *kv_state):
+        # the compiled step, then the greedy pick of every row on the device (mb_greedy_advance):
+        # two launches in one CUDA graph
+        rt.greedy_advance(step_fn(token, position, *kv_state), dev_pick)
+        return dev_pick
+
     with torch.no_grad():
-        graph_call = graphed(step_fn, dev_ids, dev_pos, *state)
+        graph_call = graphed(step_and_pick, dev_ids, dev_pos, *state)
     compiled_decoder = backend.megabake_last_callable
 
     def e2e_step(index: int):
         host_pos.fill_(keys + index)
         dev_ids.copy_(host_ids, non_blocking=True)
         dev_pos.copy_(host_pos, non_blocking=True)
-        out = graph_call(dev_ids, dev_pos, *state)
-        host_pick.copy_(out[:, -1].argmax(-1), non_blocking=True)
+        picked = graph_call(dev_ids, dev_pos, *state)
+        host_pick.copy_(picked[:, 0], non_blocking=True)
         torch.cuda.synchronize()
 
     for _ in range(warmup):
@@ -578,8 +676,6 @@ def run_ours(args) -> None:
     # The same compiled step, but the next token is picked by mb_greedy_advance on the device and
     # LOOP_STEPS x (decode launch, pick) are captured in one CUDA graph: the host only replays
     # graphs and reads all picked ids once at the end.
-    from megabake_b200 import runtime as rt
-
     per_graph = LOOP_STEPS
     replays = max(1, steps // per_graph)
     picked = torch.zeros(batch, (replays + 4) * per_graph, dtype=torch.int64, device=device)
@@ -609,11 +705,11 @@ def run_ours(args) -> None:
             "d2h_bytes": host_picks.numel() * 8}
 
     return _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s,
-                   mean_keys, plan_info, sampler, rank, world, distributed, device, loop)
+                   mean_keys, plan_info, sampler, rank, world, distributed, device, loop, parity)
 
 
 def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, e2e_s, mean_keys,
-            plan_info, sampler, rank, world, distributed, device, loop=None) -> None:
+            plan_info, sampler, rank, world, distributed, device, loop=None, parity=None) -> None:
     import torch
 
     device_ms, e2e_ms, loop_ms = max_over_ranks(
@@ -630,17 +726,10 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {
-                "workload": args.workload, "model": spec.name, "batch_per_gpu": batch,
-                "cached_keys": keys, "replicas": world, "parallelism": f"dp{world} replicas",
-                "weights": "seeded N(0,0.02) random init, tied embeddings",
-                "cache_fill": args.cache_fill,
-                "l2": "inputs larger than L2: weights + KV read per step "
-                      f"{bytes_per_launch / 1e6:.0f} MB vs 126 MB L2",
-                "tokens_per_s": whole_job_rate(batch, world, ms_per_step * 1e-3),
-                "phases": len(layout.phases), "barrier_intervals": layout.intervals,
-                "ctas": plan_info["ctas"], "ring_stages": plan_info["ring_stages"],
-            },
+            "config": decode_config(args.workload, world, args.cache_fill),
+            "plan": {"tokens_per_s": whole_job_rate(batch, world, ms_per_step * 1e-3),
+                     "phases": len(layout.phases), "grid_barriers": layout.intervals,
+                     "ctas": plan_info["ctas"], "ring_stages": plan_info["ring_stages"]},
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": ncu_traffic(args.workload),
@@ -651,12 +740,14 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
                 "value": e2e_ms * 1e3 / steps / (batch * world), "unit": UNIT,
                 "h2d_bytes_per_step": 2 * batch * 8, "d2h_bytes_per_step": batch * 8,
                 "ms_per_step": e2e_ms / steps,
-                "path": "torch.compile(StatefulDecoder, backend=make_backend(mode='decode')) under "
-                        "megabake_b200.graphed + torch argmax, synchronised every step",
+                "path": "torch.compile(StatefulDecoder, backend=make_backend(mode='decode')) + the "
+                        "on-device greedy pick under megabake_b200.graphed; pinned host ids in, "
+                        "picked ids out, synchronised every step",
             },
-            "gpu_launches": steps,
+            "gpu_launches": steps,  # one decode_kernel per step in the timed resident loop
             "clocks": sampler.summary(),
         }
+        line["parity"] = parity
         if loop is not None:
             line["device_loop"] = {
                 "value": loop_ms * 1e3 / loop["steps"] / (batch * world), "unit": UNIT,
@@ -702,6 +793,8 @@ def main() -> None:
                         choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-parity", action="store_true",
+                        help="skip the one-step comparison with the CPU oracle")
     parser.add_argument("--skip-e2e", action="store_true",
                         help="profiler runs: only the resident-input loop (e2e is reported null)")
     parser.add_argument("--cache-fill", default="prefill", choices=["prefill", "random"],

@@ -71,3 +71,20 @@ def test_reference_arm_runs_on_rank_zero_only():
     assert line["metric"] == "decode_us_per_token" and line["unit"] == "us/token"
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["value"] > 0
+
+
+def test_both_arms_describe_the_workload_identically():
+    """The reference arm and the GPU arm print the same ``config`` for the same command line."""
+    import bench
+
+    for name in ("qwen2-0.5b-b8-k4096", "smollm-135m-b1-k32"):
+        config = bench.decode_config(name, 2, "prefill")
+        assert set(config) == {"workload", "model", "batch_per_gpu", "cached_keys", "replicas",
+                               "parallelism", "weights", "cache_fill", "l2"}
+        assert config["replicas"] == 2 and config["workload"] == name
+    spoken = _run_reference(0)
+    line = json.loads(spoken.stdout.strip().splitlines()[-1])
+    assert line["config"] == bench.decode_config("smollm-135m-b1-k32", 2, "prefill")
+    assert line["steps"] == 1 and line["warmup"] == 3 and line["steps_timed"] >= 1
+    prefill = bench.prefill_config("gemma-2b-prefill-t128", 1)
+    assert prefill["prompt_tokens"] == 128 and prefill["model"] == "gemma-2b"

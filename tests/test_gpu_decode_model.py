@@ -126,21 +126,21 @@ def test_smollm_135m_protocol():
                    for a, b in zip(got_logits, ref_logits)) / len(ref_logits)
     print(f"config-1 protocol: worst max-abs {worst:.4f}, worst cosine {worst_cos:.6f}, "
           f"mean abs {mean_abs:.5f}")
-    # 30 layers deep, logits of magnitude 2-4 (bf16 spacing 0.0156): two correct
-    # implementations that merely sum in a different fp32 order already differ by 0.031 at the
-    # worst of the 64 x 49152 logits (measured on CPU: the same forward with an fp32 GEMM
-    # instead of the bf16 one).  The 3e-2 bound therefore holds on average and per call for
-    # almost all calls; the worst single logit is allowed twice that noise floor.
-    assert worst <= 2 * 0.031, worst
-    assert mean_abs <= 8e-3, mean_abs
+    # 30 layers deep, logits of magnitude 2-4 (bf16 spacing 0.0156): two correct CPU forwards that
+    # merely accumulate their GEMMs differently (exactly in fp64, in fp32, in fp32 blocks) already
+    # differ from the eager bf16 forward by 0.029-0.032 at the worst of the 64 x 49152 logits, with
+    # a worst cosine of 0.99990 and 61-64 of the 64 calls inside 3e-2
+    # (tests/test_noise_floor.py measures exactly this protocol).  The kernel adds the device
+    # sincosf and the split-key softmax to that; measured: worst 0.049, worst cosine 0.99979,
+    # mean abs 0.0050.  The bounds sit just above the measurement and within twice the floor.
+    assert worst <= 0.056, worst
+    assert mean_abs <= 6.5e-3, mean_abs
     cosines = sorted(cosine(a, b) for a, b in zip(got_logits, ref_logits))
     assert cosines[len(cosines) // 2] >= LOGIT_COSINE, cosines[len(cosines) // 2]
-    # the worst of 64 calls sits at the noise floor itself: the CPU forward with an fp32 GEMM
-    # instead of the bf16 one scores 0.99990 against the bf16 forward
-    assert worst_cos >= 0.9995, worst_cos
+    assert worst_cos >= 0.9997, worst_cos
     within = sum(max_abs(a, b) <= LOGIT_MAX_ABS for a, b in zip(got_logits, ref_logits))
-    # calls whose worst logit stays within 3e-2: all 64 for an exact (fp64) GEMM on CPU, 62 for
-    # an fp32 GEMM, 40 when only the softmax probabilities are left unrounded
+    print(f"config-1 protocol: {within} of {len(ref_logits)} calls within 3e-2, median cosine "
+          f"{cosines[len(cosines) // 2]:.6f}")
     assert within >= 0.6 * len(ref_logits), within
     _compare_state(h, ref_state, 64)
 
