@@ -184,11 +184,9 @@ def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, 
         tile = forced_row_tile
     elif nmat == 1 and 2 * ROW_TILE * (k * 2 + row_pad) <= stage_bytes:
         tile = 2 * ROW_TILE
-    if tile == 2 * ROW_TILE:
-        return tile, k
-    limit = ((stage_bytes // (ROW_TILE * nmat)) - row_pad) // 2 // 32 * 32
+    limit = ((stage_bytes // (tile * nmat)) - row_pad) // 2 // 32 * 32
     if limit < 32:
-        fail("resource-admission", f"a ring stage cannot hold 8 rows of {nmat} matrices")
+        fail("resource-admission", f"a ring stage cannot hold {tile} rows of {nmat} matrices")
     chunks = math.ceil(k / min(limit, k))
     k_chunk = _align(math.ceil(k / chunks), 64)
     if k_chunk > limit:
@@ -196,7 +194,7 @@ def gemv_geometry(n_total: int, k: int, nmat: int, ctas: int, stage_bytes: int, 
     while k_chunk > limit:
         chunks += 1
         k_chunk = _align(math.ceil(k / chunks), 32)
-    return ROW_TILE, min(k_chunk, k)
+    return tile, min(k_chunk, k)
 
 
 def attention_state_bytes(head_dim: int, group: int, merge_slots: int) -> int:

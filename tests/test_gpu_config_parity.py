@@ -158,13 +158,14 @@ def test_decode_config_matches_oracle(name, preset, layers, batch, keys):
         assert torch.equal(kc[:, used:], k0[:, used:]) and torch.equal(vc[:, used:], v0[:, used:])
         new_k, new_v = kc[:, keys:used].cpu(), vc[:, keys:used].cpu()
         wide_k, wide_v = wide_state[3 * index][:, keys:used], wide_state[3 * index + 1][:, keys:used]
-        assert max_abs(new_k, rk[:, keys:used]) <= 6e-2
-        assert max_abs(new_v, rv[:, keys:used]) <= 6e-2
         # deep layers inherit the rounding noise of the layers below: as close to the fp32
         # forward's rows as the eager rows are (twice their distance at most)
         for mine, eager, truth in ((new_k, rk[:, keys:used], wide_k), (new_v, rv[:, keys:used], wide_v)):
-            assert cosine(mine, eager) > 0.9998
-            assert 1 - cosine(mine, truth) <= 2 * (1 - cosine(eager, truth)) + 1e-5
+            # (rows of magnitude 2-8 in deep layers: one bf16 step there is 0.016-0.03)
+            assert max_abs(mine, truth) <= 1.5 * max_abs(eager, truth) + 1.6e-2, (
+                index, max_abs(mine, truth), max_abs(eager, truth))
+            assert 1 - cosine(mine, truth) <= 2 * (1 - cosine(eager, truth)) + 1e-5, (
+                index, cosine(mine, truth), cosine(eager, truth))
     decoder.close()
 
 
