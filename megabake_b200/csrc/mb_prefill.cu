@@ -230,6 +230,7 @@ struct GemmArgs {
     int n[3];
     int tile_start[3];  // first n-tile of each segment
     int tiles_n;        // n-tiles over all segments
+    int tiles_m;        // 128-row m-tiles (persistent kernel)
     unsigned short* out[3];
     const unsigned short* bias[3];
     const unsigned short* residual;
@@ -501,6 +502,298 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
         __syncthreads();
     }
     if (warp == 1) tmem_dealloc(tmem_base, BN);
+    if (threadIdx.x == 32) stamp(6);
+}
+
+// ---------------------------------------------------------------------------------------
+// The persistent GEMM: one CTA per SM walks output tiles (m-tiles fastest, so the CTAs that run
+// together share a weight tile), with the three roles decoupled across tiles:
+//   warp 0      TMA producer: keeps the operand ring (192 KB) full, across tile boundaries
+//   warp 1      MMA issuer: accumulates tile j into tensor-memory buffer j & 1
+//   warps 2-9   epilogue: drain buffer j & 1 while the MMAs of tile j + 1 fill the other one;
+//               warps 2-5 take the first half of the tile's output columns, warps 6-9 the
+//               second half (a warp reads the 32 TMEM lanes of its index modulo 4)
+// Measured on the one-tile-per-CTA kernel at 2048 rows: two co-resident CTAs start together
+// and stay in step, so their epilogues (a third of a CTA's life) leave the tensor cores
+// idle; here the epilogue of a tile is hidden behind the next tile's MMAs by construction,
+// and a ring twice as deep per CTA covers the load latency of single-wave problems.
+// The epilogue stores straight from registers: a lane owns 64 contiguous bytes of its output
+// row per 32-column chunk (whole 32-byte sectors), so no staging tile and no second pass.
+// ---------------------------------------------------------------------------------------
+constexpr int kPersistThreads = 320;
+constexpr int kPersistRingBytes = 192 * 1024;
+constexpr int kPersistSmemBytes = kPersistRingBytes + 256 + 1024;  // ring + barriers + alignment slack
+
+__device__ __forceinline__ void tmem_load32_pair(unsigned int addr_v, unsigned int addr_u, bool pair,
+                                                 float (&v)[32], float (&u)[32]) {
+    unsigned int r[32], q[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr_v)
+        : "memory");
+    if (pair) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]),
+              "=r"(q[7]), "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]),
+              "=r"(q[13]), "=r"(q[14]), "=r"(q[15]), "=r"(q[16]), "=r"(q[17]), "=r"(q[18]),
+              "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]), "=r"(q[24]),
+              "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]),
+              "=r"(q[31])
+            : "r"(addr_u)
+            : "memory");
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = __uint_as_float(r[i]);
+        u[i] = pair ? __uint_as_float(q[i]) : 0.f;
+    }
+}
+
+// Epilogue of one 32-column chunk of this thread's output row, registers -> global memory.
+// h: the residual's 32 values of the same place (read before the accumulators were awaited),
+// used by the fast path only.
+__device__ __forceinline__ void gemm_store_chunk(const GemmArgs& a, int seg, int row, int col0,
+                                                 const float (&v)[32], const float (&u)[32],
+                                                 const uint4 (&h)[4], bool fast) {
+    const int n = a.n[seg];
+    const int width = min(32, n - col0);
+    const unsigned short* bias = a.bias[seg];
+    float y[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float b = (bias != nullptr && i < width) ? bf16_bits_to_float(__ldg(bias + col0 + i)) : 0.f;
+        y[i] = bf16_round(v[i] + b);
+    }
+    if (a.epilogue == MB_EPI_SILU_MUL) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = bf16_round(silu_f32(y[i])) * bf16_round(u[i]);
+    } else if (a.epilogue == MB_EPI_GELU_TANH_MUL) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = bf16_round(gelu_tanh_f32(y[i])) * bf16_round(u[i]);
+    }
+    if (row >= a.M) return;
+    const size_t out_row = (seg >= 1 && a.out_tokens > 0)
+                               ? static_cast<size_t>(row / a.out_tokens) * a.out_capacity + row % a.out_tokens
+                               : static_cast<size_t>(row);
+    const size_t at = out_row * n + col0;
+    unsigned short* out = a.out[seg] + at;
+    if (fast) {
+        const bool res = a.epilogue == MB_EPI_RESIDUAL;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const unsigned int hw[4] = {h[q].x, h[q].y, h[q].z, h[q].w};
+            unsigned int t[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                t[e] = pack_bf16(y[8 * q + 2 * e], y[8 * q + 2 * e + 1]);
+                if (res) t[e] = pack_bf16(lo_bf16(hw[e]) + lo_bf16(t[e]), hi_bf16(hw[e]) + hi_bf16(t[e]));
+            }
+            reinterpret_cast<uint4*>(out)[q] = make_uint4(t[0], t[1], t[2], t[3]);
+        }
+    } else {
+        const unsigned short* res = a.epilogue == MB_EPI_RESIDUAL ? a.residual + at : nullptr;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < width) {
+                float r = bf16_round(y[i]);
+                if (res != nullptr) r = bf16_bits_to_float(res[i]) + r;
+                out[i] = float_to_bf16_bits(r);
+            }
+        }
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kPersistThreads, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
+    constexpr int kStageW = BN * kTileK * 2;
+    constexpr int kStage = kStageA + kStageW;
+    constexpr int kStages = kPersistRingBytes / kStage;  // 4 at BN = 256, 6 at BN = 128
+    constexpr int kHalf = BN / 2;                        // columns per matrix of a gated pair
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + kStages * kStage);
+    unsigned long long* empty = full + 8;
+    unsigned long long* acc_full = empty + 8;
+    unsigned long long* acc_empty = acc_full + 2;
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool traced = a.trace != nullptr && blockIdx.x == 0;
+    auto stamp = [&](int slot) {
+        if (traced) a.trace[slot] = global_timer_ns();
+    };
+    if (threadIdx.x == 0) stamp(0);
+    const int total = a.tiles_n * a.tiles_m;
+    const int per_tile = a.pair ? kHalf : BN;  // output columns of one n-tile
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned int tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) stamp(1);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0, round = 0;  // ring position; `round` counts wraps
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int mt = t % a.tiles_m, tile = t / a.tiles_m;
+                const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
+                const int n0 = (tile - a.tile_start[seg]) * per_tile;
+                const int m0 = mt * kTileM;
+                for (int kb = 0; kb < a.kblocks; ++kb) {
+                    if (round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1, abort_flag)) {
+                        record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 1);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* stage = smem + s * kStage;
+                    mbar_arrive_expect_tx(&full[s], kStage);
+                    const int kx = kb * kTileK;
+                    tma_load_2d(stage, &maps.a, kx, m0, &full[s]);
+                    if (a.pair) {
+                        tma_load_2d(stage + kStageA, &maps.w[0], kx, n0, &full[s]);
+                        tma_load_2d(stage + kStageA + kHalf * kTileK * 2, &maps.w[3], kx, n0, &full[s]);
+                    } else {
+                        tma_load_2d(stage + kStageA, &maps.w[seg], kx, n0, &full[s]);
+                    }
+                    if (++s == kStages) {
+                        s = 0;
+                        ++round;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, both operands K-major,
+            // N = BN, M = 128
+            const unsigned int idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       (static_cast<unsigned int>(BN >> 3) << 17) |
+                                       (static_cast<unsigned int>(kTileM >> 4) << 24);
+            int s = 0, round = 0, j = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++j) {
+                const int buf = j & 1;
+                // the epilogue must have drained this buffer's previous tile
+                if (j >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((j >> 1) - 1) & 1, abort_flag)) {
+                    record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 4);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const unsigned int acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < a.kblocks; ++kb) {
+                    if (!mbar_wait_bounded(&full[s], round & 1, abort_flag)) {
+                        record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 2);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    if (j == 0 && kb == 0) stamp(2);
+                    const unsigned int base = smem_u32(smem + s * kStage);
+                    const unsigned long long da = umma_desc(base);
+                    const unsigned long long db = umma_desc(base + kStageA);
+#pragma unroll
+                    for (int k = 0; k < kTileK / 16; ++k)  // 32 bytes along K per step: +2 encoded
+                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                    if (++s == kStages) {
+                        s = 0;
+                        ++round;
+                    }
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+                if (j == 0) stamp(3);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;        // the TMEM lanes a warp may read: 32 * (warp % 4) ...
+        const int column_half = (warp - 2) >> 2;
+        const int chunks = per_tile / 32;
+        const int c_begin = column_half * (chunks / 2), c_end = c_begin + chunks / 2;
+        int j = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++j) {
+            const int buf = j & 1;
+            const int mt = t % a.tiles_m, tile = t / a.tiles_m;
+            const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
+            const int n0 = (tile - a.tile_start[seg]) * per_tile;
+            const int row = mt * kTileM + quarter * 32 + lane;
+            const int n = a.n[seg];
+            // warp-uniform: the tcgen05.ld below must be executed by whole warps
+            const bool ok = __all_sync(0xffffffffu,
+                                       mbar_wait_bounded(&acc_full[buf], (j >> 1) & 1, abort_flag));
+            if (!ok) {
+                if (lane == 0) record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 3);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            if (j == 0 && threadIdx.x == 64) stamp(4);
+            const unsigned int lane_addr =
+                tmem_base + buf * BN + (static_cast<unsigned int>(quarter * 32) << 16);
+            const bool row_fast = (n & 7) == 0;
+            for (int c = c_begin; c < c_end; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= n) break;
+                const bool fast = row_fast && col0 + 32 <= n;
+                uint4 h[4] = {};
+                if (fast && a.epilogue == MB_EPI_RESIDUAL && row < a.M) {
+                    const uint4* src =
+                        reinterpret_cast<const uint4*>(a.residual + static_cast<size_t>(row) * n + col0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) h[q] = src[q];
+                }
+                float v[32], u[32];
+                tmem_load32_pair(lane_addr + c * 32, lane_addr + kHalf + c * 32, a.pair != 0, v, u);
+                gemm_store_chunk(a, seg, row, col0, v, u, h, fast);
+            }
+            // this warp's reads of the buffer are complete: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (j == 0 && threadIdx.x == 64) stamp(5);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // copies this CTA issued may still be landing in its shared memory: give them time
+        const unsigned long long start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
     if (threadIdx.x == 32) stamp(6);
 }
 
@@ -1188,6 +1481,8 @@ int gemm_smem_bytes(int bn, int stages) {
 
 struct GemmGeometry {
     int bn, stages, tiles_n, tiles_m, split_k, kblocks;
+    int persistent;  // 1: gemm_tc_persistent_kernel on `grid` CTAs
+    int grid;
     int tile_start[3];
 };
 
@@ -1206,6 +1501,20 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         return tiles;
     };
     g.bn = count(256) * g.tiles_m >= sm_count ? 256 : 128;
+    // the persistent kernel once its tiles fill most of the machine: wide tiles from 80 % of
+    // the SMs on (a single wave of them moves a third less operand bytes than two CTAs per SM
+    // on narrow ones), narrow tiles when only those reach one per SM
+    g.persistent = 0;
+    const char* persistent_env = std::getenv("MEGABAKE_B200_GEMM_PERSISTENT");
+    if (persistent_env == nullptr || std::atoi(persistent_env) != 0) {
+        if (count(256) * g.tiles_m * 5 >= sm_count * 4) {
+            g.persistent = 1;
+            g.bn = 256;
+        } else if (count(128) * g.tiles_m >= sm_count) {
+            g.persistent = 1;
+            g.bn = 128;
+        }
+    }
     if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_BN")) {
         const int value = std::atoi(forced);
         if (value == 128 || value == 256) g.bn = value;
@@ -1238,7 +1547,9 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         const int value = std::atoi(forced);
         if (value >= 1 && value <= 16 && value <= g.kblocks) split = value;
     }
+    if (g.persistent) split = 1;
     g.split_k = split;
+    g.grid = g.tiles_n * g.tiles_m < sm_count ? g.tiles_n * g.tiles_m : sm_count;
     return g;
 }
 
@@ -1387,6 +1698,12 @@ cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillS
         err = cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gemm_smem_bytes(256, 4));
     if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(gemm_tc_persistent_kernel<128>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSmemBytes);
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(gemm_tc_persistent_kernel<256>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSmemBytes);
+    if (err == cudaSuccess)
         err = cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    attention_tc_smem_bytes(64));
     if (err == cudaSuccess)
@@ -1439,6 +1756,7 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
             a.out_tokens = P.i[MB_GV_I_OUT_TOKENS];
             a.out_capacity = P.i[MB_GV_I_OUT_CAPACITY];
             a.tiles_n = g.tiles_n;
+            a.tiles_m = g.tiles_m;
             for (int s = 0; s < 3; ++s) {
                 a.n[s] = s < a.nseg ? P.i[MB_GV_I_N0 + s] : 0;
                 a.tile_start[s] = g.tile_start[s];
@@ -1526,7 +1844,13 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                 args.trace = trace == nullptr ? nullptr : trace + 8 * i;
                 for (int s = 0; s < args.nseg; ++s)  // outputs may be per-launch tensors (logits)
                     args.out[s] = reinterpret_cast<unsigned short*>(addr(P.slot[MB_GV_S_OUT0 + s]));
-                if (g.bn == 256)
+                if (g.persistent && g.bn == 256)
+                    gemm_tc_persistent_kernel<256>
+                        <<<g.grid, kPersistThreads, kPersistSmemBytes, stream>>>(L.maps, args);
+                else if (g.persistent)
+                    gemm_tc_persistent_kernel<128>
+                        <<<g.grid, kPersistThreads, kPersistSmemBytes, stream>>>(L.maps, args);
+                else if (g.bn == 256)
                     gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem_bytes(256, g.stages), stream>>>(
                         L.maps, args);
                 else
