@@ -30,6 +30,19 @@
 namespace mb {
 namespace prefill {
 
+// Programmatic dependent launch: a phase's kernel is launched while the previous phase's
+// kernel is still draining, runs its prologue (barrier set-up, tensor-memory allocation)
+// beside it, and blocks in chain_wait() until that kernel has completed and its writes are
+// visible.  chain_release() lets the next kernel in the stream start its own prologue; in
+// kernels that allocate tensor memory it comes after the allocation, so a successor never
+// queues for columns ahead of a CTA of this grid.
+__device__ __forceinline__ void chain_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void chain_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // Row kernels
 // ---------------------------------------------------------------------------------------
@@ -39,6 +52,8 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const unsigned short* t
                                                          int vocab, float scale, Control* ctl,
                                                          int phase) {
     const int r = blockIdx.x;
+    chain_release();
+    chain_wait();
     if (r >= rows) return;
     long long id = ids[r];
     if (id < 0 || id >= vocab) {
@@ -61,6 +76,8 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(const unsigned short*
                                                            int kind, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + warp;
+    chain_release();
+    chain_wait();
     if (r >= rows) return;
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * K);
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * K);
@@ -85,6 +102,8 @@ __global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsig
                                                         int length_count) {
     const int half = D / 2;
     const long long total = static_cast<long long>(rows) * half;
+    chain_release();
+    chain_wait();
     // state handoff: the layer's valid length(s), one shared by the batch or one per row
     if (length != nullptr && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < length_count)
         length[threadIdx.x] = length_value;
@@ -357,6 +376,8 @@ gemm_tc_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs a) {
     __syncthreads();
     tc_fence_after();
     const unsigned int tmem_base = *tmem_slot;
+    chain_release();
+    chain_wait();  // nothing above reads or writes global memory
     if (threadIdx.x == 0) stamp(1);
 
     if (warp == 0) {
@@ -636,8 +657,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
         if (traced) a.trace[slot] = global_timer_ns();
     };
     if (threadIdx.x == 0) stamp(0);
-    const int total = a.tiles_n * a.tiles_m;
+    // work units: (output tile, slice of the reduction), slices of a tile adjacent so that they
+    // finish together and the last one to arrive finds the others' partial sums in L2
+    const int total = a.tiles_n * a.tiles_m * a.split_k;
     const int per_tile = a.pair ? kHalf : BN;  // output columns of one n-tile
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -656,18 +680,23 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
     __syncthreads();
     tc_fence_after();
     const unsigned int tmem_base = *tmem_slot;
+    chain_release();
+    chain_wait();  // nothing above reads or writes global memory
     if (threadIdx.x == 0) stamp(1);
 
     if (warp == 0) {
         if (lane == 0) {
             int s = 0, round = 0;  // ring position; `round` counts wraps
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            for (int unit = blockIdx.x; unit < total && ok; unit += gridDim.x) {
+                const int t = unit / a.split_k, z = unit - t * a.split_k;
                 const int mt = t % a.tiles_m, tile = t / a.tiles_m;
                 const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
                 const int n0 = (tile - a.tile_start[seg]) * per_tile;
                 const int m0 = mt * kTileM;
-                for (int kb = 0; kb < a.kblocks; ++kb) {
+                const int kb0 = static_cast<int>(static_cast<long long>(z) * a.kblocks / a.split_k);
+                const int kb1 = static_cast<int>(static_cast<long long>(z + 1) * a.kblocks / a.split_k);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (round > 0 && !mbar_wait_bounded(&empty[s], (round - 1) & 1, abort_flag)) {
                         record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 1);
                         *abort_flag = 1;
@@ -701,8 +730,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
                                        (static_cast<unsigned int>(kTileM >> 4) << 24);
             int s = 0, round = 0, j = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++j) {
+            for (int unit = blockIdx.x; unit < total && ok; unit += gridDim.x, ++j) {
                 const int buf = j & 1;
+                const int z = unit % a.split_k;
+                const int kb0 = static_cast<int>(static_cast<long long>(z) * a.kblocks / a.split_k);
+                const int kb1 = static_cast<int>(static_cast<long long>(z + 1) * a.kblocks / a.split_k);
                 // the epilogue must have drained this buffer's previous tile
                 if (j >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((j >> 1) - 1) & 1, abort_flag)) {
                     record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 4);
@@ -711,7 +743,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
                 }
                 tc_fence_after();
                 const unsigned int acc = tmem_base + buf * BN;
-                for (int kb = 0; kb < a.kblocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(&full[s], round & 1, abort_flag)) {
                         record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 2);
                         *abort_flag = 1;
@@ -719,13 +751,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
                         break;
                     }
                     tc_fence_after();
-                    if (j == 0 && kb == 0) stamp(2);
+                    if (j == 0 && kb == kb0) stamp(2);
                     const unsigned int base = smem_u32(smem + s * kStage);
                     const unsigned long long da = umma_desc(base);
                     const unsigned long long db = umma_desc(base + kStageA);
 #pragma unroll
                     for (int k = 0; k < kTileK / 16; ++k)  // 32 bytes along K per step: +2 encoded
-                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
                     umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
                     if (++s == kStages) {
                         s = 0;
@@ -743,8 +775,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
         const int chunks = per_tile / 32;
         const int c_begin = column_half * (chunks / 2), c_end = c_begin + chunks / 2;
         int j = 0;
-        for (int t = blockIdx.x; t < total; t += gridDim.x, ++j) {
+        for (int unit = blockIdx.x; unit < total; unit += gridDim.x, ++j) {
             const int buf = j & 1;
+            const int t = unit / a.split_k, z = unit - t * a.split_k;
             const int mt = t % a.tiles_m, tile = t / a.tiles_m;
             const int seg = (tile >= a.tile_start[1] ? 1 : 0) + (tile >= a.tile_start[2] ? 1 : 0);
             const int n0 = (tile - a.tile_start[seg]) * per_tile;
@@ -756,13 +789,75 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
             if (!ok) {
                 if (lane == 0) record_status(a.ctl, MB_ST_PIPE_TIMEOUT, a.phase, 3);
                 *abort_flag = 1;
-                break;
+                if (a.split_k == 1) break;
             }
             tc_fence_after();
             if (j == 0 && threadIdx.x == 64) stamp(4);
             const unsigned int lane_addr =
                 tmem_base + buf * BN + (static_cast<unsigned int>(quarter * 32) << 16);
             const bool row_fast = (n & 7) == 0;
+            if (a.split_k > 1) {
+                // the eight warps meet at barriers below: leave together or not at all
+                if (named_barrier_or(2, 256, !ok)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                // park the partial sums ([tile][slice][column][row]: a warp's 32 rows are one
+                // 128-byte line per column), give the buffer back, and let the slice that
+                // arrives last add all of them up in slice order, so that the result does not
+                // depend on the order of arrival
+                const int row_in_tile = quarter * 32 + lane;
+                float* parts = a.workspace + static_cast<size_t>(t) * a.split_k * (kTileM * BN) + row_in_tile;
+                float* mine = parts + static_cast<size_t>(z) * (kTileM * BN);
+                for (int c = column_half * (BN / 64); c < (column_half + 1) * (BN / 64); ++c) {
+                    float v[32];
+                    tmem_load32(lane_addr + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) __stcg(mine + (c * 32 + i) * kTileM, v[i]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                __threadfence();
+                named_barrier(1, 256);
+                if (warp == 2 && lane == 0) {
+                    const int arrived = atomicAdd(a.counters + t, 1);
+                    *last_flag = arrived == a.split_k - 1 ? 1 : 0;
+                    if (arrived == a.split_k - 1) a.counters[t] = 0;  // re-arm for the next launch
+                    __threadfence();
+                }
+                named_barrier(1, 256);
+                if (*last_flag != 0) {
+                    for (int c = c_begin; c < c_end; ++c) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 >= n) break;
+                        const bool fast = row_fast && col0 + 32 <= n;
+                        uint4 h[4] = {};
+                        if (fast && a.epilogue == MB_EPI_RESIDUAL && row < a.M) {
+                            const uint4* src = reinterpret_cast<const uint4*>(
+                                a.residual + static_cast<size_t>(row) * n + col0);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) h[q] = src[q];
+                        }
+                        float v[32], u[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = u[i] = 0.f;
+                        for (int sl = 0; sl < a.split_k; ++sl) {
+                            const float* p = parts + static_cast<size_t>(sl) * (kTileM * BN);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += __ldcg(p + (c * 32 + i) * kTileM);
+                            if (a.pair) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    u[i] += __ldcg(p + (kHalf + c * 32 + i) * kTileM);
+                            }
+                        }
+                        gemm_store_chunk(a, seg, row, col0, v, u, h, fast);
+                    }
+                }
+                named_barrier(1, 256);  // last_flag is rewritten by the next unit
+                continue;
+            }
             for (int c = c_begin; c < c_end; ++c) {
                 const int col0 = n0 + c * 32;
                 if (col0 >= n) break;
@@ -1113,6 +1208,8 @@ __global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned sh
                                                                int padded, int kv_heads, int D,
                                                                int kv_rows) {
     __shared__ unsigned short tile[64][66];
+    chain_release();
+    chain_wait();
     const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
     const int bh = blockIdx.z, b = bh / kv_heads, h = bh - b * kv_heads;
     const size_t row_stride = static_cast<size_t>(kv_heads) * D;
@@ -1145,6 +1242,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
     extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
     unsigned char* smem = tc_smem_raw;
     if ((smem_u32(smem) & 1023u) != 0u) {
+        chain_wait();
         if (threadIdx.x == 0) record_status(ctl, MB_ST_BAD_PHASE, phase, -1);
         return;
     }
@@ -1202,6 +1300,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
     __syncthreads();
     tc_fence_after();
     const unsigned int tmem_base = *tmem_slot;
+    chain_release();
+    chain_wait();  // nothing above reads or writes global memory
 
     auto give_up = [&](int where) {
         record_status(ctl, MB_ST_PIPE_TIMEOUT, phase, where);
@@ -1505,14 +1605,39 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
     // the SMs on (a single wave of them moves a third less operand bytes than two CTAs per SM
     // on narrow ones), narrow tiles when only those reach one per SM
     g.persistent = 0;
+    int persistent_split = 1;
     const char* persistent_env = std::getenv("MEGABAKE_B200_GEMM_PERSISTENT");
     if (persistent_env == nullptr || std::atoi(persistent_env) != 0) {
-        if (count(256) * g.tiles_m * 5 >= sm_count * 4) {
-            g.persistent = 1;
-            g.bn = 256;
-        } else if (count(128) * g.tiles_m >= sm_count) {
-            g.persistent = 1;
-            g.bn = 128;
+        // Tile width and number of reduction slices by a cost model in microseconds, with the
+        // figures measured on this kernel: a CTA takes a k-block every 0.44 us (256 columns)
+        // or 0.29 us (128) when every SM streams operands; the weights cannot arrive faster
+        // than HBM delivers them; a sliced tile pays for parking its partial sums and for
+        // the last slice's pass over all of them.
+        g.persistent = 1;
+        double best = 1e30;
+        const double weight_bytes = 2.0 * K * (pair ? 2 : 1) * [&] {
+            long long n = 0;
+            for (int s = 0; s < P.i[MB_GV_I_NSEG]; ++s) n += P.i[MB_GV_I_N0 + s];
+            return static_cast<double>(n);
+        }();
+        for (int bn = 256; bn >= 128; bn -= 128) {
+            const int tiles = count(bn) * g.tiles_m;
+            for (int split = 1; split <= 16; ++split) {
+                if (split > 1 && g.kblocks / split < 4) break;
+                const int units = tiles * split;
+                const int waves = (units + sm_count - 1) / sm_count;
+                const int per_unit = (g.kblocks + split - 1) / split;
+                double stream = waves * per_unit * (bn == 256 ? 0.44 : 0.29);
+                const double hbm = weight_bytes / 6.0e6;
+                if (stream < hbm) stream = hbm;
+                const double slices = split > 1 ? (bn == 256 ? 3.0 : 1.5) * waves + 0.4 * split : 0.0;
+                const double cost = stream + slices;
+                if (cost < best - 1e-9) {
+                    best = cost;
+                    g.bn = bn;
+                    persistent_split = split;
+                }
+            }
         }
     }
     if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_BN")) {
@@ -1547,9 +1672,16 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
         const int value = std::atoi(forced);
         if (value >= 1 && value <= 16 && value <= g.kblocks) split = value;
     }
-    if (g.persistent) split = 1;
+    if (g.persistent) {
+        split = persistent_split;
+        if (const char* forced = std::getenv("MEGABAKE_B200_GEMM_SPLIT")) {
+            const int value = std::atoi(forced);
+            if (value >= 1 && value <= 16 && value <= g.kblocks) split = value;
+        }
+    }
     g.split_k = split;
-    g.grid = g.tiles_n * g.tiles_m < sm_count ? g.tiles_n * g.tiles_m : sm_count;
+    const int units = g.tiles_n * g.tiles_m * g.split_k;
+    g.grid = units < sm_count ? units : sm_count;
     return g;
 }
 
@@ -1809,6 +1941,40 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
     return MB_OK;
 }
 
+namespace {
+
+// One phase's kernel; `chained`: launched with programmatic stream serialization, so that it
+// may start while its predecessor drains (every kernel of this file blocks in chain_wait()
+// before it touches global memory).
+template <typename... Params, typename... Args>
+cudaError_t launch_phase(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, bool chained, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = chained ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+bool chaining_enabled() {
+    static const bool enabled = [] {
+        // off unless asked for: measured on the gemma-2b shape, chaining takes 3-4 % off a step
+        // launched kernel by kernel (128 and 512 tokens) and adds 1-2 % to the same step
+        // replayed from a CUDA graph, the way the backend runs it
+        const char* value = std::getenv("MEGABAKE_B200_PREFILL_CHAIN");
+        return value != nullptr && std::atoi(value) != 0;
+    }();
+    return enabled;
+}
+
+}  // namespace
+
 // Enqueues every phase in order.  Dynamic slots (token ids) are resolved here on the host.
 cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases,
                            const std::vector<unsigned long long>& slots, unsigned int n_dynamic,
@@ -1819,19 +1985,21 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
         if (s < 0) return 0ull;
         return static_cast<unsigned int>(s) < n_dynamic ? dyn[s] : slots[s];
     };
+    bool chained = false;  // the first kernel of an invocation follows foreign work: plain launch
+    cudaError_t err = cudaSuccess;
     for (size_t i = 0; i < phases.size(); ++i) {
         const mb_phase& P = phases[i];
         const PrefillLaunch& L = st->launches[i];
         switch (P.body) {
             case MB_BODY_EMBED_ROWS:
-                embed_rows_kernel<<<P.i[MB_EM_I_ROWS], 128, 0, stream>>>(
+                err = launch_phase(embed_rows_kernel, dim3(P.i[MB_EM_I_ROWS]), dim3(128), 0, stream, chained,
                     reinterpret_cast<const unsigned short*>(addr(P.slot[MB_EM_S_TABLE])),
                     reinterpret_cast<const long long*>(addr(P.slot[MB_EM_S_IDS])),
                     reinterpret_cast<unsigned short*>(addr(P.slot[MB_EM_S_OUT])), P.i[MB_EM_I_ROWS],
                     P.i[MB_EM_I_K], P.i[MB_EM_I_VOCAB], P.f[MB_EM_F_SCALE], ctl, static_cast<int>(i));
                 break;
             case MB_BODY_RMSNORM_ROWS:
-                rmsnorm_rows_kernel<<<(P.i[MB_RN_I_ROWS] + 3) / 4, 128, 0, stream>>>(
+                err = launch_phase(rmsnorm_rows_kernel, dim3((P.i[MB_RN_I_ROWS] + 3) / 4), dim3(128), 0, stream, chained,
                     reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_X])),
                     reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_W])),
                     reinterpret_cast<unsigned short*>(addr(P.slot[MB_RN_S_OUT])), P.i[MB_RN_I_ROWS],
@@ -1845,17 +2013,17 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                 for (int s = 0; s < args.nseg; ++s)  // outputs may be per-launch tensors (logits)
                     args.out[s] = reinterpret_cast<unsigned short*>(addr(P.slot[MB_GV_S_OUT0 + s]));
                 if (g.persistent && g.bn == 256)
-                    gemm_tc_persistent_kernel<256>
-                        <<<g.grid, kPersistThreads, kPersistSmemBytes, stream>>>(L.maps, args);
+                    err = launch_phase(gemm_tc_persistent_kernel<256>, dim3(g.grid), dim3(kPersistThreads),
+                                       kPersistSmemBytes, stream, chained, L.maps, args);
                 else if (g.persistent)
-                    gemm_tc_persistent_kernel<128>
-                        <<<g.grid, kPersistThreads, kPersistSmemBytes, stream>>>(L.maps, args);
+                    err = launch_phase(gemm_tc_persistent_kernel<128>, dim3(g.grid), dim3(kPersistThreads),
+                                       kPersistSmemBytes, stream, chained, L.maps, args);
                 else if (g.bn == 256)
-                    gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem_bytes(256, g.stages), stream>>>(
-                        L.maps, args);
+                    err = launch_phase(gemm_tc_kernel<256>, grid, dim3(kGemmThreads),
+                                       gemm_smem_bytes(256, g.stages), stream, chained, L.maps, args);
                 else
-                    gemm_tc_kernel<128><<<grid, kGemmThreads, gemm_smem_bytes(128, g.stages), stream>>>(
-                        L.maps, args);
+                    err = launch_phase(gemm_tc_kernel<128>, grid, dim3(kGemmThreads),
+                                       gemm_smem_bytes(128, g.stages), stream, chained, L.maps, args);
                 break;
             }
             case MB_BODY_ROPE_ROWS: {
@@ -1863,7 +2031,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                                        (P.i[MB_RP_I_HEAD_DIM] / 2);
                 long long blocks = (work + 255) / 256;
                 if (blocks > 4 * 148 * 8) blocks = 4 * 148 * 8;
-                rope_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+                err = launch_phase(rope_rows_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, stream, chained,
                     reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_Q])),
                     reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_K])),
                     reinterpret_cast<const long long*>(addr(P.slot[MB_RP_S_POS])),
@@ -1880,18 +2048,22 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                 if (L.vt != nullptr) {
                     const AttnArgs& a = L.attn;
                     const dim3 tgrid(L.padded_tokens / 64, D / 64, a.batch * a.kv_heads);
-                    transpose_values_kernel<<<tgrid, 256, 0, stream>>>(a.v, L.vt, a.tokens,
-                                                                       L.padded_tokens, a.kv_heads, D,
-                                                                       a.kv_rows);
+                    err = launch_phase(transpose_values_kernel, tgrid, dim3(256), 0, stream, chained, a.v,
+                                       L.vt, a.tokens, L.padded_tokens, a.kv_heads, D, a.kv_rows);
+                    if (err != cudaSuccess) return err;
+                    chained = chaining_enabled();
                     const dim3 grid((a.tokens + kTcRows - 1) / kTcRows, a.heads, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
                     const int ph = static_cast<int>(i);
                     if (D == 64)
-                        attention_tc_kernel<64><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                        err = launch_phase(attention_tc_kernel<64>, grid, dim3(kTcThreads), smem, stream,
+                                           chained, L.attn_maps, a, ctl, ph);
                     else if (D == 128)
-                        attention_tc_kernel<128><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                        err = launch_phase(attention_tc_kernel<128>, grid, dim3(kTcThreads), smem, stream,
+                                           chained, L.attn_maps, a, ctl, ph);
                     else
-                        attention_tc_kernel<256><<<grid, kTcThreads, smem, stream>>>(L.attn_maps, a, ctl, ph);
+                        err = launch_phase(attention_tc_kernel<256>, grid, dim3(kTcThreads), smem, stream,
+                                           chained, L.attn_maps, a, ctl, ph);
                     break;
                 }
                 cudaError_t launched = D == 64    ? attn_launch<64>(L.attn, stream)
@@ -1903,8 +2075,9 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
             default:
                 break;
         }
-        cudaError_t err = cudaGetLastError();
+        if (err == cudaSuccess) err = cudaGetLastError();
         if (err != cudaSuccess) return err;
+        if (P.body != MB_BODY_NOP) chained = chaining_enabled();
     }
     return cudaSuccess;
 }
