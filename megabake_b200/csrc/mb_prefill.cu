@@ -2,14 +2,20 @@
 // the caller's stream (and captured as a whole by a CUDA graph when the caller does so).
 //
 //   embed_rows_kernel      gather of embedding rows (+ Gemma's bf16 scalar scale)
-//   rmsnorm_rows_kernel    row-wise RMSNorm, Llama and Gemma spellings
-//   gemm_tc_kernel         C[M, N] = A[M, K] . W[N, K]^T on the 5th-generation tensor cores:
-//                          TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring ->
-//                          tcgen05.mma issued by one thread, fp32 accumulators in tensor memory,
-//                          tcgen05.ld epilogue (bias / residual / gated activation), optional
-//                          split-K with a last-arriver reduction
-//   rope_rows_kernel       rotary embedding of q and k rows in place
-//   attention_prefill_kernel   masked softmax attention with the eager rounding points
+//   rmsnorm_block_kernel   row-wise RMSNorm, Llama and Gemma spellings, one CTA per row
+//                          (rmsnorm_rows_kernel: rows longer than 8192 elements)
+//   gemm_tc_persistent_kernel   C[M, N] = A[M, K] . W[N, K]^T on the 5th-generation tensor
+//                          cores, one CTA per SM walking (tile, reduction slice) units:
+//                          TMA (cp.async.bulk.tensor, 128-byte swizzle) -> 192 KB shared-
+//                          memory ring -> tcgen05.mma issued by one thread into one of two
+//                          tensor-memory accumulators -> tcgen05.ld epilogue on eight warps
+//                          (bias / residual / gated activation) behind the next unit's MMAs
+//   gemm_tc_kernel         the same contraction with one tile per CTA and two CTAs per SM
+//                          (kept selectable: MEGABAKE_B200_GEMM_PERSISTENT=0)
+//   rope_transpose_kernel  rotary embedding of q and k rows in place and, in the same launch,
+//                          the transpose of v the tensor-core attention reads
+//   attention_tc_kernel    masked softmax attention with the eager rounding points, S and O in
+//                          tensor memory (attention_prefill_kernel: the mma.sync fallback)
 //
 // Every load in this file is a plain (single-CTA) TMA or cp.async load, so the library runs
 // unchanged at any GPU count.  Every wait is bounded and reports through
@@ -90,25 +96,78 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(const unsigned short*
     for (int v = lane; v < K / 8; v += 32) dst[v] = normalise_vector(src[v], __ldg(wv + v), inv, kind);
 }
 
+// One CTA per row, the row held in registers between the sum of squares and the scaling: one
+// read of x where the warp-per-row kernel makes two, at a third of its latency (these kernels
+// are latency, not bandwidth: a 128-token step runs 37 of them).  Rows of up to 8192 elements.
+__global__ void __launch_bounds__(256) rmsnorm_block_kernel(const unsigned short* x,
+                                                            const unsigned short* w,
+                                                            unsigned short* out, int K, int kind,
+                                                            float eps) {
+    __shared__ float partial[8];
+    chain_release();
+    chain_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int vectors = K / 8;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * K);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * K);
+    const uint4* wv = reinterpret_cast<const uint4*>(w);
+    uint4 v[4], g[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int idx = static_cast<int>(threadIdx.x) + j * 256;
+        if (idx < vectors) {
+            v[j] = src[idx];
+            g[j] = __ldg(wv + idx);
+            ss += sum_squares(v[j]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) partial[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(K) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int idx = static_cast<int>(threadIdx.x) + j * 256;
+        if (idx < vectors) dst[idx] = normalise_vector(v[j], g[j], inv, kind);
+    }
+}
+
 // One thread per (row, i): the cos / sin pair of that position and frequency is computed once
 // and applied to element pair (i, i + D/2) of every q and k head of the row, with the rounding
 // points of the eager graph: tables in bf16, every product and the sum rounded to bf16.
-__global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsigned short* k,
-                                                        const long long* pos, const void* inv_freq,
-                                                        int rows, int heads, int kv_heads, int D,
-                                                        int invfreq_bf16, float rope_scale,
-                                                        float q_scale, int k_tokens, int k_capacity,
-                                                        int* length, int length_value,
-                                                        int length_count) {
+struct RopeArgs {
+    unsigned short* q;
+    unsigned short* k;
+    const long long* pos;
+    const void* inv_freq;
+    int rows, heads, kv_heads, D, invfreq_bf16;
+    float rope_scale, q_scale;
+    int k_tokens, k_capacity;
+    int* length;
+    int length_value, length_count;
+};
+
+// block / blocks: this CTA's index among the CTAs that share the work
+__device__ __forceinline__ void rope_rows_body(const RopeArgs& a, int block, int blocks) {
+    unsigned short* q = a.q;
+    unsigned short* k = a.k;
+    const long long* pos = a.pos;
+    const void* inv_freq = a.inv_freq;
+    const int rows = a.rows, heads = a.heads, kv_heads = a.kv_heads, D = a.D;
+    const int invfreq_bf16 = a.invfreq_bf16, k_tokens = a.k_tokens, k_capacity = a.k_capacity;
+    const float rope_scale = a.rope_scale, q_scale = a.q_scale;
     const int half = D / 2;
     const long long total = static_cast<long long>(rows) * half;
-    chain_release();
-    chain_wait();
     // state handoff: the layer's valid length(s), one shared by the batch or one per row
-    if (length != nullptr && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < length_count)
-        length[threadIdx.x] = length_value;
-    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
-         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    if (a.length != nullptr && block == 0 && static_cast<int>(threadIdx.x) < a.length_count)
+        a.length[threadIdx.x] = a.length_value;
+    for (long long e = block * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(blocks) * blockDim.x) {
         const int r = static_cast<int>(e / half);
         const int i = static_cast<int>(e - static_cast<long long>(r) * half);
         const float f = invfreq_bf16
@@ -136,6 +195,12 @@ __global__ void __launch_bounds__(256) rope_rows_kernel(unsigned short* q, unsig
             row[i + half] = float_to_bf16_bits(r2);
         }
     }
+}
+
+__global__ void __launch_bounds__(256) rope_rows_kernel(const RopeArgs a) {
+    chain_release();
+    chain_wait();
+    rope_rows_body(a, blockIdx.x, gridDim.x);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1203,15 +1268,21 @@ constexpr int kTcThreads = 64 + 16 * 32;
 constexpr int kTcSoftmaxWarps = 16;  // one elected lane per warp arrives on the shared barriers
 
 // V [batch * tokens, kv_heads * D] -> V^T [batch * kv_heads * D, padded], zero beyond `tokens`
-__global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned short* v,
-                                                               unsigned short* vt, int tokens,
-                                                               int padded, int kv_heads, int D,
-                                                               int kv_rows) {
+struct TransposeArgs {
+    const unsigned short* v;
+    unsigned short* vt;
+    int tokens, padded, kv_heads, D, kv_rows;
+};
+
+// block: index among padded / 64 x D / 64 x batch * kv_heads tiles, tokens fastest
+__device__ __forceinline__ void transpose_values_body(const TransposeArgs& a, int block) {
     __shared__ unsigned short tile[64][66];
-    chain_release();
-    chain_wait();
-    const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
-    const int bh = blockIdx.z, b = bh / kv_heads, h = bh - b * kv_heads;
+    const unsigned short* v = a.v;
+    unsigned short* vt = a.vt;
+    const int tokens = a.tokens, padded = a.padded, kv_heads = a.kv_heads, D = a.D, kv_rows = a.kv_rows;
+    const int tiles_t = padded / 64, tiles_d = D / 64;
+    const int t0 = (block % tiles_t) * 64, d0 = ((block / tiles_t) % tiles_d) * 64;
+    const int bh = block / (tiles_t * tiles_d), b = bh / kv_heads, h = bh - b * kv_heads;
     const size_t row_stride = static_cast<size_t>(kv_heads) * D;
     for (int e = threadIdx.x; e < 64 * 64; e += 256) {
         const int t = e >> 6, d = e & 63;
@@ -1225,6 +1296,25 @@ __global__ void __launch_bounds__(256) transpose_values_kernel(const unsigned sh
         if (t0 + t < padded)
             vt[(static_cast<size_t>(bh) * D + d0 + d) * padded + t0 + t] = tile[t][d];
     }
+}
+
+__global__ void __launch_bounds__(256) transpose_values_kernel(const TransposeArgs a) {
+    chain_release();
+    chain_wait();
+    transpose_values_body(a, blockIdx.x);
+}
+
+// The rotary embedding of q and k and the transpose of v both follow the q|k|v projection and
+// touch disjoint tensors: one launch, the first `rope_blocks` CTAs rotate, the others transpose.
+__global__ void __launch_bounds__(256) rope_transpose_kernel(const RopeArgs rope,
+                                                             const TransposeArgs transpose,
+                                                             int rope_blocks) {
+    chain_release();
+    chain_wait();
+    if (static_cast<int>(blockIdx.x) < rope_blocks)
+        rope_rows_body(rope, blockIdx.x, rope_blocks);
+    else
+        transpose_values_body(transpose, blockIdx.x - rope_blocks);
 }
 
 template <int D>
@@ -1962,6 +2052,22 @@ cudaError_t launch_phase(void (*kernel)(Params...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+prefill::TransposeArgs transpose_args(const prefill::PrefillLaunch& L, int head_dim) {
+    prefill::TransposeArgs t;
+    t.v = L.attn.v;
+    t.vt = L.vt;
+    t.tokens = L.attn.tokens;
+    t.padded = L.padded_tokens;
+    t.kv_heads = L.attn.kv_heads;
+    t.D = head_dim;
+    t.kv_rows = L.attn.kv_rows;
+    return t;
+}
+
+int transpose_blocks(const prefill::TransposeArgs& t, int batch) {
+    return (t.padded / 64) * (t.D / 64) * batch * t.kv_heads;
+}
+
 bool chaining_enabled() {
     static const bool enabled = [] {
         // off unless asked for: measured on the gemma-2b shape, chaining takes 3-4 % off a step
@@ -1986,6 +2092,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
         return static_cast<unsigned int>(s) < n_dynamic ? dyn[s] : slots[s];
     };
     bool chained = false;  // the first kernel of an invocation follows foreign work: plain launch
+    size_t transposed_by = phases.size() + 1;  // the rotary phase that transposed the values, if any
     cudaError_t err = cudaSuccess;
     for (size_t i = 0; i < phases.size(); ++i) {
         const mb_phase& P = phases[i];
@@ -1999,6 +2106,15 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                     P.i[MB_EM_I_K], P.i[MB_EM_I_VOCAB], P.f[MB_EM_F_SCALE], ctl, static_cast<int>(i));
                 break;
             case MB_BODY_RMSNORM_ROWS:
+                if (P.i[MB_RN_I_K] <= 8192) {
+                    err = launch_phase(rmsnorm_block_kernel, dim3(P.i[MB_RN_I_ROWS]), dim3(256), 0, stream,
+                                       chained,
+                                       reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_X])),
+                                       reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_W])),
+                                       reinterpret_cast<unsigned short*>(addr(P.slot[MB_RN_S_OUT])),
+                                       P.i[MB_RN_I_K], P.i[MB_RN_I_KIND], P.f[MB_RN_F_EPS]);
+                    break;
+                }
                 err = launch_phase(rmsnorm_rows_kernel, dim3((P.i[MB_RN_I_ROWS] + 3) / 4), dim3(128), 0, stream, chained,
                     reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_X])),
                     reinterpret_cast<const unsigned short*>(addr(P.slot[MB_RN_S_W])),
@@ -2031,27 +2147,53 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                                        (P.i[MB_RP_I_HEAD_DIM] / 2);
                 long long blocks = (work + 255) / 256;
                 if (blocks > 4 * 148 * 8) blocks = 4 * 148 * 8;
-                err = launch_phase(rope_rows_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, stream, chained,
-                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_Q])),
-                    reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_K])),
-                    reinterpret_cast<const long long*>(addr(P.slot[MB_RP_S_POS])),
-                    reinterpret_cast<const void*>(addr(P.slot[MB_RP_S_INVFREQ])), P.i[MB_RP_I_ROWS],
-                    P.i[MB_RP_I_HEADS], P.i[MB_RP_I_KV_HEADS], P.i[MB_RP_I_HEAD_DIM],
-                    P.i[MB_RP_I_INVFREQ_BF16], P.f[MB_RP_F_ROPE_SCALE], P.f[MB_RP_F_Q_SCALE],
-                    P.i[MB_RP_I_K_TOKENS], P.i[MB_RP_I_K_CAPACITY],
-                    reinterpret_cast<int*>(addr(P.slot[MB_RP_S_LEN])), P.i[MB_RP_I_LEN_VALUE],
-                    P.i[MB_RP_I_LEN_COUNT] > 1 ? P.i[MB_RP_I_LEN_COUNT] : 1);
+                RopeArgs rope;
+                rope.q = reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_Q]));
+                rope.k = reinterpret_cast<unsigned short*>(addr(P.slot[MB_RP_S_K]));
+                rope.pos = reinterpret_cast<const long long*>(addr(P.slot[MB_RP_S_POS]));
+                rope.inv_freq = reinterpret_cast<const void*>(addr(P.slot[MB_RP_S_INVFREQ]));
+                rope.rows = P.i[MB_RP_I_ROWS];
+                rope.heads = P.i[MB_RP_I_HEADS];
+                rope.kv_heads = P.i[MB_RP_I_KV_HEADS];
+                rope.D = P.i[MB_RP_I_HEAD_DIM];
+                rope.invfreq_bf16 = P.i[MB_RP_I_INVFREQ_BF16];
+                rope.rope_scale = P.f[MB_RP_F_ROPE_SCALE];
+                rope.q_scale = P.f[MB_RP_F_Q_SCALE];
+                rope.k_tokens = P.i[MB_RP_I_K_TOKENS];
+                rope.k_capacity = P.i[MB_RP_I_K_CAPACITY];
+                rope.length = reinterpret_cast<int*>(addr(P.slot[MB_RP_S_LEN]));
+                rope.length_value = P.i[MB_RP_I_LEN_VALUE];
+                rope.length_count = P.i[MB_RP_I_LEN_COUNT] > 1 ? P.i[MB_RP_I_LEN_COUNT] : 1;
+                // the attention phase that follows wants its values transposed: same launch
+                const bool with_transpose = i + 1 < phases.size() &&
+                                            phases[i + 1].body == MB_BODY_ATTN_PREFILL &&
+                                            st->launches[i + 1].vt != nullptr;
+                if (with_transpose) {
+                    const PrefillLaunch& next = st->launches[i + 1];
+                    const TransposeArgs transpose = transpose_args(next, phases[i + 1].i[MB_AP_I_HEAD_DIM]);
+                    const int tblocks = transpose_blocks(transpose, next.attn.batch);
+                    err = launch_phase(rope_transpose_kernel, dim3(static_cast<int>(blocks) + tblocks),
+                                       dim3(256), 0, stream, chained, rope, transpose,
+                                       static_cast<int>(blocks));
+                    transposed_by = i;
+                } else {
+                    err = launch_phase(rope_rows_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0,
+                                       stream, chained, rope);
+                }
                 break;
             }
             case MB_BODY_ATTN_PREFILL: {
                 const int D = P.i[MB_AP_I_HEAD_DIM];
                 if (L.vt != nullptr) {
                     const AttnArgs& a = L.attn;
-                    const dim3 tgrid(L.padded_tokens / 64, D / 64, a.batch * a.kv_heads);
-                    err = launch_phase(transpose_values_kernel, tgrid, dim3(256), 0, stream, chained, a.v,
-                                       L.vt, a.tokens, L.padded_tokens, a.kv_heads, D, a.kv_rows);
-                    if (err != cudaSuccess) return err;
-                    chained = chaining_enabled();
+                    if (transposed_by + 1 != i) {  // not done by the rotary phase just before
+                        const TransposeArgs transpose = transpose_args(L, D);
+                        err = launch_phase(transpose_values_kernel,
+                                           dim3(transpose_blocks(transpose, a.batch)), dim3(256), 0,
+                                           stream, chained, transpose);
+                        if (err != cudaSuccess) return err;
+                        chained = chaining_enabled();
+                    }
                     const dim3 grid((a.tokens + kTcRows - 1) / kTcRows, a.heads, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
                     const int ph = static_cast<int>(i);
