@@ -723,7 +723,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs 
     };
     if (threadIdx.x == 0) stamp(0);
     // work units: (output tile, slice of the reduction), slices of a tile adjacent so that they
-    // finish together and the last one to arrive finds the others' partial sums in L2
+    // finish together and the last one to arrive finds the others' partial sums in L2.  Every
+    // unit starts at the same k offsets as its neighbours, so CTAs that share an operand tile
+    // ask for the same k-block at the same time and L2 serves all but one of them.  (Measured
+    // and dropped: equal runs of k-blocks per CTA cut across tiles.  They balance the CTAs
+    // exactly but skew the k offsets, the operands then overflow L2 between two uses, and
+    // every shape that needed them ran 20-60 % slower.)
     const int total = a.tiles_n * a.tiles_m * a.split_k;
     const int per_tile = a.pair ? kHalf : BN;  // output columns of one n-tile
     int* last_flag = const_cast<int*>(abort_flag) + 1;
@@ -2068,15 +2073,13 @@ int transpose_blocks(const prefill::TransposeArgs& t, int batch) {
     return (t.padded / 64) * (t.D / 64) * batch * t.kv_heads;
 }
 
+// Read at every launch (not cached) so that one process can run both ways.
 bool chaining_enabled() {
-    static const bool enabled = [] {
-        // off unless asked for: measured on the gemma-2b shape, chaining takes 3-4 % off a step
-        // launched kernel by kernel (128 and 512 tokens) and adds 1-2 % to the same step
-        // replayed from a CUDA graph, the way the backend runs it
-        const char* value = std::getenv("MEGABAKE_B200_PREFILL_CHAIN");
-        return value != nullptr && std::atoi(value) != 0;
-    }();
-    return enabled;
+    // off unless asked for: measured on the gemma-2b shape, chaining takes 3-4 % off a step
+    // launched kernel by kernel (128 and 512 tokens) and adds 1-2 % to the same step
+    // replayed from a CUDA graph, the way the backend runs it
+    const char* value = std::getenv("MEGABAKE_B200_PREFILL_CHAIN");
+    return value != nullptr && std::atoi(value) != 0;
 }
 
 }  // namespace

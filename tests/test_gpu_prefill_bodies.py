@@ -131,6 +131,73 @@ def test_gemm_plain(rows, n, k):
     _check_gemm(out, _ref_linear(x, w))
 
 
+GEMM_VARIANTS = [
+    {"MEGABAKE_B200_GEMM_PERSISTENT": "0"},                              # one tile per CTA, two CTAs per SM
+    {"MEGABAKE_B200_GEMM_BN": "256", "MEGABAKE_B200_GEMM_SPLIT": "1"},   # persistent, whole reductions
+    {"MEGABAKE_B200_GEMM_BN": "256", "MEGABAKE_B200_GEMM_SPLIT": "3"},   # persistent, ragged slices
+    {"MEGABAKE_B200_GEMM_BN": "128", "MEGABAKE_B200_GEMM_SPLIT": "5"},
+]
+
+
+@pytest.mark.parametrize("env", GEMM_VARIANTS, ids=lambda e: ",".join(f"{k[19:]}={v}" for k, v in e.items()))
+@pytest.mark.parametrize("rows,n,k", [(130, 1000, 576), (512, 8192, 2048), (16, 2048, 16384)])
+def test_gemm_tile_and_slice_choices(monkeypatch, env, rows, n, k):
+    """Every kernel and geometry the cost model can pick gives the same contraction."""
+    for key, value in env.items():
+        monkeypatch.setenv(key, value)
+    x = _bf16(rows, k, seed=rows + n)
+    w = _bf16(n, k, scale=k ** -0.5, seed=k)
+    out = torch.zeros(rows, n, dtype=torch.bfloat16, device="cuda")
+    runner = PhaseRunner()
+    ph = _gemm_phase(runner, x=x.cuda(), segs=[(w.cuda(), None, out)])
+    plan = _run(runner, [ph])
+    _check_gemm(out, _ref_linear(x, w))
+    first = out.clone()
+    out.zero_()
+    plan.launch([], torch.cuda.current_stream().cuda_stream)   # arrival counters re-armed
+    torch.cuda.synchronize()
+    assert plan.status().code == 0
+    assert torch.equal(out, first)
+
+
+@pytest.mark.parametrize("env", GEMM_VARIANTS[2:], ids=lambda e: ",".join(f"{k[19:]}={v}" for k, v in e.items()))
+def test_gemm_epilogues_on_sliced_reductions(monkeypatch, env):
+    """Gated pair, bias segments and the in-place residual when the last slice to arrive runs
+    the epilogue from the parked partial sums."""
+    for key, value in env.items():
+        monkeypatch.setenv(key, value)
+    rows, n, k = 200, 1536, 576
+    x = _bf16(rows, k, seed=7)
+    wg, wu = _bf16(n, k, scale=k ** -0.5, seed=8), _bf16(n, k, scale=k ** -0.5, seed=9)
+    out = torch.zeros(rows, n, dtype=torch.bfloat16, device="cuda")
+    runner = PhaseRunner()
+    ph = _gemm_phase(runner, x=x.cuda(), segs=[(wg.cuda(), None, out)], pair=wu.cuda(),
+                     epilogue=rt.EPI_GELU_TANH_MUL)
+    _run(runner, [ph])
+    ref = oracle._activation(_ref_linear(x, wg), "gelu_tanh") * _ref_linear(x, wu)
+    assert _mismatch(out, ref) < 0.03 and cosine(out, ref) > 0.99999
+
+    ws = [_bf16(m, k, scale=k ** -0.5, seed=10 + i) for i, m in enumerate((896, 128, 128))]
+    bs = [_bf16(m, seed=20 + i) for i, m in enumerate((896, 128, 128))]
+    outs = [torch.zeros(rows, m, dtype=torch.bfloat16, device="cuda") for m in (896, 128, 128)]
+    runner = PhaseRunner()
+    ph = _gemm_phase(runner, x=x.cuda(), segs=[(w.cuda(), b.cuda(), o) for w, b, o in zip(ws, bs, outs)])
+    _run(runner, [ph])
+    for w, b, o in zip(ws, bs, outs):
+        _check_gemm(o, _ref_linear(x, w, b))
+
+    w = _bf16(k, n, scale=n ** -0.5, seed=4)
+    y = _bf16(rows, n, seed=6)
+    hidden0 = _bf16(rows, k, seed=5)
+    hidden = hidden0.clone().cuda()
+    runner = PhaseRunner()
+    ph = _gemm_phase(runner, x=y.cuda(), segs=[(w.cuda(), None, hidden)], residual=hidden,
+                     epilogue=rt.EPI_RESIDUAL)
+    _run(runner, [ph])
+    ref = hidden0 + _ref_linear(y, w)
+    assert _mismatch(hidden, ref) < 0.01 and cosine(hidden, ref) > 0.99999
+
+
 def test_gemm_runs_twice_with_split_k():
     # the arrival counters of a split-K phase must be back at zero after a launch
     x = _bf16(16, 4096, seed=1)
