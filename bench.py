@@ -414,6 +414,7 @@ def run_prefill(args) -> None:
         barrier()
     bound.check()
     device_ms = start.elapsed_time(stop)
+    launches = bound.plan.launches   # kernel launches one prefill enqueues, as the library reports it
 
     # End to end through the public API: torch.compile(PrefillLogits(model),
     # backend=make_backend(mode="prefill")) captured once with megabake_b200.graphed.  Per step:
@@ -460,7 +461,6 @@ def run_prefill(args) -> None:
         gemm_flops *= batch
         attn_flops *= batch
         achieved = gemm_flops / (ms_per_step * 1e-3) / 1e12
-        launches = len(layout.phases)
         line = {
             "metric": "prefill_tokens_per_s",
             "value": whole_job_rate(batch * tokens, world, ms_per_step * 1e-3),

@@ -320,7 +320,8 @@ typedef struct mb_plan_info {
     int32_t stages;           /* weight-ring stages                                       */
     int32_t barriers;         /* grid barriers per launch                                 */
     int32_t sm_count;
-    int32_t reserved[2];
+    int32_t launches;         /* kernel launches one mb_plan_launch enqueues              */
+    int32_t reserved[1];
 } mb_plan_info;
 
 typedef struct mb_plan mb_plan;

@@ -366,6 +366,7 @@ int mb_plan_query(const mb_plan* plan, mb_plan_info* out) {
     out->stages = plan->stages;
     out->barriers = plan->barriers;
     out->sm_count = plan->sm_count;
+    out->launches = plan->mode == MB_MODE_PREFILL ? mb::prefill_launch_count(plan->prefill) : 1;
     return MB_OK;
 }
 

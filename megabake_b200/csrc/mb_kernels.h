@@ -25,6 +25,7 @@ struct PrefillState;
 struct Control;
 int prefill_validate(const mb_phase& phase, unsigned int n_slots, unsigned int n_dynamic);
 cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillState** out);
+int prefill_launch_count(const PrefillState* state);  // kernels one prefill_launch enqueues
 void prefill_destroy(PrefillState* state);
 int prefill_bind(PrefillState* state, const std::vector<mb_phase>& phases,
                  const std::vector<unsigned long long>& slots, Control* ctl);

@@ -980,7 +980,16 @@ struct AttnArgs {
     int batch, tokens, heads, kv_heads, causal, mask_batch;
     int kv_rows;  // rows per batch of the K and V tensors (tokens, or a cache's capacity)
     float scale;
+    // attention_tc_kernel with the keys of a query tile shared out (see there); 0 = one CTA per tile
+    int mode;           // kAttnWhole, kAttnStats or kAttnValues
+    int chunk;          // key blocks per CTA at most
+    int parts_max;      // ceil(all key blocks / chunk): stride of the scratch below
+    float* stats_ws;    // [item][part][128 rows][2]: row maximum and denominator over the part's keys
+    float* o_ws;        // [item][part][head_dim][128 rows]: fp32 partial outputs
+    int* counters;      // [item]: parts arrived, zero between launches
 };
+
+constexpr int kAttnWhole = 0, kAttnStats = 1, kAttnValues = 2;
 
 constexpr int kAttnKeys = 64;  // keys per block
 
@@ -1261,6 +1270,16 @@ cudaError_t attn_configure() {
 //               16 * ((w - 2) / 4) .. of a block (sixteen warps: the softmax, not the tensor
 //               cores, is the long pole of a step, and it is latency-bound per warp)
 // Tensor memory: S double-buffered in columns [0, 64) and [64, 128), O in [128, 128 + D).
+//
+// Few query tiles: 512 tokens of 8 heads are 32 tiles on 148 SMs, and under a causal mask the
+// last tile has four times the key blocks of the first.  The keys of a tile can therefore be
+// shared out in parts of at most `chunk` blocks (the host decides when: attention_parts), and
+// the two sweeps become two launches, so that no CTA ever waits for another one: kAttnStats runs the first sweep over
+// its part and leaves each row's maximum and denominator; kAttnValues combines the parts'
+// statistics (as the column parts inside a CTA are combined), runs the second sweep over its part
+// and, when a tile has several parts, parks its fp32 output -- the part that arrives last adds
+// them in key order and rounds once.  Probabilities are still rounded after normalisation by
+// the whole row's sum; only the order of the fp32 additions changes.
 // ---------------------------------------------------------------------------------------
 struct AttnMaps {
     CUtensorMap q;   // [batch * tokens, heads * D], boxes of 128 rows x 64 columns
@@ -1359,19 +1378,42 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
     unsigned long long* v_empty = bars + 17;   // [2]
     unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 19);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    int* last_flag = abort_flag + 1;
     // row statistics of the four column parts meet here once, between the sweeps (the first P
     // buffer is idle until then)
     float* stats = reinterpret_cast<float*>(Ps);  // [4 parts][128 rows][2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int T = a.tokens;
-    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long rows first
     const int head = blockIdx.y, b = blockIdx.z;
     const int kvh = head / (a.heads / a.kv_heads);
-    const int q0 = qt * kTcRows;
     const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
-    const int last_row = min(q0 + kTcRows, T) - 1;
-    const int n = a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
+    const int q_tiles = (T + kTcRows - 1) / kTcRows;
+    auto visible_blocks = [&](int tile) {
+        const int last_row = min(tile * kTcRows + kTcRows, T) - 1;
+        return a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
+    };
+    // blockIdx.x -> (query tile, part of its keys), long rows first
+    int qt = q_tiles - 1, part_index = 0, parts = 1;
+    if (a.mode == kAttnWhole) {
+        qt = q_tiles - 1 - static_cast<int>(blockIdx.x);
+    } else {
+        int x = blockIdx.x;
+        for (;; --qt) {
+            parts = (visible_blocks(qt) + a.chunk - 1) / a.chunk;
+            if (x < parts || qt == 0) break;
+            x -= parts;
+        }
+        part_index = min(x, parts - 1);
+    }
+    const int q0 = qt * kTcRows;
+    const int visible = visible_blocks(qt);
+    const int per_part = (visible + parts - 1) / parts;
+    const int j_begin = min(part_index * per_part, visible);
+    const int n = min(visible, j_begin + per_part) - j_begin;  // key blocks of this CTA
+    const int n1 = a.mode == kAttnValues ? 0 : n;              // steps of the first sweep
+    const int steps = n1 + (a.mode == kAttnStats ? 0 : n);     // of both
+    const int item = (b * a.heads + head) * q_tiles + qt;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -1408,8 +1450,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             mbar_arrive_expect_tx(q_full, kQBytes);
             for (int kb = 0; kb < D / 64; ++kb)
                 tma_load_2d(Qs + kb * (kTcRows * 128), &maps.q, head * D + kb * 64, b * T + q0, q_full);
-            for (int g = 0; g < 2 * n; ++g) {
-                const int st = g & 1, jb = g < n ? g : g - n;
+            for (int g = 0; g < steps; ++g) {
+                const int st = g & 1, jb = j_begin + (g < n1 ? g : g - n1);
                 if (g >= 2 && !mbar_wait_bounded(&k_empty[st], ((g >> 1) - 1) & 1, abort_flag)) {
                     give_up(10);
                     break;
@@ -1420,15 +1462,15 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                                 kvh * D + kb * 64, b * a.kv_rows + jb * kAttnKeys, &k_full[st]);
             }
         } else if (lane == 1) {
-            for (int j = 0; j < n; ++j) {  // second sweep only
+            for (int j = 0; j < steps - n1; ++j) {  // second sweep only
                 const int sv = j & 1;
                 if (j >= 2 && !mbar_wait_bounded(&v_empty[sv], ((j >> 1) - 1) & 1, abort_flag)) {
                     give_up(11);
                     break;
                 }
                 mbar_arrive_expect_tx(&v_full[sv], kVBytes);
-                tma_load_2d(Vst + sv * kVBytes, &maps.vt, j * kAttnKeys, (b * a.kv_heads + kvh) * D,
-                            &v_full[sv]);
+                tma_load_2d(Vst + sv * kVBytes, &maps.vt, (j_begin + j) * kAttnKeys,
+                            (b * a.kv_heads + kvh) * D, &v_full[sv]);
             }
         }
         __syncwarp();
@@ -1445,9 +1487,9 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             // values . probabilities of step g (second sweep), issued one step late so that the
             // scores of step g + 1 are already under way while the softmax of step g runs
             auto issue_pv = [&](int g) {
-                const int st = g & 1, sv = (g - n) & 1;
-                if (!mbar_wait_bounded(&v_full[sv], ((g - n) >> 1) & 1, abort_flag) ||
-                    !mbar_wait_bounded(&p_full[st], ((g - n) >> 1) & 1, abort_flag)) {
+                const int st = g & 1, sv = (g - n1) & 1;
+                if (!mbar_wait_bounded(&v_full[sv], ((g - n1) >> 1) & 1, abort_flag) ||
+                    !mbar_wait_bounded(&p_full[st], ((g - n1) >> 1) & 1, abort_flag)) {
                     give_up(21);
                     return false;
                 }
@@ -1457,12 +1499,12 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
 #pragma unroll
                 for (int k = 0; k < kAttnKeys / 16; ++k)
                     umma_bf16(tmem_base + kColO, dp + 2 * k, dv + 2 * k, idesc_o,
-                              (g > n || k > 0) ? 1u : 0u);
+                              (g > n1 || k > 0) ? 1u : 0u);
                 umma_commit(&v_empty[sv]);
                 umma_commit(&p_empty[st]);
                 return true;
             };
-            for (int g = 0; ok && g < 2 * n; ++g) {
+            for (int g = 0; ok && g < steps; ++g) {
                 const int st = g & 1;
                 if (!mbar_wait_bounded(&k_full[st], (g >> 1) & 1, abort_flag) ||
                     (g >= 2 && !mbar_wait_bounded(&s_empty[st], ((g >> 1) - 1) & 1, abort_flag))) {
@@ -1483,10 +1525,10 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 }
                 umma_commit(&s_full[st]);
                 umma_commit(&k_empty[st]);  // the K stage is free as soon as these MMAs have read it
-                if (g > n) ok = issue_pv(g - 1);
+                if (g > n1) ok = issue_pv(g - 1);
             }
-            if (ok) ok = issue_pv(2 * n - 1);
-            if (ok) umma_commit(o_full);
+            if (ok && steps > n1) ok = issue_pv(steps - 1);
+            if (ok && steps > n1) umma_commit(o_full);
         }
         __syncwarp();
     } else {
@@ -1501,8 +1543,24 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                    static_cast<size_t>(min(row, T - 1)) * T;
         float m_run = -INFINITY, l_run = 0.f, inv_l = 0.f;
         bool ok = true;
-        for (int g = 0; g < 2 * n; ++g) {
-            const int st = g & 1, jb = g < n ? g : g - n;
+        const size_t stats_row = (static_cast<size_t>(item) * a.parts_max) * kTcRows + r;
+        if (a.mode == kAttnValues) {
+            // the first sweep ran as a launch of its own: combine the parts' statistics, in
+            // part order, exactly as the column parts of one CTA are combined below
+            float fm = -INFINITY;
+            for (int q = 0; q < parts; ++q)
+                fm = fmaxf(fm, __ldcg(a.stats_ws + (stats_row + static_cast<size_t>(q) * kTcRows) * 2));
+            const float fbase = fm == -INFINITY ? 0.f : fm;
+            float total = 0.f;
+            for (int q = 0; q < parts; ++q) {
+                const float* entry = a.stats_ws + (stats_row + static_cast<size_t>(q) * kTcRows) * 2;
+                total += __ldcg(entry + 1) * __expf(__ldcg(entry) - fbase);
+            }
+            m_run = fbase;
+            inv_l = total > 0.f ? __frcp_rn(total) : 0.f;
+        }
+        for (int g = 0; g < steps; ++g) {
+            const int st = g & 1, jb = j_begin + (g < n1 ? g : g - n1);
             ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[st], (g >> 1) & 1, abort_flag));
             if (!ok) {
                 if (lane == 0) give_up(30);
@@ -1524,7 +1582,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 if (mrow != nullptr && key < T) t = bf16_round(t + bf16_bits_to_float(__ldg(mrow + key)));
                 v[i] = (key < T && (!a.causal || key <= row)) ? t : -INFINITY;
             }
-            if (g < n) {
+            if (g < n1) {
                 float bm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) bm = fmaxf(bm, v[i]);
@@ -1537,7 +1595,7 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 for (int i = 0; i < 16; ++i) sum += __expf(v[i] - base);
                 l_run = sum;
                 m_run = nm;
-                if (g == n - 1) {
+                if (g == n1 - 1) {
                     // the four parts of a row meet: combine their maxima and denominators, in
                     // part order, so that all four get the same sum
                     stats[(part * kTcRows + r) * 2] = m_run;
@@ -1560,6 +1618,11 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                                  __expf(stats[(q * kTcRows + r) * 2] - fbase);
                     m_run = fbase;
                     inv_l = total > 0.f ? __frcp_rn(total) : 0.f;
+                    if (a.mode == kAttnStats && part == 0) {
+                        float* entry = a.stats_ws + (stats_row + static_cast<size_t>(part_index) * kTcRows) * 2;
+                        __stcg(entry, fm);
+                        __stcg(entry + 1, total);
+                    }
                     // nobody may overwrite the statistics (they alias the first P tile) before
                     // every warp has read them
                     __syncwarp();
@@ -1571,9 +1634,9 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                     }
                 }
             } else {
-                if (g >= n + 2 &&
+                if (g >= n1 + 2 &&
                     !__all_sync(0xffffffffu,
-                                mbar_wait_bounded(&p_empty[st], (((g - n) >> 1) - 1) & 1, abort_flag))) {
+                                mbar_wait_bounded(&p_empty[st], (((g - n1) >> 1) - 1) & 1, abort_flag))) {
                     if (lane == 0) give_up(31);
                     ok = false;
                     break;
@@ -1598,10 +1661,58 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 if (lane == 0) mbar_arrive(&p_full[st]);
             }
         }
-        ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(o_full, 0, abort_flag));
-        if (!ok && lane == 0 && *abort_flag == 0) give_up(32);
-        tc_fence_after();
-        if (ok) {
+        if (a.mode != kAttnStats) {
+            ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(o_full, 0, abort_flag));
+            if (!ok && lane == 0 && *abort_flag == 0) give_up(32);
+            tc_fence_after();
+        }
+        if (a.mode == kAttnValues && parts > 1) {
+            // Several CTAs hold parts of this tile's output: park this one ([column][row], a warp's
+            // 32 rows are one 128-byte line), and let the part that arrives last add them in key
+            // order and round once.  The sixteen warps meet at barriers: all leave or none.
+            if (!named_barrier_or(3, kTcSoftmaxWarps * 32, !ok)) {
+                const size_t tile_floats = static_cast<size_t>(D) * kTcRows;
+                float* parts_base = a.o_ws + static_cast<size_t>(item) * a.parts_max * tile_floats + r;
+                float* mine = parts_base + part_index * tile_floats;
+#pragma unroll 1
+                for (int c = 0; c < D / 64; ++c) {
+                    float o[16];
+                    tmem_load16(lane_addr + kColO + part * (D / 4) + c * 16, o);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (part * (D / 4) + c * 16 + i) * kTcRows, o[i]);
+                }
+                __threadfence();
+                named_barrier(4, kTcSoftmaxWarps * 32);
+                if (warp == 2 && lane == 0) {
+                    const int arrived = atomicAdd(a.counters + item, 1);
+                    *last_flag = arrived == parts - 1 ? 1 : 0;
+                    if (arrived == parts - 1) a.counters[item] = 0;  // re-arm for the next launch
+                    __threadfence();
+                }
+                named_barrier(4, kTcSoftmaxWarps * 32);
+                if (*last_flag != 0 && row < T) {
+                    unsigned short* orow = a.out + (static_cast<size_t>(b) * T + row) * (static_cast<size_t>(a.heads) * D) +
+                                           head * D + part * (D / 4);
+#pragma unroll 1
+                    for (int c = 0; c < D / 64; ++c) {
+                        float o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = 0.f;
+                        for (int q = 0; q < parts; ++q) {
+                            const float* theirs = parts_base + q * tile_floats;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                o[i] += __ldcg(theirs + (part * (D / 4) + c * 16 + i) * kTcRows);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+                            reinterpret_cast<uint4*>(orow + c * 16)[q] =
+                                make_uint4(pack_bf16(o[8 * q], o[8 * q + 1]), pack_bf16(o[8 * q + 2], o[8 * q + 3]),
+                                           pack_bf16(o[8 * q + 4], o[8 * q + 5]), pack_bf16(o[8 * q + 6], o[8 * q + 7]));
+                    }
+                }
+            }
+        } else if (ok && a.mode != kAttnStats) {
             unsigned short* orow = a.out + (static_cast<size_t>(b) * T + row) * (static_cast<size_t>(a.heads) * D) +
                                    head * D + part * (D / 4);
 #pragma unroll 1
@@ -1630,7 +1741,58 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
 
 inline int attention_tc_smem_bytes(int D) {
     return kTcRows * D * 2 + 2 * kAttnKeys * D * 2 + 2 * D * kAttnKeys * 2 + 2 * kTcRows * kAttnKeys * 2 +
-           20 * 8;
+           21 * 8;
+}
+
+// How attention_tc_kernel shares out the keys of a query tile (host side of the kernel's own
+// arithmetic): parts of at most `chunk` key blocks, at most four per tile.
+struct AttnParts {
+    int chunk = 0;      // 0: one CTA per tile, both sweeps in one launch
+    int parts_max = 1;
+    int grid_x = 0;     // CTAs per (head, batch row)
+    int items = 0;      // query tiles x heads x batch rows
+    size_t stats_floats = 0, output_floats = 0;
+};
+
+inline AttnParts attention_parts(int batch, int tokens, int heads, int D, bool causal, int sm_count) {
+    AttnParts p;
+    const int all_blocks = (tokens + kAttnKeys - 1) / kAttnKeys;
+    const int q_tiles = (tokens + kTcRows - 1) / kTcRows;
+    p.items = q_tiles * heads * batch;
+    p.grid_x = q_tiles;
+    const char* env = std::getenv("MEGABAKE_B200_ATTN_PARTS");
+    const bool allowed = env == nullptr || std::atoi(env) != 0;
+    if (!allowed || all_blocks < 4) return p;
+    // Measured on the gemma-2b shape: a CTA costs 4.5 us before and after its key blocks and
+    // 1.84 us per block and sweep, and CTAs run one per SM, in waves.  Sharing out the keys
+    // pays while the tiles alone leave half of the SMs idle (512 tokens: 32 tiles, -3 % on the
+    // step); at 2048 tokens the 128 tiles become 320 parts in three waves per launch and the
+    // step gets 1 % slower, so tiles stay whole there.  (What would pay at any length is one
+    // wave of CTAs that each walk an equal run of key blocks across tiles: not built.)
+    p.chunk = (all_blocks + 3) / 4 > 2 ? (all_blocks + 3) / 4 : 2;
+    bool wanted = 2 * p.items <= sm_count;
+    if (const char* forced = std::getenv("MEGABAKE_B200_ATTN_CHUNK")) {
+        const int value = std::atoi(forced);
+        if (value >= 1 && (all_blocks + value - 1) / value <= 8) {
+            p.chunk = value;
+            wanted = true;
+        }
+    }
+    if (!wanted) {
+        p.chunk = 0;
+        return p;
+    }
+    p.parts_max = (all_blocks + p.chunk - 1) / p.chunk;
+    p.grid_x = 0;
+    for (int qt = 0; qt < q_tiles; ++qt) {
+        const int last_row = (qt * kTcRows + kTcRows < tokens ? qt * kTcRows + kTcRows : tokens) - 1;
+        int visible = causal ? last_row / kAttnKeys + 1 : all_blocks;
+        if (visible > all_blocks) visible = all_blocks;
+        p.grid_x += (visible + p.chunk - 1) / p.chunk;
+    }
+    p.stats_floats = static_cast<size_t>(p.items) * p.parts_max * kTcRows * 2;
+    p.output_floats = static_cast<size_t>(p.items) * p.parts_max * kTcRows * D;
+    return p;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1791,6 +1953,8 @@ struct PrefillLaunch {
     AttnMaps attn_maps;
     unsigned short* vt = nullptr;  // transposed values of the tensor-core attention, or null
     int padded_tokens = 0;
+    bool tensor_core = false;      // the phase names scratch for transposed values
+    AttnParts parts;
 };
 
 }  // namespace prefill
@@ -1900,6 +2064,17 @@ cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillS
     for (size_t i = 0; i < phases.size(); ++i) {
         mb_phase& P = phases[i];
         st->launches[i].body = P.body;
+        if (P.body == MB_BODY_ATTN_PREFILL && P.slot[MB_AP_S_VT] >= 0) {
+            const AttnParts parts = attention_parts(P.i[MB_AP_I_BATCH], P.i[MB_AP_I_TOKENS], P.i[MB_AP_I_HEADS],
+                                                    P.i[MB_AP_I_HEAD_DIM], P.i[MB_AP_I_CAUSAL] != 0, sm_count);
+            st->launches[i].parts = parts;
+            st->launches[i].tensor_core = true;
+            if (parts.chunk > 0) {
+                const size_t need = parts.stats_floats + parts.output_floats;
+                if (need > floats) floats = need;
+                if (static_cast<size_t>(parts.items) > counters) counters = parts.items;
+            }
+        }
         if (P.body != MB_BODY_GEMM_TC) continue;
         GemmGeometry g = gemm_geometry(P, sm_count);
         st->launches[i].geometry = g;
@@ -1950,6 +2125,24 @@ cudaError_t prefill_create(std::vector<mb_phase>& phases, int sm_count, PrefillS
     st->counter_count = counters;
     *out = st;
     return cudaSuccess;
+}
+
+int prefill_launch_count(const PrefillState* st) {
+    using namespace prefill;
+    if (st == nullptr) return 0;
+    int count = 0;
+    for (size_t i = 0; i < st->launches.size(); ++i) {
+        const PrefillLaunch& L = st->launches[i];
+        if (L.body == MB_BODY_NOP) continue;
+        if (L.body != MB_BODY_ATTN_PREFILL || !L.tensor_core) {
+            ++count;
+            continue;
+        }
+        // values transposed by the rotary phase just before, or by a launch of their own
+        if (i == 0 || st->launches[i - 1].body != MB_BODY_ROPE_ROWS) ++count;
+        count += L.parts.chunk > 0 ? 2 : 1;
+    }
+    return count;
 }
 
 void prefill_destroy(PrefillState* st) {
@@ -2019,6 +2212,12 @@ int prefill_bind(PrefillState* st, const std::vector<mb_phase>& phases,
             a.mask_batch = P.i[MB_AP_I_MASK_BATCH];
             a.kv_rows = P.i[MB_AP_I_KV_CAPACITY] > 0 ? P.i[MB_AP_I_KV_CAPACITY] : a.tokens;
             a.scale = P.f[MB_AP_F_SCALE];
+            a.mode = kAttnWhole;
+            a.chunk = L.parts.chunk;
+            a.parts_max = L.parts.parts_max;
+            a.stats_ws = st->workspace;
+            a.o_ws = st->workspace == nullptr ? nullptr : st->workspace + L.parts.stats_floats;
+            a.counters = st->counters;
             L.vt = reinterpret_cast<unsigned short*>(addr(P.slot[MB_AP_S_VT]));
             if (L.vt != nullptr) {
                 const int D = P.i[MB_AP_I_HEAD_DIM];
@@ -2197,18 +2396,24 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                         if (err != cudaSuccess) return err;
                         chained = chaining_enabled();
                     }
-                    const dim3 grid((a.tokens + kTcRows - 1) / kTcRows, a.heads, a.batch);
+                    const dim3 grid(L.parts.grid_x, a.heads, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
                     const int ph = static_cast<int>(i);
-                    if (D == 64)
-                        err = launch_phase(attention_tc_kernel<64>, grid, dim3(kTcThreads), smem, stream,
-                                           chained, L.attn_maps, a, ctl, ph);
-                    else if (D == 128)
-                        err = launch_phase(attention_tc_kernel<128>, grid, dim3(kTcThreads), smem, stream,
-                                           chained, L.attn_maps, a, ctl, ph);
-                    else
-                        err = launch_phase(attention_tc_kernel<256>, grid, dim3(kTcThreads), smem, stream,
-                                           chained, L.attn_maps, a, ctl, ph);
+                    // keys shared out: the first sweep and the second one as two launches
+                    for (int pass = 0; pass < (L.parts.chunk > 0 ? 2 : 1) && err == cudaSuccess; ++pass) {
+                        AttnArgs args = a;
+                        args.mode = L.parts.chunk == 0 ? kAttnWhole : (pass == 0 ? kAttnStats : kAttnValues);
+                        if (D == 64)
+                            err = launch_phase(attention_tc_kernel<64>, grid, dim3(kTcThreads), smem, stream,
+                                               chained, L.attn_maps, args, ctl, ph);
+                        else if (D == 128)
+                            err = launch_phase(attention_tc_kernel<128>, grid, dim3(kTcThreads), smem, stream,
+                                               chained, L.attn_maps, args, ctl, ph);
+                        else
+                            err = launch_phase(attention_tc_kernel<256>, grid, dim3(kTcThreads), smem, stream,
+                                               chained, L.attn_maps, args, ctl, ph);
+                        chained = chaining_enabled();
+                    }
                     break;
                 }
                 cudaError_t launched = D == 64    ? attn_launch<64>(L.attn, stream)

@@ -115,7 +115,8 @@ class PlanInfo(ctypes.Structure):
         ("stages", ctypes.c_int32),
         ("barriers", ctypes.c_int32),
         ("sm_count", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("launches", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 1),
     ]
 
 
@@ -317,6 +318,7 @@ class Plan:
                "mb_plan_query")
         self.ctas, self.threads, self.smem_bytes = info.ctas, info.threads, info.smem_bytes
         self.stages, self.barriers, self.sm_count = info.stages, info.barriers, info.sm_count
+        self.launches = info.launches     # kernel launches per launch() call
         self._dynamic = (ctypes.c_uint64 * MB_MAX_DYNAMIC)()
 
     def bind(self, addresses: list[int]) -> None:

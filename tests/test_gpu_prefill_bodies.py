@@ -294,6 +294,30 @@ def test_rope_rows(rows, heads, kv_heads, dim):
 @pytest.mark.parametrize("explicit_mask", [False, True])
 @pytest.mark.parametrize("tensor_core", [True, False])
 def test_attention_prefill(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core):
+    _attention_case(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core)
+
+
+@pytest.mark.parametrize("env", [
+    {"MEGABAKE_B200_ATTN_PARTS": "0"},     # one CTA per query tile, both sweeps in one launch
+    {"MEGABAKE_B200_ATTN_CHUNK": "1"},     # every key block a part of its own
+    {"MEGABAKE_B200_ATTN_CHUNK": "3"},     # ragged parts
+], ids=lambda e: ",".join(f"{k[19:]}={v}" for k, v in e.items()))
+@pytest.mark.parametrize("explicit_mask", [False, True])
+def test_attention_prefill_key_parts(monkeypatch, env, explicit_mask):
+    """The keys of a query tile shared out over several CTAs (statistics launch, values launch,
+    last-arriver sum of the partial outputs) against the same oracle, twice with one plan."""
+    for key, value in env.items():
+        monkeypatch.setenv(key, value)
+    plan, out, runner = _attention_case(1, 500, 4, 2, 128, explicit_mask, True)   # runner owns the inputs
+    first = out.clone()
+    out.zero_()
+    plan.launch([], torch.cuda.current_stream().cuda_stream)   # arrival counters re-armed
+    torch.cuda.synchronize()
+    assert plan.status().code == 0
+    assert torch.equal(out, first)
+
+
+def _attention_case(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core):
     q = _bf16(batch, tokens, heads, dim, seed=tokens)
     k = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 1)
     v = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 2)
@@ -319,9 +343,10 @@ def test_attention_prefill(batch, tokens, heads, kv_heads, dim, explicit_mask, t
         padded = (tokens + 63) // 64 * 64
         ph.slot[rt.AP_S_VT] = runner.slot("vt", torch.full(
             (batch * kv_heads * dim, padded), float("nan"), dtype=torch.bfloat16, device="cuda"))
-    _run(runner, [ph])
+    plan = _run(runner, [ph])
     assert max_abs(out, ref) <= 2e-2, max_abs(out, ref)
     assert cosine(out, ref) > 0.9999
     # the probabilities are rounded after normalisation, as in the eager operator: nearly every
     # output element is bit-identical, the rest differ by fp32 summation order
     assert _mismatch(out, ref) < 0.1, _mismatch(out, ref)
+    return plan, out, runner

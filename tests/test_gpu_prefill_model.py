@@ -92,6 +92,22 @@ def test_prefill_chained_launches_give_the_same_bits(monkeypatch):
     assert torch.equal(plain, chained)
 
 
+def test_plan_reports_its_kernel_launches(monkeypatch):
+    """`mb_plan_info.launches`: one kernel per phase, plus one per attention phase whose keys are
+    shared out over several CTAs (statistics launch + values launch)."""
+    spec = models.get_spec("tiny-llama")
+    weights = models.init_weights(spec, 1)
+    layout = plan_prefill(models.direct_prefill_program(spec, 1, 300))
+    ids = torch.zeros((1, 300), dtype=torch.int64, device="cuda")
+    args = models.direct_prefill_arguments(spec, {k: v.cuda() for k, v in weights.items()},
+                                           models.inv_freq_buffer(spec).cuda(), ids)
+    monkeypatch.setenv("MEGABAKE_B200_ATTN_PARTS", "0")
+    assert BoundDecoder(layout, args).plan.launches == len(layout.phases)
+    monkeypatch.delenv("MEGABAKE_B200_ATTN_PARTS")
+    monkeypatch.setenv("MEGABAKE_B200_ATTN_CHUNK", "2")
+    assert BoundDecoder(layout, args).plan.launches == len(layout.phases) + spec.layers
+
+
 def test_prefill_reports_bad_token():
     from megabake_b200.diagnostics import CompilerError
 
