@@ -1273,7 +1273,7 @@ cudaError_t attn_configure() {
 //
 // Few query tiles: 512 tokens of 8 heads are 32 tiles on 148 SMs, and under a causal mask the
 // last tile has four times the key blocks of the first.  The keys of a tile can therefore be
-// shared out in parts of at most `chunk` blocks (the host decides when: attention_parts), and
+// shared out in parts of at most `chunk` blocks (the host decides how: attention_parts), and
 // the two sweeps become two launches, so that no CTA ever waits for another one: kAttnStats runs the first sweep over
 // its part and leaves each row's maximum and denominator; kAttnValues combines the parts'
 // statistics (as the column parts inside a CTA are combined), runs the second sweep over its part
@@ -1385,7 +1385,9 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int T = a.tokens;
-    const int head = blockIdx.y, b = blockIdx.z;
+    // heads vary fastest in the grid: CTAs are handed out heaviest work first over the whole
+    // grid, not head by head, so light CTAs fill in behind heavy ones
+    const int head = blockIdx.x, b = blockIdx.z;
     const int kvh = head / (a.heads / a.kv_heads);
     const int all_blocks = (T + kAttnKeys - 1) / kAttnKeys;
     const int q_tiles = (T + kTcRows - 1) / kTcRows;
@@ -1393,12 +1395,12 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
         const int last_row = min(tile * kTcRows + kTcRows, T) - 1;
         return a.causal ? min(last_row / kAttnKeys + 1, all_blocks) : all_blocks;
     };
-    // blockIdx.x -> (query tile, part of its keys), long rows first
+    // blockIdx.y -> (query tile, part of its keys), long rows first
     int qt = q_tiles - 1, part_index = 0, parts = 1;
     if (a.mode == kAttnWhole) {
-        qt = q_tiles - 1 - static_cast<int>(blockIdx.x);
+        qt = q_tiles - 1 - static_cast<int>(blockIdx.y);
     } else {
-        int x = blockIdx.x;
+        int x = blockIdx.y;
         for (;; --qt) {
             parts = (visible_blocks(qt) + a.chunk - 1) / a.chunk;
             if (x < parts || qt == 0) break;
@@ -1763,25 +1765,51 @@ inline AttnParts attention_parts(int batch, int tokens, int heads, int D, bool c
     const char* env = std::getenv("MEGABAKE_B200_ATTN_PARTS");
     const bool allowed = env == nullptr || std::atoi(env) != 0;
     if (!allowed || all_blocks < 4) return p;
-    // Measured on the gemma-2b shape: a CTA costs 4.5 us before and after its key blocks and
-    // 1.84 us per block and sweep, and CTAs run one per SM, in waves.  Sharing out the keys
-    // pays while the tiles alone leave half of the SMs idle (512 tokens: 32 tiles, -3 % on the
-    // step); at 2048 tokens the 128 tiles become 320 parts in three waves per launch and the
-    // step gets 1 % slower, so tiles stay whole there.  (What would pay at any length is one
-    // wave of CTAs that each walk an equal run of key blocks across tiles: not built.)
-    p.chunk = (all_blocks + 3) / 4 > 2 ? (all_blocks + 3) / 4 : 2;
-    bool wanted = 2 * p.items <= sm_count;
-    if (const char* forced = std::getenv("MEGABAKE_B200_ATTN_CHUNK")) {
-        const int value = std::atoi(forced);
-        if (value >= 1 && (all_blocks + value - 1) / value <= 8) {
-            p.chunk = value;
-            wanted = true;
+    // Which chunk?  Measured on the gemma-2b shape: a CTA costs 4.5 us before and after its key
+    // blocks and 1.84 us per block and sweep, CTAs run one per SM and are handed out in grid
+    // order, heaviest first.  The host plays that schedule for every way of cutting the keys
+    // into at most eight parts per tile, and for whole tiles, and keeps the shortest.
+    auto visible_blocks = [&](int qt) {
+        const int last_row = (qt * kTcRows + kTcRows < tokens ? qt * kTcRows + kTcRows : tokens) - 1;
+        const int visible = causal ? last_row / kAttnKeys + 1 : all_blocks;
+        return visible < all_blocks ? visible : all_blocks;
+    };
+    auto makespan = [&](int chunk, double per_block, double merge) {
+        std::vector<double> free_at(sm_count, 0.0);
+        double end = 0.0;
+        for (int qt = q_tiles - 1; qt >= 0; --qt) {
+            const int visible = visible_blocks(qt);
+            const int parts = chunk > 0 ? (visible + chunk - 1) / chunk : 1;
+            const int per_part = (visible + parts - 1) / parts;
+            for (int part = 0; part < parts; ++part) {
+                const int begin = part * per_part < visible ? part * per_part : visible;
+                const int blocks = (begin + per_part < visible ? begin + per_part : visible) - begin;
+                for (int copy = 0; copy < heads * batch; ++copy) {
+                    size_t first = 0;
+                    for (size_t m = 1; m < free_at.size(); ++m)
+                        if (free_at[m] < free_at[first]) first = m;
+                    free_at[first] += 4.5 + blocks * per_block + (parts > 1 ? merge : 0.0);
+                    if (free_at[first] > end) end = free_at[first];
+                }
+            }
+        }
+        return end;
+    };
+    double best = makespan(0, 2 * 1.84, 0.0);
+    for (int parts = 2; parts <= 8 && parts <= all_blocks; ++parts) {
+        const int chunk = (all_blocks + parts - 1) / parts;
+        if ((all_blocks + chunk - 1) / chunk != parts) continue;  // same cut as a smaller count
+        const double cost = makespan(chunk, 1.84, 0.0) + makespan(chunk, 1.84, 2.0) + 3.0;
+        if (cost < best) {
+            best = cost;
+            p.chunk = chunk;
         }
     }
-    if (!wanted) {
-        p.chunk = 0;
-        return p;
+    if (const char* forced = std::getenv("MEGABAKE_B200_ATTN_CHUNK")) {
+        const int value = std::atoi(forced);
+        if (value >= 1 && (all_blocks + value - 1) / value <= 8) p.chunk = value;
     }
+    if (p.chunk == 0) return p;
     p.parts_max = (all_blocks + p.chunk - 1) / p.chunk;
     p.grid_x = 0;
     for (int qt = 0; qt < q_tiles; ++qt) {
@@ -2396,7 +2424,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                         if (err != cudaSuccess) return err;
                         chained = chaining_enabled();
                     }
-                    const dim3 grid(L.parts.grid_x, a.heads, a.batch);
+                    const dim3 grid(a.heads, L.parts.grid_x, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
                     const int ph = static_cast<int>(i);
                     // keys shared out: the first sweep and the second one as two launches
