@@ -2300,13 +2300,18 @@ int transpose_blocks(const prefill::TransposeArgs& t, int batch) {
     return (t.padded / 64) * (t.D / 64) * batch * t.kv_heads;
 }
 
-// Read at every launch (not cached) so that one process can run both ways.
-bool chaining_enabled() {
-    // off unless asked for: measured on the gemma-2b shape, chaining takes 3-4 % off a step
-    // launched kernel by kernel (128 and 512 tokens) and adds 1-2 % to the same step
-    // replayed from a CUDA graph, the way the backend runs it
-    const char* value = std::getenv("MEGABAKE_B200_PREFILL_CHAIN");
-    return value != nullptr && std::atoi(value) != 0;
+// Whether the kernels of one prefill are chained by programmatic dependent launch.  Measured
+// on the gemma-2b shape: a launch boundary between two dependent kernels costs about 5 us on a
+// stream (CTA-level stamps of consecutive GEMMs), chaining takes 3-4 % off a step launched
+// kernel by kernel at 128 and 512 tokens, and adds 1-2 % to the same step replayed from a CUDA
+// graph.  So: on for plain stream launches, off while the stream is being captured;
+// MEGABAKE_B200_PREFILL_CHAIN = 0 / 1 forces it (read at every launch, not cached, so that one
+// process can run both ways).
+bool chaining_enabled(cudaStream_t stream) {
+    if (const char* value = std::getenv("MEGABAKE_B200_PREFILL_CHAIN")) return std::atoi(value) != 0;
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &status) != cudaSuccess) return false;
+    return status == cudaStreamCaptureStatusNone;
 }
 
 }  // namespace
@@ -2321,6 +2326,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
         if (s < 0) return 0ull;
         return static_cast<unsigned int>(s) < n_dynamic ? dyn[s] : slots[s];
     };
+    const bool chain = chaining_enabled(stream);
     bool chained = false;  // the first kernel of an invocation follows foreign work: plain launch
     size_t transposed_by = phases.size() + 1;  // the rotary phase that transposed the values, if any
     cudaError_t err = cudaSuccess;
@@ -2422,7 +2428,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                                            dim3(transpose_blocks(transpose, a.batch)), dim3(256), 0,
                                            stream, chained, transpose);
                         if (err != cudaSuccess) return err;
-                        chained = chaining_enabled();
+                        chained = chain;
                     }
                     const dim3 grid(a.heads, L.parts.grid_x, a.batch);
                     const int smem = attention_tc_smem_bytes(D);
@@ -2440,7 +2446,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
                         else
                             err = launch_phase(attention_tc_kernel<256>, grid, dim3(kTcThreads), smem, stream,
                                                chained, L.attn_maps, args, ctl, ph);
-                        chained = chaining_enabled();
+                        chained = chain;
                     }
                     break;
                 }
@@ -2455,7 +2461,7 @@ cudaError_t prefill_launch(PrefillState* st, const std::vector<mb_phase>& phases
         }
         if (err == cudaSuccess) err = cudaGetLastError();
         if (err != cudaSuccess) return err;
-        if (P.body != MB_BODY_NOP) chained = chaining_enabled();
+        if (P.body != MB_BODY_NOP) chained = chain;
     }
     return cudaSuccess;
 }

@@ -82,10 +82,11 @@ def test_prefill_matches_reference_fixture(key):
 
 
 def test_prefill_chained_launches_give_the_same_bits(monkeypatch):
-    """Programmatic dependent launch between the phases (off by default) changes when a
-    kernel's prologue runs, never what it reads."""
+    """Programmatic dependent launch between the phases (on for plain stream launches, off
+    under graph capture) changes when a kernel's prologue runs, never what it reads."""
     spec = models.get_spec("tiny-gemma256")
     tokens = torch.randint(0, spec.vocab, (2, 150), generator=torch.Generator().manual_seed(5))
+    monkeypatch.setenv("MEGABAKE_B200_PREFILL_CHAIN", "0")
     _, _, _, plain = _prefill_on_gpu("tiny-gemma256", 3, tokens)
     monkeypatch.setenv("MEGABAKE_B200_PREFILL_CHAIN", "1")
     _, _, _, chained = _prefill_on_gpu("tiny-gemma256", 3, tokens)
