@@ -1893,11 +1893,12 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
     int persistent_split = 1;
     const char* persistent_env = std::getenv("MEGABAKE_B200_GEMM_PERSISTENT");
     if (persistent_env == nullptr || std::atoi(persistent_env) != 0) {
-        // Tile width and number of reduction slices by a cost model in microseconds, with the
-        // figures measured on this kernel: a CTA takes a k-block every 0.44 us (256 columns)
-        // or 0.29 us (128) when every SM streams operands; the weights cannot arrive faster
-        // than HBM delivers them; a sliced tile pays for parking its partial sums and for
-        // the last slice's pass over all of them.
+        // Tile width and number of reduction slices by a cost model in microseconds, fitted to
+        // a sweep of both over the twelve GEMM shapes of the gemma-2b prefill (128 / 512 / 2048
+        // rows): a CTA takes a k-block every 0.44 us (256 columns) or 0.30 us (128) when every
+        // SM streams operands; the weights cannot arrive faster than HBM delivers them; a wave
+        // of sliced tiles pays 4 us (2 us) for parking its partial sums and the last slice
+        // 2 us (1 us) per slice for its pass over them, a chain of L2 round trips.
         g.persistent = 1;
         double best = 1e30;
         const double weight_bytes = 2.0 * K * (pair ? 2 : 1) * [&] {
@@ -1912,10 +1913,11 @@ GemmGeometry gemm_geometry(const mb_phase& P, int sm_count) {
                 const int units = tiles * split;
                 const int waves = (units + sm_count - 1) / sm_count;
                 const int per_unit = (g.kblocks + split - 1) / split;
-                double stream = waves * per_unit * (bn == 256 ? 0.44 : 0.29);
+                double stream = waves * per_unit * (bn == 256 ? 0.44 : 0.30);
                 const double hbm = weight_bytes / 6.0e6;
                 if (stream < hbm) stream = hbm;
-                const double slices = split > 1 ? (bn == 256 ? 3.0 : 1.5) * waves + 0.4 * split : 0.0;
+                const double slices =
+                    split > 1 ? (bn == 256 ? 4.0 : 2.0) * waves + (bn == 256 ? 2.0 : 1.0) * split : 0.0;
                 const double cost = stream + slices;
                 if (cost < best - 1e-9) {
                     best = cost;
