@@ -1545,6 +1545,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                    static_cast<size_t>(min(row, T - 1)) * T;
         float m_run = -INFINITY, l_run = 0.f, inv_l = 0.f;
         bool ok = true;
+        // a power of two times a bf16 value is exact: rounding the product again is a no-op
+        const bool scale_exact = (__float_as_uint(a.scale) & 0x007fffffu) == 0u;
         const size_t stats_row = (static_cast<size_t>(item) * a.parts_max) * kTcRows + r;
         if (a.mode == kAttnValues) {
             // the first sweep ran as a launch of its own: combine the parts' statistics, in
@@ -1575,14 +1577,29 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[st]);  // per-thread arrivals would serialise
             const int key0 = jb * kAttnKeys + part * 16;
-            // scores with the operator's rounding points; -inf marks keys that are not visible
+            // scores with the operator's rounding points; -inf marks keys that are not visible.
+            // The softmax warps are bound by the instructions they issue (measured: two sets
+            // of warps on alternate steps gain nothing), so the common block -- every key
+            // visible to every row of the tile, no mask tensor -- skips the visibility tests,
+            // and a power-of-two scale (head sizes 64 and 256) skips a rounding that changes
+            // nothing.
+            const bool interior = mrow == nullptr && jb * kAttnKeys + kAttnKeys <= T &&
+                                  (!a.causal || jb * kAttnKeys + kAttnKeys - 1 <= q0);
+            if (interior && scale_exact) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int key = key0 + i;
-                float t = bf16_round(v[i]);
-                t = bf16_round(t * a.scale);
-                if (mrow != nullptr && key < T) t = bf16_round(t + bf16_bits_to_float(__ldg(mrow + key)));
-                v[i] = (key < T && (!a.causal || key <= row)) ? t : -INFINITY;
+                for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]) * a.scale;
+            } else if (interior) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = bf16_round(bf16_round(v[i]) * a.scale);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int key = key0 + i;
+                    float t = bf16_round(v[i]);
+                    t = bf16_round(t * a.scale);
+                    if (mrow != nullptr && key < T) t = bf16_round(t + bf16_bits_to_float(__ldg(mrow + key)));
+                    v[i] = (key < T && (!a.causal || key <= row)) ? t : -INFINITY;
+                }
             }
             if (g < n1) {
                 float bm = -INFINITY;
