@@ -49,6 +49,15 @@ __device__ __forceinline__ void chain_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// Two floats to a bf16 pair in one instruction (same bits as two cvt.rn.bf16.f32, checked over
+// every finite float): the attention's softmax warps and the GEMM epilogue are bound by the
+// instructions they issue, and packing was four of them per pair.
+__device__ __forceinline__ unsigned int pack_bf16_pair(float lo, float hi) {
+    unsigned int packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+    return packed;
+}
+
 // ---------------------------------------------------------------------------------------
 // Row kernels
 // ---------------------------------------------------------------------------------------
@@ -682,8 +691,9 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmArgs& a, int seg, int
             unsigned int t[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                t[e] = pack_bf16(y[8 * q + 2 * e], y[8 * q + 2 * e + 1]);
-                if (res) t[e] = pack_bf16(lo_bf16(hw[e]) + lo_bf16(t[e]), hi_bf16(hw[e]) + hi_bf16(t[e]));
+                t[e] = pack_bf16_pair(y[8 * q + 2 * e], y[8 * q + 2 * e + 1]);
+                if (res)
+                    t[e] = pack_bf16_pair(lo_bf16(hw[e]) + lo_bf16(t[e]), hi_bf16(hw[e]) + hi_bf16(t[e]));
             }
             reinterpret_cast<uint4*>(out)[q] = make_uint4(t[0], t[1], t[2], t[3]);
         }
@@ -1663,8 +1673,8 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 unsigned int packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                    packed[i] = pack_bf16(__expf(v[2 * i] - m_run) * inv_l,
-                                          __expf(v[2 * i + 1] - m_run) * inv_l);
+                    packed[i] = pack_bf16_pair(__expf(v[2 * i] - m_run) * inv_l,
+                                               __expf(v[2 * i + 1] - m_run) * inv_l);
                 // row r of the P tile: 128 bytes, 16-byte chunk c stored at c ^ (r % 8) (the
                 // 128-byte swizzle the MMA's shared-memory descriptor expects)
                 unsigned char* prow = Ps + st * kPBytes + r * 128;
