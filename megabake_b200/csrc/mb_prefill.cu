@@ -52,6 +52,11 @@ __device__ __forceinline__ void chain_wait() {
 // Two floats to a bf16 pair in one instruction (same bits as two cvt.rn.bf16.f32, checked over
 // every finite float): the attention's softmax warps and the GEMM epilogue are bound by the
 // instructions they issue, and packing was four of them per pair.
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned int pack_bf16_pair(float lo, float hi) {
     unsigned int packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -1595,9 +1600,15 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
             // nothing.
             const bool interior = mrow == nullptr && jb * kAttnKeys + kAttnKeys <= T &&
                                   (!a.causal || jb * kAttnKeys + kAttnKeys - 1 <= q0);
-            if (interior && scale_exact) {
+            // `unit`: what one unit of v is worth in scaled scores.  On the common path v stays
+            // unscaled and the scale rides along in the exponent's multiplier and in the row
+            // maximum (a power of two commutes with both): one multiplication per element less.
+            const bool folded = interior && scale_exact;
+            const float unit = folded ? a.scale : 1.0f;
+            const float to_log2 = unit * 1.4426950408889634f;
+            if (folded) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]) * a.scale;
+                for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]);
             } else if (interior) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = bf16_round(bf16_round(v[i]) * a.scale);
@@ -1615,13 +1626,23 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                 float bm = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) bm = fmaxf(bm, v[i]);
-                const float nm = fmaxf(m_run, bm);
+                const float nm = fmaxf(m_run, bm * unit);
                 // exp(-inf - x) is 0 for every finite x: invisible keys need no branch, only a
                 // maximum that is still -inf must not be subtracted
                 const float base = nm == -INFINITY ? 0.f : nm;
                 float sum = l_run * __expf(m_run - base);
+                // exp(s - base) as 2^(v * to_log2 - base * log2 e), one fused multiply-add and one
+                // ex2 per element (the softmax warps are bound by the instructions they issue)
+                // (a mask tensor of finite minima can leave a maximum near -3.4e38, whose product
+                // with log2 e overflows: such rows subtract first, as the plain formula does)
+                const float base_log2 = base * 1.4426950408889634f;
+                if (base > -1e30f) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) sum += __expf(v[i] - base);
+                    for (int i = 0; i < 16; ++i) sum += exp2_approx(__fmaf_rn(v[i], to_log2, -base_log2));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) sum += __expf(v[i] * unit - base);
+                }
                 l_run = sum;
                 m_run = nm;
                 if (g == n1 - 1) {
@@ -1670,11 +1691,20 @@ attention_tc_kernel(const __grid_constant__ AttnMaps maps, const AttnArgs a, Con
                     ok = false;
                     break;
                 }
+                const float max_log2 = m_run * 1.4426950408889634f;
                 unsigned int packed[8];
+                if (m_run > -1e30f) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    packed[i] = pack_bf16_pair(__expf(v[2 * i] - m_run) * inv_l,
-                                               __expf(v[2 * i + 1] - m_run) * inv_l);
+                    for (int i = 0; i < 8; ++i)
+                        packed[i] = pack_bf16_pair(
+                            exp2_approx(__fmaf_rn(v[2 * i], to_log2, -max_log2)) * inv_l,
+                            exp2_approx(__fmaf_rn(v[2 * i + 1], to_log2, -max_log2)) * inv_l);
+                } else {  // a row whose every key is masked by a finite minimum: subtract first
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        packed[i] = pack_bf16_pair(__expf(v[2 * i] * unit - m_run) * inv_l,
+                                                   __expf(v[2 * i + 1] * unit - m_run) * inv_l);
+                }
                 // row r of the P tile: 128 bytes, 16-byte chunk c stored at c ^ (r % 8) (the
                 // 128-byte swizzle the MMA's shared-memory descriptor expects)
                 unsigned char* prow = Ps + st * kPBytes + r * 128;
