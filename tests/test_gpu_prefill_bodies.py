@@ -317,12 +317,22 @@ def test_attention_prefill_key_parts(monkeypatch, env, explicit_mask):
     assert torch.equal(out, first)
 
 
-def _attention_case(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core):
+@pytest.mark.parametrize("tensor_core", [True, False])
+def test_attention_prefill_rows_without_a_visible_key(tensor_core):
+    """A mask tensor of finite minima (the Hugging Face form) that hides every key from some
+    rows -- the rows of a left-padded prompt: eager softmax gives them the mean of V, and so
+    must the kernel (their maximum is near -3.4e38, where a careless exponent overflows)."""
+    _attention_case(1, 200, 4, 2, 64, True, tensor_core, hidden_rows=(0, 5, 150))
+
+
+def _attention_case(batch, tokens, heads, kv_heads, dim, explicit_mask, tensor_core, hidden_rows=()):
     q = _bf16(batch, tokens, heads, dim, seed=tokens)
     k = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 1)
     v = _bf16(batch, tokens, kv_heads, dim, seed=tokens + 2)
     scale = dim ** -0.5
     mask = oracle.causal_mask(batch, tokens).contiguous()
+    for hidden in hidden_rows:
+        mask[:, :, hidden, :] = torch.finfo(torch.bfloat16).min
     ref = oracle.prefill_attention(q, k, v, mask, scale)          # [B*H, T, D]
     ref = ref.view(batch, heads, tokens, dim).transpose(1, 2).reshape(batch * tokens, heads * dim)
     out = torch.zeros(batch * tokens, heads * dim, dtype=torch.bfloat16, device="cuda")
