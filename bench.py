@@ -270,7 +270,7 @@ def parity_check(spec, weights, inv_freq, state, ids, position, decoder, ids_dev
     }
 
 
-def cpu_reference_run(name: str, steps: int, warmup: int, budget_s: float, rank: int = 0) -> dict:
+def cpu_reference_run(name: str, steps: int, warmup: int, time_limit_s: float, rank: int = 0) -> dict:
     """Time the CPU port of the reference forward on this box's host cores."""
     import torch
 
@@ -309,7 +309,7 @@ def cpu_reference_run(name: str, steps: int, warmup: int, budget_s: float, rank:
             dt = time.perf_counter() - t0
             if call >= warmup:
                 times.append(dt)
-            if time.perf_counter() - started > budget_s and len(times) >= 2:
+            if time.perf_counter() - started > time_limit_s and len(times) >= 2:
                 break
     per_step = statistics.median(times)
     return {
@@ -330,7 +330,7 @@ def prefill_flops(spec, tokens: int) -> tuple[float, float]:
     return 2.0 * params * tokens, 4.0 * tokens * tokens * q_dim * spec.layers
 
 
-def cpu_prefill_run(name: str, steps: int, budget_s: float) -> dict:
+def cpu_prefill_run(name: str, steps: int, time_limit_s: float) -> dict:
     """Time the CPU port of the reference prefill forward on this box's host cores."""
     import torch
 
@@ -352,7 +352,7 @@ def cpu_prefill_run(name: str, steps: int, budget_s: float) -> dict:
             t0 = time.perf_counter()
             oracle.prefill(cfg, ow, ids)
             times.append(time.perf_counter() - t0)
-            if time.perf_counter() - started > budget_s:
+            if time.perf_counter() - started > time_limit_s:
                 break
     per_step = statistics.median(times)
     return {
@@ -490,7 +490,7 @@ def run_prefill(args) -> None:
             "clocks": sampler.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
-            base = cpu_prefill_run(args.workload, 3, budget_s=25.0)
+            base = cpu_prefill_run(args.workload, 3, time_limit_s=25.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         emit(line)
     if distributed:
@@ -510,7 +510,7 @@ def run_reference(args) -> None:
         return
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.workload in PREFILL_WORKLOADS:
-        result = cpu_prefill_run(args.workload, steps, budget_s=120.0)
+        result = cpu_prefill_run(args.workload, steps, time_limit_s=120.0)
         emit({
             "impl": "reference", "metric": "prefill_tokens_per_s", "value": result["value"],
             "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
@@ -524,7 +524,7 @@ def run_reference(args) -> None:
             "gpu_launches": 0, "device": "host cpu",
         })
         return
-    result = cpu_reference_run(args.workload, steps, warmup, budget_s=120.0)
+    result = cpu_reference_run(args.workload, steps, warmup, time_limit_s=120.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": result["value"], "unit": UNIT,
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "steps_timed": result["steps"],
@@ -759,7 +759,7 @@ def _report(args, spec, program, layout, batch, keys, steps, warmup, device_ms, 
                         "ids read once at the end",
             }
         if world == 1 and not args.no_cpu_baseline:
-            base = cpu_reference_run(args.workload, 8, 1, budget_s=25.0)
+            base = cpu_reference_run(args.workload, 8, 1, time_limit_s=25.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         emit(line)
     if distributed:

@@ -343,7 +343,7 @@ void mb_plan_destroy(mb_plan* plan);
 /* ---- decode attention that allocates nothing ---------------------------------------------
  * No counterpart in the reference (its attention body only exists inside a compiled plan).
  * For callers that must not allocate device memory where they need an attention step (a
- * plugin inside a foreign stream-ordered pipeline, a process living on a memory budget fixed
+ * plugin inside a foreign stream-ordered pipeline, a process living on an amount of memory fixed
  * at start-up, a region where cudaMalloc would synchronise the device): the same decode
  * attention as MB_BODY_ATTN_DECODE -- RoPE of q and the new k, append at valid_length,
  * valid_length += 1, attention over every valid key -- with its scratch (split-key partials,

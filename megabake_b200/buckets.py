@@ -9,7 +9,7 @@ bucket's length along ``output_dim`` back to the real length.
 
 That is exact only if results at real positions cannot see the padding -- true for a causal
 decoder padded after its last token.  The claim is checked on the first call of every bucket,
-with the eager module as the judge: two different paddings must give bit-identical results at
+with the eager module as the arbiter: two different paddings must give bit-identical results at
 the real positions, and padded and unpadded eager results must agree there up to the rounding
 noise of differently shaped library kernels (relative L2 distance at most 5 %).
 

@@ -1883,7 +1883,7 @@ cudaError_t decode_launch(const KernelParams& params, int ctas, int smem_bytes,
 //
 // Some hosts may not allocate device memory at the point where they need one attention
 // step: a plugin called from inside someone else's stream-ordered pipeline, a process that
-// runs with a fixed memory budget handed out at start-up, a caller inside a region where
+// runs inside a fixed amount of memory handed out at start-up, a caller inside a region where
 // cudaMalloc would synchronise the device.  For them this entry point runs the same
 // attention body as the plan path, but everything the plan path keeps in allocated memory
 // (phase table, control block, split-key partials, arrival counters) lives either in the

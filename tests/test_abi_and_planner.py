@@ -138,7 +138,7 @@ def test_planner_refusals():
         planner.plan_decode(models.direct_program(odd, 1, 16))
 
 
-def test_weight_bytes_match_survey_table():
+def test_weight_bytes_match_the_roofline_table():
     # bytes of weights one decode step reads (bf16), per the hot-path scope table
     expect = {"smollm-135m": 134_515_008, "qwen2-0.5b": 494_032_768,
               "llama-3.2-1b": 1_235_814_400, "smollm-1.7b": 1_711_376_384}

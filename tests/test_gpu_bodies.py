@@ -2,7 +2,7 @@
 
 GEMV references are computed in fp64 from the bf16 operands and rounded once, the way the
 reference's own Blackwell GEMM test does (``tests/gpu/test_blackwell_gemm.py:60-63``): a
-bf16 library GEMM on the GPU is not accurate enough to be the judge.
+bf16 library GEMM on the GPU is not accurate enough to be the yardstick.
 """
 
 import math
