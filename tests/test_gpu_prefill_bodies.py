@@ -308,7 +308,7 @@ def test_attention_prefill_key_parts(monkeypatch, env, explicit_mask):
     last-arriver sum of the partial outputs) against the same oracle, twice with one plan."""
     for key, value in env.items():
         monkeypatch.setenv(key, value)
-    plan, out, runner = _attention_case(1, 500, 4, 2, 128, explicit_mask, True)   # runner owns the inputs
+    plan, out, runner = _attention_case(2, 300, 4, 2, 128, explicit_mask, True)   # runner owns the inputs
     first = out.clone()
     out.zero_()
     plan.launch([], torch.cuda.current_stream().cuda_stream)   # arrival counters re-armed
